@@ -1,0 +1,171 @@
+"""TEST INFRASTRUCTURE ONLY: ctypes doorway onto the CPU oracle (oracle/libsmat_oracle.so) and, when it
+was built, onto the unmodified reference CPU code (oracle/_ref/libsmat_ref.so).
+
+Only tests, the smoke check and the benchmark's CPU-baseline leg import this package; the product
+package never does.  Build with ``make -C oracle`` (and ``make -C oracle ref`` where the reference
+tree is present).
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+_REF = None
+
+i64p = np.ctypeslib.ndpointer(dtype=np.int64, flags="C_CONTIGUOUS")
+i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
+u16p = np.ctypeslib.ndpointer(dtype=np.uint16, flags="C_CONTIGUOUS")
+f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
+
+
+def build(ref_root="/root/reference"):
+    """Compile the oracle; also the reference-backed library/programs when the reference tree exists."""
+    subprocess.check_call(["make", "-s", "-C", _HERE, "all"])
+    if os.path.isdir(os.path.join(ref_root, "preprocess", "src", "general")):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REF={ref_root}"])
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        path = os.path.join(_HERE, "libsmat_oracle.so")
+        if not os.path.exists(path):
+            build()
+        L = C.CDLL(path)
+        L.orc_double_to_half_bits.restype = C.c_uint16
+        L.orc_double_to_half_bits.argtypes = [C.c_double]
+        L.orc_read_mtx.argtypes = [C.c_char_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64),
+                                   C.POINTER(C.c_int), C.POINTER(C.POINTER(C.c_int)), C.POINTER(C.POINTER(C.c_int)),
+                                   C.POINTER(C.POINTER(C.c_uint16))]
+        L.orc_free.argtypes = [C.c_void_p]
+        L.orc_csr_to_bcsr.argtypes = [C.c_int64, C.c_int64, i32p, i32p, u16p, C.POINTER(C.c_int64), i32p,
+                                      C.c_void_p, C.c_void_p]
+        L.orc_bcsr_spmm_f32.argtypes = [u16p, i32p, i32p, u16p, f32p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                        C.c_int64, C.c_int]
+        L.orc_jaccard_group.restype = C.c_float
+        L.orc_jaccard_group.argtypes = [i64p, C.c_int64, C.c_int64, i64p, C.c_int64, C.c_int64, C.c_int64]
+        L.orc_hamming_group.restype = C.c_float
+        L.orc_hamming_group.argtypes = [i64p, C.c_int64, C.c_int64, i64p, C.c_int64, C.c_int64, C.c_int64]
+        L.orc_keeper_grouping.argtypes = [C.c_int64, i64p, i64p, C.c_float, C.c_int64, C.c_int64, C.c_int, i64p]
+        L.orc_get_permutation.argtypes = [C.c_int64, i64p, i64p]
+        L.orc_fixed_size_grouping.argtypes = [C.c_int64, i64p, C.c_int64, i64p]
+        L.orc_reorder_rows.argtypes = [C.c_int64, i64p, i64p, C.c_float, C.c_int64, C.c_int64, i64p, i64p]
+        _LIB = L
+    return _LIB
+
+
+def ref_dir():
+    return os.path.join(_HERE, "_ref")
+
+
+def have_ref():
+    return os.path.exists(os.path.join(ref_dir(), "libsmat_ref.so"))
+
+
+def ref():
+    """The unmodified reference CPU code (None if oracle/_ref was not built)."""
+    global _REF
+    if _REF is None and have_ref():
+        L = C.CDLL(os.path.join(ref_dir(), "libsmat_ref.so"))
+        L.ref_jaccard_group.restype = C.c_float
+        L.ref_jaccard_group.argtypes = [i64p, C.c_long, C.c_long, i64p, C.c_long, C.c_long, C.c_long]
+        L.ref_hamming_group.restype = C.c_float
+        L.ref_hamming_group.argtypes = [i64p, C.c_long, C.c_long, i64p, C.c_long, C.c_long, C.c_long]
+        L.ref_group_and_permute.restype = C.c_long
+        L.ref_group_and_permute.argtypes = [C.c_char_p, C.c_float, C.c_long, C.c_long, C.c_int, C.c_long, i64p, i64p]
+        L.ref_get_permutation.restype = C.c_long
+        L.ref_get_permutation.argtypes = [C.c_long, i64p, i64p]
+        L.ref_fixed_size_grouping.restype = C.c_long
+        L.ref_fixed_size_grouping.argtypes = [C.c_long, i64p, C.c_long, i64p]
+        L.ref_vbr_multiply.argtypes = [C.c_long, C.c_long, C.c_long, C.c_long, i64p, i64p, f32p, C.c_long, C.c_long,
+                                       f32p, C.c_int, f32p]
+        _REF = L
+    return _REF
+
+
+# ----------------------------------------------------------------------------------------------
+# numpy-level helpers
+# ----------------------------------------------------------------------------------------------
+def read_mtx(path):
+    """mmio_allinone restatement -> (M, K, rowptr int32, colidx int32, vals float16, is_symmetric)."""
+    L = lib()
+    M, N, nnz, sym = C.c_int64(), C.c_int64(), C.c_int64(), C.c_int()
+    rp, ci, vv = C.POINTER(C.c_int)(), C.POINTER(C.c_int)(), C.POINTER(C.c_uint16)()
+    rc = L.orc_read_mtx(path.encode(), C.byref(M), C.byref(N), C.byref(nnz), C.byref(sym), C.byref(rp), C.byref(ci),
+                        C.byref(vv))
+    if rc != 0:
+        raise IOError(f"orc_read_mtx({path}) -> {rc}")
+    rowptr = np.ctypeslib.as_array(rp, shape=(M.value + 1,)).copy()
+    colidx = np.ctypeslib.as_array(ci, shape=(max(nnz.value, 1),))[: nnz.value].copy()
+    vals = np.ctypeslib.as_array(vv, shape=(max(nnz.value, 1),))[: nnz.value].copy().view(np.float16)
+    for p in (rp, ci, vv):
+        L.orc_free(C.cast(p, C.c_void_p))
+    return M.value, N.value, rowptr, colidx, vals, bool(sym.value)
+
+
+def csr_to_bcsr(M, K, rowptr, colidx, vals):
+    """csrToBcsr restatement -> (bcsr_rowptr int32[M/16+1], bcsr_colidx int32[nnzb], bcsr_vals float16[nnzb*256])."""
+    L = lib()
+    rowptr = np.ascontiguousarray(rowptr, dtype=np.int32)
+    colidx = np.ascontiguousarray(colidx, dtype=np.int32)
+    v16 = np.ascontiguousarray(vals, dtype=np.float16).view(np.uint16)
+    if colidx.size == 0:
+        colidx = np.zeros(1, np.int32)
+        v16 = np.zeros(1, np.uint16)
+    nnzb = C.c_int64()
+    brp = np.zeros(M // 16 + 1, np.int32)
+    L.orc_csr_to_bcsr(M, K, rowptr, colidx, v16, C.byref(nnzb), brp, None, None)
+    bci = np.zeros(max(nnzb.value, 1), np.int32)
+    bv = np.zeros(max(nnzb.value, 1) * 256, np.uint16)
+    L.orc_csr_to_bcsr(M, K, rowptr, colidx, v16, C.byref(nnzb), brp, bci.ctypes.data, bv.ctypes.data)
+    return brp, bci[: nnzb.value], bv[: nnzb.value * 256].view(np.float16)
+
+
+def bcsr_spmm(bvals, browptr, bcolidx, B_nk, M, N, K, brow_begin=0, brow_end=None, threads=1):
+    """fp32 blocked multiply (VBR::multiply arithmetic). B_nk is the [N][K] fp16 array. Returns fp32 C rows."""
+    L = lib()
+    if brow_end is None:
+        brow_end = M // 16
+    out = np.zeros(((brow_end - brow_begin) * 16, N), np.float32)
+    bv = np.ascontiguousarray(bvals, dtype=np.float16).view(np.uint16)
+    if bv.size == 0:
+        bv = np.zeros(1, np.uint16)
+    bc = np.ascontiguousarray(bcolidx, dtype=np.int32)
+    if bc.size == 0:
+        bc = np.zeros(1, np.int32)
+    Bu = np.ascontiguousarray(B_nk, dtype=np.float16).view(np.uint16).reshape(-1)
+    L.orc_bcsr_spmm_f32(bv, np.ascontiguousarray(browptr, dtype=np.int32), bc, Bu, out.reshape(-1), M, N, K,
+                        brow_begin, brow_end, threads)
+    return out
+
+
+def _i64(a):
+    a = np.ascontiguousarray(a, dtype=np.int64)
+    return a if a.size else np.zeros(1, np.int64)
+
+
+def jaccard_group(rowA, gA, rowB, gB, bs):
+    return float(lib().orc_jaccard_group(_i64(rowA), len(rowA), gA, _i64(rowB), len(rowB), gB, bs))
+
+
+def hamming_group(rowA, gA, rowB, gB, bs):
+    return float(lib().orc_hamming_group(_i64(rowA), len(rowA), gA, _i64(rowB), len(rowB), gB, bs))
+
+
+def keeper_grouping(rowptr, cols, tau=0.5, col_block=16, row_block=16):
+    rows = len(rowptr) - 1
+    g = np.zeros(max(rows, 1), np.int64)
+    lib().orc_keeper_grouping(rows, _i64(rowptr), _i64(cols), tau, col_block, row_block, 1, g)
+    return g[:rows]
+
+
+def reorder_rows(rowptr, cols, tau=0.5, col_block=16, row_block=16):
+    """-> (fixed-size grouping, permutation) as Matrix_Blocking -a 5 -F 1 produces them."""
+    rows = len(rowptr) - 1
+    g = np.zeros(max(rows, 1), np.int64)
+    p = np.zeros(max(rows, 1), np.int64)
+    lib().orc_reorder_rows(rows, _i64(rowptr), _i64(cols), tau, col_block, row_block, g, p)
+    return g[:rows], p[:rows]

@@ -1,0 +1,102 @@
+// TEST INFRASTRUCTURE ONLY -- thin extern "C" doorway onto the UNMODIFIED reference CPU code.
+//
+// This file contains no algorithm of its own: it includes the reference's headers and is linked
+// with the reference's own preprocess/src/general/*.cpp, compiled from where they lie (see
+// oracle/Makefile, target `ref`).  The result, oracle/_ref/libsmat_ref.so, lets the test-suite call
+// the real reference functions through ctypes to validate the restatement in smat_oracle.cpp, and
+// lets the benchmark time the reference's CPU blocked multiply as the CPU baseline.
+//
+// Reference entry points used:
+//   JaccardDistanceGroup / HammingDistanceGroup   preprocess/src/general/blocking.cpp:904-975, 701-760
+//   BlockingEngine::GetGrouping (-a 5 -> Keeper)  preprocess/src/general/blocking.cpp:616-657, 431-547
+//   get_permutation / get_fixed_size_grouping     preprocess/src/general/utilities.cpp:8-20, 45-54
+//   CSR(ifstream) = read_from_edgelist            preprocess/src/general/csr.cpp:166-290
+//   VBR::multiply                                 preprocess/src/general/vbr.cpp:323-372
+
+#include <cstdint>
+#include <cstring>
+#include <fstream>
+#include <vector>
+
+#include "blocking.h"
+#include "definitions.h"
+#include "matrices.h"
+#include "utilities.h"
+
+extern "C" {
+
+float ref_jaccard_group(const long* rowA, long sizeA, long gA, long* rowB, long sizeB, long gB, long bs) {
+    std::vector<intT> a(rowA, rowA + sizeA);
+    return JaccardDistanceGroup(a, gA, rowB, sizeB, gB, bs);
+}
+
+float ref_hamming_group(const long* rowA, long sizeA, long gA, long* rowB, long sizeB, long gB, long bs) {
+    std::vector<intT> a(rowA, rowA + sizeA);
+    return HammingDistanceGroup(a, gA, rowB, sizeB, gB, bs);
+}
+
+// Reads an edge-list file with the reference reader, runs the reference grouping exactly as
+// Matrix_Blocking does with "-a 5 -b cb -B rb -F force_fixed -t tau" and returns
+// (rows, grouping, permutation-of-CSR::reorder).  Arrays must hold at least max_rows entries.
+long ref_group_and_permute(const char* el_path, float tau, long cb, long rb, int force_fixed, long max_rows,
+                           long* grouping_out, long* perm_out) {
+    std::ifstream fin(el_path);
+    if (!fin.good()) return -1;
+    CSR cmat(fin, " ", true, el);
+    BlockingEngine eng;
+    eng.tau = tau;
+    eng.col_block_size = cb;
+    eng.row_block_size = rb;
+    eng.use_groups = false;
+    eng.use_pattern = true;
+    eng.force_fixed_size = force_fixed != 0;
+    eng.blocking_algo = iterative_max_size;
+    eng.SetComparator(1);  // Jaccard, the CLI default (preprocess/include/input.h:29)
+    std::vector<intT> g = eng.GetGrouping(cmat);
+    long rows = (long)g.size();
+    if (rows > max_rows) return -2;
+    std::vector<intT> perm = get_permutation(g);
+    for (long i = 0; i < rows; i++) { grouping_out[i] = g[i]; perm_out[i] = perm[i]; }
+    return rows;
+}
+
+long ref_get_permutation(long n, const long* grouping, long* perm_out) {
+    std::vector<intT> g(grouping, grouping + n);
+    std::vector<intT> p = get_permutation(g);
+    for (long i = 0; i < n; i++) perm_out[i] = p[i];
+    return n;
+}
+
+long ref_fixed_size_grouping(long n, const long* grouping, long rb, long* out) {
+    std::vector<intT> g(grouping, grouping + n);
+    std::vector<intT> r = get_fixed_size_grouping(g, rb);
+    for (long i = 0; i < n; i++) out[i] = r[i];
+    return n;
+}
+
+// Runs VBR::multiply on caller-provided VBR arrays (fixed 16-row blocks): mab holds the blocks
+// consecutively, COLUMN-major inside a block; jab holds block-column indices; B and C are
+// column-major fp32 (B_rows = cols, C_rows = rows); C must be zeroed by the caller.
+int ref_vbr_multiply(long rows, long cols, long block_rows, long block_col_size, const long* nzcount,
+                     const long* jab, const float* mab, long nblocks, long row_block, float* B, int B_cols,
+                     float* C) {
+    VBR v;
+    v.rows = rows;
+    v.cols = cols;
+    v.block_rows = block_rows;
+    v.block_cols = (cols - 1) / block_col_size + 1;
+    v.block_col_size = block_col_size;
+    v.nzcount = new intT[block_rows];
+    v.row_part = new intT[block_rows + 1];
+    v.jab = new intT[nblocks > 0 ? nblocks : 1];
+    v.nztot = nblocks * row_block * block_col_size;
+    v.mab = new DataT[v.nztot > 0 ? v.nztot : 1];
+    for (long i = 0; i < block_rows; i++) { v.nzcount[i] = nzcount[i]; v.row_part[i] = i * row_block; }
+    v.row_part[block_rows] = rows;
+    for (long i = 0; i < nblocks; i++) v.jab[i] = jab[i];
+    memcpy(v.mab, mab, sizeof(DataT) * (size_t)v.nztot);
+    v.multiply(B, B_cols, C);
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,124 @@
+/* smat_b200 -- C ABI of the B200-native block-sparse SpMM engine.
+ *
+ * Drop-in boundary for the SpMM path of SMaT: every entry point below replaces one piece of the
+ * reference's host/GPU code and keeps its argument meaning and memory layouts.  Plain pointers and
+ * sizes only; `stream` is a cudaStream_t passed as void* (NULL = default stream).  All functions
+ * return 0 on success or a negative smat_status code; none of them exits the process (the reference
+ * calls exit() on error, src/cuda_hgemm/src/common/common.h:21-63).
+ *
+ * Layouts (identical to the reference kernels, src/cuda_hgemm/src/mma/mmaCBT.cu:13-88):
+ *   vals     fp16, block p occupies [p*256, p*256+256), row-major 16x16
+ *   rowptr   int32[M/16 + 1]
+ *   colidx   int32[nnzb], ELEMENT column of the block's left edge (multiple of 16), ascending per row
+ *   B        fp16, logical K x N, element (k, n) at B[n*K + k]   (K contiguous)
+ *   C        fp16, row-major M x N, fully overwritten
+ * M and K are multiples of 16, N a multiple of 8, device pointers 16-byte aligned.
+ */
+#ifndef SMAT_B200_H
+#define SMAT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum smat_status {
+    SMAT_OK = 0,
+    SMAT_ERR_BAD_ARG = -1,      /* null pointer, misaligned pointer, size not a multiple of the tile */
+    SMAT_ERR_CUDA = -2,         /* a CUDA runtime / driver call failed; see smat_last_error_string() */
+    SMAT_ERR_DEVICE_WAIT = -3,  /* a bounded wait inside a kernel ran out (device status word set) */
+    SMAT_ERR_IO = -4,           /* file could not be opened / parsed */
+    SMAT_ERR_NOMEM = -5,
+    SMAT_ERR_RANGE = -6         /* index out of range / size beyond a stated limit */
+} smat_status;
+
+/* C = A_bcsr x B on the current device, asynchronous on `stream`.
+ * Replaces  void mmaCBTKernel(half*, int*, int*, half*, half*, size_t M, size_t N, size_t K,
+ *                             size_t nonzeroBlocks, int* blockInfo, int* relativeBlockIndexMapping)
+ * (src/cuda_hgemm/src/mma/mmaCBT.cu:83-88; declared through HGEMM_FUNC_SPARSE2,
+ * src/cuda_hgemm/src/main.cu:7,19).  Same argument order; blockInfo and relativeBlockIndexMapping
+ * are accepted for signature compatibility and ignored (may be NULL): the dense Mb*Kb maps are
+ * redundant with rowptr/colidx. */
+int smat_spmm_bcsr_f16(const void* bcsrValuesA, const int* bcsrRowPtrA, const int* bcsrColIdxA, const void* B, void* C,
+                       size_t M, size_t N, size_t K, size_t nonzeroBlocks, const int* blockInfo,
+                       const int* relativeBlockIndexMapping, void* stream);
+
+/* Same product restricted to block-rows [brow_begin, brow_end): writes rows
+ * [16*brow_begin, 16*brow_end) of C, where C points at the FIRST row of that range (the shard's own
+ * C buffer).  This is the per-GPU unit of the block-row partitioning; the reference is single-GPU
+ * (src/cuda_hgemm/src/main.cu:32,41 only selects a device), so there is no reference counterpart
+ * beyond mmaCBTKernel itself.  rowptr/colidx/vals are the full matrix arrays or a shard of them:
+ * only rowptr[brow_begin..brow_end] is read and its values index colidx/vals directly. */
+int smat_spmm_bcsr_f16_rows(const void* bcsrValuesA, const int* bcsrRowPtrA, const int* bcsrColIdxA, const void* B,
+                            void* C, size_t M, size_t N, size_t K, size_t nonzeroBlocks, size_t brow_begin,
+                            size_t brow_end, void* stream);
+
+/* Kernel variant selection for smat_spmm_bcsr_f16*: 0 = automatic (default), otherwise a variant id
+ * (see smat_spmm_variant_name).  Process-wide; meant for benchmarks and tests. */
+int smat_spmm_set_variant(int variant);
+const char* smat_spmm_variant_name(int variant);
+
+/* Synchronises `stream` and reports whether any kernel launched by this library on the current
+ * device recorded a device-side error (a bounded wait that ran out).  Clears the device status word.
+ * The reference never checks its launches (src/cuda_hgemm/src/mma/mmaCBT.cu:87). */
+int smat_device_status(void* stream);
+
+/* Number of this library's kernels launched so far by the calling process (all devices). */
+long long smat_launch_count(void);
+
+/* Device-side BCSR builder: CSR (device arrays, int32 indices, fp16 values, M and K multiples of 16,
+ * any column order inside a row; duplicate (row, col) entries allowed, the last one in CSR order
+ * wins) -> 16x16 BCSR in the layout above.
+ * Replaces SparseMatrix::csrToBcsr and the host-to-device uploads of its result
+ * (src/cuda_hgemm/src/common/matrix.h:376-502, 185-199); the dense Mb*Kb maps blockInfo and
+ * relativeBlockIndexMapping are never built.
+ * Two-phase: smat_bcsr_count writes bcsr_rowptr (device, int32[M/16+1]) and returns nnzb to the
+ * host (synchronises the stream); the caller allocates colidx (int32[nnzb]) and vals
+ * (fp16[nnzb*256]) and calls smat_bcsr_fill, which is asynchronous on `stream`.
+ * Limit: K <= 12,582,912 (one block-row's column-block bitmap is kept in shared memory). */
+int smat_bcsr_count(const int* csr_rowptr, const int* csr_colidx, size_t M, size_t K, size_t nnz, int* bcsr_rowptr,
+                    size_t* nnzb_out, void* stream);
+int smat_bcsr_fill(const int* csr_rowptr, const int* csr_colidx, const void* csr_vals, size_t M, size_t K, size_t nnz,
+                   const int* bcsr_rowptr, int* bcsr_colidx, void* bcsr_vals, size_t nnzb, void* stream);
+
+/* Matrix-Market reader (host).  Replaces mmio_allinone
+ * (src/cuda_hgemm/src/common/mmio_highlevel.h:619-786): dimensions padded up to multiples of 16,
+ * 0-based CSR in file order inside each row, symmetric/hermitian files mirrored, pattern files get
+ * value 1, values rounded double -> fp16 once.  Output arrays are malloc'ed by the library and
+ * released with smat_free_host.  `vals` receives fp16 bit patterns. */
+int smat_read_mtx(const char* filename, size_t* M, size_t* K, size_t* nnz, int* is_symmetric, int** csr_rowptr,
+                  int** csr_colidx, uint16_t** csr_vals);
+void smat_free_host(void* p);
+
+/* Similarity-based row reordering (host, multi-threaded).  Replaces the Matrix_Blocking program run
+ * as `-a 5 -b col_block -B row_block -F 1 -t tau`
+ * (preprocess/test/general/Matrix_Blocking.cpp:10-50 -> BlockingEngine::GetGrouping,
+ * preprocess/src/general/blocking.cpp:616-657 -> IterativeBlockingKeeper :431-547 with
+ * JaccardDistanceGroup :904-975, merge_rows preprocess/src/general/utilities.cpp:145-173,
+ * get_fixed_size_grouping / get_permutation utilities.cpp:45-54, 8-20, CSR::reorder csr.cpp:97-105).
+ * Input: CSR pattern with ASCENDING columns in every row (64-bit row pointers, 32-bit columns).
+ * Output: grouping[rows] (the fixed-size grouping the program writes to its .g file) and
+ * perm[rows] with "new row r = old row perm[r]".  Bit-identical to the reference program.
+ * threads <= 0 uses every hardware thread. */
+int smat_reorder_rows(size_t rows, const int64_t* rowptr, const int32_t* cols, float tau, int col_block,
+                      int row_block, int threads, int64_t* grouping, int64_t* perm);
+
+/* Jaccard distance on column-block quotients between a group pattern and a row
+ * (JaccardDistanceGroup, preprocess/src/general/blocking.cpp:904-975). */
+float smat_jaccard_group(const int64_t* rowA, size_t sizeA, int64_t groupA, const int64_t* rowB, size_t sizeB,
+                         int64_t groupB, int64_t block_size);
+
+/* nnzb-balanced contiguous block-row ranges for `parts` GPUs: bounds[parts+1], bounds[0] = 0,
+ * bounds[parts] = Mb; chosen on the prefix sums in bcsr_rowptr (host array) so that every part holds
+ * about nnzb/parts blocks.  New work: the reference has no multi-GPU path. */
+int smat_partition_block_rows(const int* bcsr_rowptr_host, size_t Mb, int parts, size_t* bounds);
+
+/* Text of the most recent error on the calling thread ("" if none). */
+const char* smat_last_error_string(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SMAT_B200_H */

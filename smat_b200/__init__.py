@@ -1,0 +1,26 @@
+"""smat_b200: B200-native block-sparse SpMM engine behind SMaT's kernel-launcher boundary.
+
+The product is the C-ABI shared library ``libsmat_b200.so`` (declared in ``include/smat_b200.h``,
+sources in ``smat_b200/csrc``).  This Python package is the host-side mirror of the reference's
+harness objects (``SparseMatrix``, ``Matrix``, ``Tester``; src/cuda_hgemm/src/common/matrix.h,
+tester.h) on top of that library, using torch only for device memory and streams.
+
+There is no CPU fallback: every compute entry point goes through the CUDA library and raises if it is
+missing or if no sm_100 device is present.
+"""
+from .api import (  # noqa: F401
+    Matrix,
+    SmatError,
+    SparseMatrix,
+    Tester,
+    apply_row_permutation,
+    jaccard_group,
+    launch_count,
+    lib,
+    partition_block_rows,
+    read_mtx,
+    reorder_rows,
+    set_variant,
+    spmm,
+    spmm_rows,
+)

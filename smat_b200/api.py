@@ -1,0 +1,310 @@
+"""Host-side mirror of the reference's harness objects on top of the C-ABI library.
+
+Names and argument meaning follow the reference (src/cuda_hgemm/src/common/matrix.h,
+src/cuda_hgemm/src/common/tester.h, src/reorder.py); compute always goes through
+``libsmat_b200.so``.  torch provides device memory and streams only.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+
+class SmatError(RuntimeError):
+    def __init__(self, code, text):
+        super().__init__(f"smat_b200 error {code}: {text}")
+        self.code = code
+
+
+def lib():
+    """Loads libsmat_b200.so (built in-tree by ``smat_b200._build``).  Raises if it is missing."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = os.path.join(_HERE, "libsmat_b200.so")
+    if not os.path.exists(path):
+        raise SmatError(-2, f"{path} is missing: build it with `python -m smat_b200._build` "
+                            "(there is no CPU fallback)")
+    L = C.CDLL(path)
+    vp, sz, ip = C.c_void_p, C.c_size_t, C.c_void_p
+    L.smat_spmm_bcsr_f16.argtypes = [vp, ip, ip, vp, vp, sz, sz, sz, sz, ip, ip, vp]
+    L.smat_spmm_bcsr_f16_rows.argtypes = [vp, ip, ip, vp, vp, sz, sz, sz, sz, sz, sz, vp]
+    L.smat_spmm_set_variant.argtypes = [C.c_int]
+    L.smat_spmm_variant_name.argtypes = [C.c_int]
+    L.smat_spmm_variant_name.restype = C.c_char_p
+    L.smat_device_status.argtypes = [vp]
+    L.smat_launch_count.restype = C.c_longlong
+    L.smat_bcsr_count.argtypes = [ip, ip, sz, sz, sz, ip, C.POINTER(sz), vp]
+    L.smat_bcsr_fill.argtypes = [ip, ip, vp, sz, sz, sz, ip, ip, vp, sz, vp]
+    L.smat_read_mtx.argtypes = [C.c_char_p, C.POINTER(sz), C.POINTER(sz), C.POINTER(sz), C.POINTER(C.c_int),
+                                C.POINTER(C.POINTER(C.c_int)), C.POINTER(C.POINTER(C.c_int)),
+                                C.POINTER(C.POINTER(C.c_uint16))]
+    L.smat_free_host.argtypes = [vp]
+    L.smat_free_host.restype = None
+    L.smat_reorder_rows.argtypes = [sz, vp, vp, C.c_float, C.c_int, C.c_int, C.c_int, vp, vp]
+    L.smat_jaccard_group.argtypes = [vp, sz, C.c_int64, vp, sz, C.c_int64, C.c_int64]
+    L.smat_jaccard_group.restype = C.c_float
+    L.smat_partition_block_rows.argtypes = [vp, sz, C.c_int, vp]
+    L.smat_last_error_string.restype = C.c_char_p
+    _LIB = L
+    return L
+
+
+def _check(rc):
+    if rc != 0:
+        raise SmatError(rc, lib().smat_last_error_string().decode())
+
+
+def launch_count():
+    return int(lib().smat_launch_count())
+
+
+def set_variant(v):
+    _check(lib().smat_spmm_set_variant(int(v)))
+
+
+def _stream():
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+# ------------------------------------------------------------------------------------------------
+# host-side steps
+# ------------------------------------------------------------------------------------------------
+def read_mtx(path):
+    """Matrix-Market file -> (M, K, rowptr int32, colidx int32, vals float16, is_symmetric);
+    the behaviour of mmio_allinone (src/cuda_hgemm/src/common/mmio_highlevel.h:619-786)."""
+    L = lib()
+    M, K, nnz, sym = C.c_size_t(), C.c_size_t(), C.c_size_t(), C.c_int()
+    rp, ci, vv = C.POINTER(C.c_int)(), C.POINTER(C.c_int)(), C.POINTER(C.c_uint16)()
+    _check(L.smat_read_mtx(os.fsencode(path), C.byref(M), C.byref(K), C.byref(nnz), C.byref(sym), C.byref(rp),
+                           C.byref(ci), C.byref(vv)))
+    try:
+        rowptr = np.ctypeslib.as_array(rp, shape=(M.value + 1,)).copy()
+        colidx = np.ctypeslib.as_array(ci, shape=(nnz.value + 1,))[: nnz.value].copy()
+        vals = np.ctypeslib.as_array(vv, shape=(nnz.value + 1,))[: nnz.value].copy().view(np.float16)
+    finally:
+        for p in (rp, ci, vv):
+            L.smat_free_host(C.cast(p, C.c_void_p))
+    return M.value, K.value, rowptr, colidx, vals, bool(sym.value)
+
+
+def jaccard_group(rowA, gA, rowB, gB, block_size):
+    a = np.ascontiguousarray(rowA, dtype=np.int64)
+    b = np.ascontiguousarray(rowB, dtype=np.int64)
+    return float(lib().smat_jaccard_group(a.ctypes.data, a.size, gA, b.ctypes.data, b.size, gB, block_size))
+
+
+def reorder_rows(rowptr, colidx, tau=0.5, col_block=16, row_block=16, threads=0):
+    """Similarity row reordering as `Matrix_Blocking -a 5 -b col_block -B row_block -F 1 -t tau`
+    (src/reorder.py:107-139).  Columns must be ascending inside each row.
+    Returns (grouping int64[rows], perm int64[rows]) with new row r = old row perm[r]."""
+    rp = np.ascontiguousarray(rowptr, dtype=np.int64)
+    ci = np.ascontiguousarray(colidx, dtype=np.int32)
+    rows = rp.size - 1
+    grouping = np.zeros(max(rows, 1), np.int64)
+    perm = np.zeros(max(rows, 1), np.int64)
+    _check(lib().smat_reorder_rows(rows, rp.ctypes.data, ci.ctypes.data if ci.size else None, tau, col_block,
+                                   row_block, threads, grouping.ctypes.data, perm.ctypes.data))
+    return grouping[:rows], perm[:rows]
+
+
+def apply_row_permutation(rowptr, colidx, vals, perm):
+    """CSR with rows permuted: new row r = old row perm[r] (CSR::permute_rows,
+    preprocess/src/general/csr.cpp:65-74).  Unlike the reference's text round trip, which drops the
+    values (preprocess/test/general/Matrix_Blocking.cpp:46, src/reorder.py:39-40), values are carried."""
+    rowptr = np.asarray(rowptr, dtype=np.int64)
+    perm = np.asarray(perm, dtype=np.int64)
+    lens = np.diff(rowptr)[perm]
+    new_rp = np.zeros(rowptr.size, np.int64)
+    np.cumsum(lens, out=new_rp[1:])
+    starts = rowptr[:-1][perm]
+    idx = np.repeat(starts - new_rp[:-1], lens) + np.arange(new_rp[-1], dtype=np.int64)
+    return new_rp.astype(np.int32), np.asarray(colidx)[idx], np.asarray(vals)[idx]
+
+
+def partition_block_rows(bcsr_rowptr_host, parts):
+    """nnzb-balanced contiguous block-row ranges -> bounds int64[parts+1]."""
+    rp = np.ascontiguousarray(bcsr_rowptr_host, dtype=np.int32)
+    bounds = np.zeros(parts + 1, np.uint64)
+    _check(lib().smat_partition_block_rows(rp.ctypes.data, rp.size - 1, parts, bounds.ctypes.data))
+    return bounds.astype(np.int64)
+
+
+# ------------------------------------------------------------------------------------------------
+# device objects
+# ------------------------------------------------------------------------------------------------
+class Matrix:
+    """Dense fp16 device matrix (src/cuda_hgemm/src/common/matrix.h:18-139).  ``data`` is a torch
+    CUDA tensor; for B it has shape [N, K] (K contiguous), for C shape [M, N]."""
+
+    def __init__(self, rows, cols, name="Matrix", device="cuda", fill=None):
+        import torch
+        self.rows, self.cols, self.name = rows, cols, name
+        self.data = torch.empty((rows, cols), dtype=torch.float16, device=device)
+        if fill is not None:
+            self.data.fill_(fill)
+
+    @classmethod
+    def from_host(cls, array, name="Matrix", device="cuda"):
+        import torch
+        m = cls.__new__(cls)
+        a = np.ascontiguousarray(array, dtype=np.float16)
+        m.rows, m.cols, m.name = a.shape[0], a.shape[1], name
+        m.data = torch.from_numpy(a.view(np.int16)).to(device).view(torch.float16)
+        return m
+
+    def getDevPtr(self):
+        return self.data.data_ptr()
+
+    def checkValue(self, other):
+        """max / average absolute difference (matrix.h:103-121)."""
+        d = (self.data.float() - other.data.float()).abs()
+        return float(d.max()), float(d.mean())
+
+
+class SparseMatrix:
+    """Sparse matrix blocked on the device (src/cuda_hgemm/src/common/matrix.h:143-721).
+
+    Built from a host CSR (``from_csr``) or a Matrix-Market file (``from_file``, the reference's
+    constructor path readCsr -> csrToBcsr -> upload, matrix.h:145-202).  The CSR is uploaded and the
+    16x16 BCSR is built ON THE DEVICE by the library (smat_bcsr_count / smat_bcsr_fill)."""
+
+    def __init__(self):
+        self.M = self.K = self.nnz = self.nnzb = 0
+        self.bcsrRowPtr = self.bcsrColIdx = self.bcsrVal = None
+
+    @classmethod
+    def from_csr(cls, M, K, rowptr, colidx, vals, device="cuda", keep_csr=False):
+        import torch
+        self = cls()
+        self.M, self.K, self.nnz = int(M), int(K), int(len(colidx))
+        dev = torch.device(device)
+        with torch.cuda.device(dev):
+            d_rp = torch.from_numpy(np.ascontiguousarray(rowptr, dtype=np.int32)).to(dev)
+            d_ci = torch.from_numpy(np.ascontiguousarray(colidx, dtype=np.int32)).to(dev)
+            d_v = torch.from_numpy(np.ascontiguousarray(vals, dtype=np.float16).view(np.int16)).to(dev)
+            self.bcsrRowPtr = torch.empty(self.M // 16 + 1, dtype=torch.int32, device=dev)
+            nnzb = C.c_size_t()
+            L = lib()
+            _check(L.smat_bcsr_count(d_rp.data_ptr(), d_ci.data_ptr(), self.M, self.K, self.nnz,
+                                     self.bcsrRowPtr.data_ptr(), C.byref(nnzb), _stream()))
+            self.nnzb = int(nnzb.value)
+            self.bcsrColIdx = torch.empty(max(self.nnzb, 1), dtype=torch.int32, device=dev)
+            self.bcsrVal = torch.empty(max(self.nnzb, 1) * 256, dtype=torch.float16, device=dev)
+            _check(L.smat_bcsr_fill(d_rp.data_ptr(), d_ci.data_ptr(), d_v.data_ptr(), self.M, self.K, self.nnz,
+                                    self.bcsrRowPtr.data_ptr(), self.bcsrColIdx.data_ptr(), self.bcsrVal.data_ptr(),
+                                    self.nnzb, _stream()))
+            torch.cuda.current_stream().synchronize()
+            if keep_csr:
+                self.csrRowPtr, self.csrColIdx, self.csrVal = d_rp, d_ci, d_v
+        return self
+
+    @classmethod
+    def from_bcsr(cls, M, K, bcsr_rowptr, bcsr_colidx, bcsr_vals, device="cuda"):
+        """Upload host BCSR arrays that are already in the kernel's layout."""
+        import torch
+        self = cls()
+        self.M, self.K, self.nnzb = int(M), int(K), int(len(bcsr_colidx))
+        dev = torch.device(device)
+        self.bcsrRowPtr = torch.from_numpy(np.ascontiguousarray(bcsr_rowptr, dtype=np.int32)).to(dev)
+        ci = np.ascontiguousarray(bcsr_colidx, dtype=np.int32)
+        v = np.ascontiguousarray(bcsr_vals, dtype=np.float16).view(np.int16)
+        if self.nnzb == 0:
+            ci, v = np.zeros(1, np.int32), np.zeros(256, np.int16)
+        self.bcsrColIdx = torch.from_numpy(ci).to(dev)
+        self.bcsrVal = torch.from_numpy(v).to(dev).view(torch.float16)
+        return self
+
+    @classmethod
+    def from_file(cls, filename, device="cuda"):
+        M, K, rowptr, colidx, vals, _ = read_mtx(filename)
+        return cls.from_csr(M, K, rowptr, colidx, vals, device=device)
+
+    # getters named as in matrix.h:228-262
+    def getRow(self):
+        return self.M
+
+    def getCol(self):
+        return self.K
+
+    def getNonzeroblocks(self):
+        return self.nnzb
+
+    def getBcsrValues(self):
+        return self.bcsrVal.data_ptr()
+
+    def getBcsrRowPtr(self):
+        return self.bcsrRowPtr.data_ptr()
+
+    def getBcsrColIdx(self):
+        return self.bcsrColIdx.data_ptr()
+
+    def host_arrays(self):
+        rp = self.bcsrRowPtr.cpu().numpy()
+        ci = self.bcsrColIdx.cpu().numpy()[: self.nnzb]
+        v = self.bcsrVal.view(dtype=__import__("torch").int16).cpu().numpy().view(np.float16)[: self.nnzb * 256]
+        return rp, ci, v
+
+
+def spmm(A, B, Cout, check=False):
+    """C = A x B through smat_spmm_bcsr_f16 (the mmaCBTKernel signature, mmaCBT.cu:83-88).
+    B: Matrix / tensor [N, K]; Cout: Matrix / tensor [M, N]."""
+    Bt = B.data if isinstance(B, Matrix) else B
+    Ct = Cout.data if isinstance(Cout, Matrix) else Cout
+    N = Bt.shape[0]
+    assert Bt.shape[1] == A.K and tuple(Ct.shape) == (A.M, N) and Bt.is_contiguous() and Ct.is_contiguous()
+    _check(lib().smat_spmm_bcsr_f16(A.getBcsrValues(), A.getBcsrRowPtr(), A.getBcsrColIdx(), Bt.data_ptr(),
+                                    Ct.data_ptr(), A.M, N, A.K, A.nnzb, None, None, _stream()))
+    if check:
+        _check(lib().smat_device_status(_stream()))
+
+
+def spmm_rows(A, B, Cshard, brow_begin, brow_end, check=False):
+    """Block-rows [brow_begin, brow_end) of C = A x B into ``Cshard`` ([16*(end-begin), N])."""
+    Bt = B.data if isinstance(B, Matrix) else B
+    Ct = Cshard.data if isinstance(Cshard, Matrix) else Cshard
+    N = Bt.shape[0]
+    assert tuple(Ct.shape) == ((brow_end - brow_begin) * 16, N)
+    _check(lib().smat_spmm_bcsr_f16_rows(A.getBcsrValues(), A.getBcsrRowPtr(), A.getBcsrColIdx(), Bt.data_ptr(),
+                                         Ct.data_ptr(), A.M, N, A.K, A.nnzb, brow_begin, brow_end, _stream()))
+    if check:
+        _check(lib().smat_device_status(_stream()))
+
+
+class Tester:
+    """Timing harness (src/cuda_hgemm/src/common/tester.h:12-73, 166-209, 338-377): warm-up
+    launches, then ``profiling_iterations`` launches timed as one region.  Differences: CUDA events
+    on the launch stream instead of gettimeofday (tester.h:339-361), and the throughput counts N:
+    2*16*16*N*nnzb / t (the reference's print omits N, tester.h:362-363)."""
+
+    def __init__(self, A, N, warmup_iterations=1, profiling_iterations=10, B=None):
+        import torch
+        assert warmup_iterations > 0 and profiling_iterations > 0  # HGEMM_CHECK_GT, tester.h:24-29
+        self.A, self.N = A, N
+        self.warmup_iterations, self.profiling_iterations = warmup_iterations, profiling_iterations
+        self.B = B if B is not None else Matrix(N, A.K, "Matrix B", fill=1.0)  # all ones, matrix.h:38
+        self.C = Matrix(A.M, N, "Matrix C")
+        self.profiling_time_ms = 0.0
+        self.throughput_tflops = 0.0
+        self._torch = torch
+
+    def evaluateSparse2(self, name="smat_b200"):
+        torch = self._torch
+        for _ in range(self.warmup_iterations):
+            spmm(self.A, self.B, self.C)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(self.profiling_iterations):
+            spmm(self.A, self.B, self.C)
+        e1.record()
+        torch.cuda.synchronize()
+        _check(lib().smat_device_status(_stream()))
+        self.profiling_time_ms = e0.elapsed_time(e1) / self.profiling_iterations
+        flops = 2.0 * 256.0 * self.N * self.A.nnzb
+        self.throughput_tflops = flops * 1e-12 / (self.profiling_time_ms * 1e-3)
+        return self.profiling_time_ms, self.throughput_tflops

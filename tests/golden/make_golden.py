@@ -1,0 +1,149 @@
+"""Generates the golden fixtures in this directory FROM THE UNMODIFIED REFERENCE.
+
+Run in a container that has the reference tree (it is not needed to run the tests):
+
+    make -C oracle ref REF=/root/reference
+    python tests/golden/make_golden.py
+
+It drives the reference's own code through oracle/_ref (built from the reference sources by
+oracle/Makefile): the Matrix_Blocking / TEST_similarities programs and, through the thin ctypes
+doorway libsmat_ref.so, BlockingEngine::GetGrouping, get_permutation and VBR::multiply.  The inputs
+are small seeded matrices, so the fixtures stay a few hundred KB.
+
+Outputs:
+  similarities.json     stdout figures of TEST_similarities for -b 1, 3, 4, 16
+  reorder_<name>.npz    CSR pattern + reference grouping (.g file of Matrix_Blocking) + permutation
+                        (from its *_reordered.el) for -a 5 -F 1 runs
+  multiply_<name>.npz   BCSR arrays + B + fp32 C of the reference's VBR::multiply
+"""
+import json
+import os
+import re
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+import oracle  # noqa: E402
+from smat_b200 import generators as gen  # noqa: E402
+
+REFDIR = oracle.ref_dir()
+
+
+def similarities():
+    out = {}
+    for b in (1, 3, 4, 16):
+        txt = subprocess.run([os.path.join(REFDIR, "TEST_similarities"), "-b", str(b)], capture_output=True, text=True,
+                             check=True).stdout
+        out[str(b)] = {k: float(v) for k, v in re.findall(r"(Hamming|Jaccard): ([-0-9.e]+)", txt)}
+    out["row_A"] = [1, 2, 5, 10, 12, 20]
+    out["row_B"] = [0, 2, 4, 10, 16]
+    with open(os.path.join(HERE, "similarities.json"), "w") as f:
+        json.dump(out, f, indent=1)
+    print("similarities", out)
+
+
+def run_matrix_blocking(rowptr, cols, tau, cb, rb):
+    """Runs the reference PROGRAM on an edge list; returns (grouping from .g, permutation recovered
+    from the reordered edge list)."""
+    n = len(rowptr) - 1
+    with tempfile.TemporaryDirectory() as d:
+        el = os.path.join(d, "m.el")
+        rows = np.repeat(np.arange(n), np.diff(rowptr))
+        np.savetxt(el, np.stack([rows, cols], 1), fmt="%d")
+        subprocess.run([os.path.join(REFDIR, "Matrix_Blocking"), "-f", el, "-a", "5", "-b", str(cb), "-B", str(rb), "-F",
+                        "1", "-t", str(tau), "-o", os.path.join(d, "out"), "-v", "0"], check=True, capture_output=True)
+        # the .g file is one line: "GROUPING,g0,g1,...," (preprocess/src/general/utilities.cpp:175-240)
+        toks = open(os.path.join(d, "out.g")).read().strip().split(",")
+        assert toks[0] == "GROUPING"
+        g = np.array([int(t) for t in toks[1:] if t.strip() != ""], dtype=np.int64)
+        reordered = np.loadtxt(os.path.join(d, "m_reordered.el"), dtype=np.int64, ndmin=2)
+    return g, reordered
+
+
+def random_pattern(n, ncols, kmax, seed, clustered=False):
+    rng = np.random.default_rng(seed)
+    rows, cols = [], []
+    for i in range(n):
+        if clustered:
+            base = (i // 24) * 40 % max(1, ncols - 64)
+            c = base + rng.integers(0, 64, rng.integers(1, kmax + 1))
+        else:
+            c = rng.integers(0, ncols, rng.integers(0, kmax + 1))
+        c = np.unique(np.minimum(c, ncols - 1))
+        if i == n - 1:
+            c = np.unique(np.append(c, ncols - 1))
+        rows += [i] * len(c)
+        cols += list(c)
+    rowptr = np.zeros(n + 1, np.int64)
+    rowptr[1:] = np.cumsum(np.bincount(np.array(rows, dtype=np.int64), minlength=n))
+    return rowptr, np.array(cols, dtype=np.int64)
+
+
+def reorder_fixtures():
+    R = oracle.ref()
+    cases = {
+        "random_small": (*random_pattern(96, 96, 5, 1), 0.5, 16, 16),
+        "random_wide": (*random_pattern(200, 640, 12, 2), 0.5, 16, 16),
+        "clustered": (*random_pattern(240, 400, 20, 3, clustered=True), 0.5, 16, 16),
+        "clustered_tau08": (*random_pattern(160, 300, 10, 4, clustered=True), 0.8, 16, 16),
+        "blocks3": (*random_pattern(60, 60, 6, 5), 0.6, 3, 3),
+    }
+    for name, sc in (("band", 0.125), ("uniform", 0.015625), ("powerlaw", 0.0078125), ("clustered_cfg", 0.003),
+                     ("llm", 0.0625)):
+        p = gen.make_config(name.replace("_cfg", ""), scale=sc)
+        cases["cfg_" + name] = (p.rowptr.astype(np.int64), p.colidx.astype(np.int64), 0.5, 16, 16)
+    for name, (rowptr, cols, tau, cb, rb) in cases.items():
+        n = len(rowptr) - 1
+        g_prog, reordered = run_matrix_blocking(rowptr, cols, tau, cb, rb)
+        G = np.zeros(n, np.int64)
+        P = np.zeros(n, np.int64)
+        with tempfile.TemporaryDirectory() as d:
+            el = os.path.join(d, "m.el")
+            np.savetxt(el, np.stack([np.repeat(np.arange(n), np.diff(rowptr)), cols], 1), fmt="%d")
+            got = R.ref_group_and_permute(el.encode(), tau, cb, rb, 1, n, G, P)
+        assert got == n and np.array_equal(G, g_prog), name
+        # the program's reordered edge list must be the CSR with rows taken in order P
+        lens = np.diff(rowptr)[P]
+        exp_rows = np.repeat(np.arange(n), lens)
+        exp_cols = np.concatenate([cols[rowptr[r]:rowptr[r + 1]] for r in P]) if len(cols) else cols
+        assert np.array_equal(reordered[:, 0], exp_rows) and np.array_equal(reordered[:, 1], exp_cols), name
+        np.savez_compressed(os.path.join(HERE, f"reorder_{name}.npz"), rowptr=rowptr, cols=cols.astype(np.int32),
+                            tau=np.float32(tau), col_block=cb, row_block=rb, grouping=G.astype(np.int32),
+                            perm=P.astype(np.int32))
+        print("reorder", name, n, "rows; identity perm:", bool(np.array_equal(P, np.arange(n))))
+
+
+def multiply_fixtures():
+    R = oracle.ref()
+    for name, sc, N in (("band", 0.03125, 24), ("uniform", 0.00390625, 40), ("llm", 0.03125, 16)):
+        p = gen.make_config(name, scale=sc)
+        brp, bci, bv = oracle.csr_to_bcsr(p.M, p.K, p.rowptr, p.colidx, p.vals)
+        rng = np.random.default_rng(7)
+        B_nk = rng.standard_normal((N, p.K)).astype(np.float16)
+        nb = len(bci)
+        # reference VBR: blocks column-major inside, block-column indices, fp32, column-major B and C
+        mab = np.ascontiguousarray(bv.reshape(nb, 16, 16).transpose(0, 2, 1)).astype(np.float32).reshape(-1)
+        jab = (bci // 16).astype(np.int64)
+        nzcount = np.diff(brp).astype(np.int64)
+        Bf = np.ascontiguousarray(B_nk.astype(np.float32)).reshape(-1)          # [n][k] == column-major K x N
+        Cf = np.zeros(p.M * N, np.float32)                                        # column-major M x N
+        R.ref_vbr_multiply(p.M, p.K, p.M // 16, 16, nzcount, jab if nb else np.zeros(1, np.int64),
+                           mab if nb else np.zeros(1, np.float32), nb, 16, Bf, N, Cf)
+        C = Cf.reshape(N, p.M).T.copy()
+        np.savez_compressed(os.path.join(HERE, f"multiply_{name}.npz"), M=p.M, K=p.K, N=N, rowptr=p.rowptr,
+                            colidx=p.colidx, vals=p.vals, bcsr_rowptr=brp, bcsr_colidx=bci, bcsr_vals=bv, B_nk=B_nk,
+                            C_f32=C)
+        print("multiply", name, p.M, p.K, N, "nnzb", nb)
+
+
+if __name__ == "__main__":
+    assert oracle.have_ref(), "build oracle/_ref first: make -C oracle ref REF=/root/reference"
+    similarities()
+    reorder_fixtures()
+    multiply_fixtures()

@@ -1,0 +1,197 @@
+"""Parity of the CUDA SpMM (through the C ABI) with the CPU oracle and the reference-generated
+fixtures.  Tolerance: max relative error 1e-2 (fp16 in, fp32 accumulate, fp16 out), where the error of
+an entry is measured against max(|c_ref|, 1e-2 * sum_k |a||b|) so that entries dominated by
+cancellation are judged against the magnitude of the terms that were summed."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+import smat_b200 as S
+from smat_b200 import generators as gen
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def _oracle_c(bv, brp, bci, B_nk, M, N, K, rows=None):
+    b0, b1 = (0, M // 16) if rows is None else rows
+    C = oracle.bcsr_spmm(bv, brp, bci, B_nk, M, N, K, b0, b1, threads=8)
+    Cabs = oracle.bcsr_spmm(np.abs(bv), brp, bci, np.abs(B_nk), M, N, K, b0, b1, threads=8)
+    return C, Cabs
+
+
+def _rel_err(C_gpu, C_ref, C_abs):
+    c = C_gpu.astype(np.float32)
+    ref16 = C_ref.astype(np.float16).astype(np.float32)
+    denom = np.maximum(np.abs(ref16), 1e-2 * C_abs) + 1e-30
+    return float(np.max(np.abs(c - ref16) / denom))
+
+
+def _run(brp, bci, bv, B_nk, M, N, K, variant=0):
+    torch = _torch()
+    A = S.SparseMatrix.from_bcsr(M, K, brp, bci, bv)
+    B = S.Matrix.from_host(B_nk)
+    C = S.Matrix(M, N, fill=float("nan"))
+    S.set_variant(variant)
+    try:
+        S.spmm(A, B, C, check=True)
+    finally:
+        S.set_variant(0)
+    torch.cuda.synchronize()
+    return C.data.cpu().numpy()
+
+
+def _problem(name, scale, N=None):
+    p = gen.make_config(name, scale=scale)
+    if N is not None and N != p.N:  # same A, a B with the requested number of columns
+        p["B_nk"] = np.random.default_rng(99).standard_normal((N, p.K)).astype(np.float16)
+        p["N"] = N
+    brp, bci, bv = oracle.csr_to_bcsr(p.M, p.K, p.rowptr, p.colidx, p.vals)
+    return p, brp, bci, bv
+
+
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("name,scale,N", [("band", 1.0, 64), ("band", 0.1, 8), ("uniform", 0.02, 256),
+                                          ("uniform", 0.01, 136), ("powerlaw", 0.01, 128), ("clustered", 0.004, 512),
+                                          ("llm", 0.0625, 256), ("llm", 0.04, 24)])
+def test_matches_oracle(name, scale, N, variant):
+    p, brp, bci, bv = _problem(name, scale, N)
+    C = _run(brp, bci, bv, p.B_nk, p.M, N, p.K, variant)
+    Cref, Cabs = _oracle_c(bv, brp, bci, p.B_nk, p.M, N, p.K)
+    assert not np.isnan(C.astype(np.float32)).any()
+    assert _rel_err(C, Cref, Cabs) <= TOL
+
+
+@pytest.mark.parametrize("name", ["band", "uniform", "llm"])
+def test_matches_reference_vbr_multiply_fixture(golden_dir, name):
+    """C of the reference's own CPU blocked multiply (VBR::multiply) on the same inputs."""
+    z = np.load(os.path.join(golden_dir, f"multiply_{name}.npz"))
+    M, K, N = int(z["M"]), int(z["K"]), int(z["N"])
+    C = _run(z["bcsr_rowptr"], z["bcsr_colidx"], z["bcsr_vals"], z["B_nk"], M, N, K)
+    Cabs = oracle.bcsr_spmm(np.abs(z["bcsr_vals"]), z["bcsr_rowptr"], z["bcsr_colidx"], np.abs(z["B_nk"]), M, N, K)
+    assert _rel_err(C, z["C_f32"], Cabs) <= TOL
+
+
+def test_reordered_matrix_matches_oracle():
+    """Config-2 pipeline at reduced size: reorder rows (values carried), block, multiply."""
+    p = gen.make_config("uniform", scale=0.03)
+    _, perm = S.reorder_rows(p.rowptr, p.colidx)
+    rp, ci, v = S.apply_row_permutation(p.rowptr, p.colidx, p.vals, perm)
+    brp, bci, bv = oracle.csr_to_bcsr(p.M, p.K, rp, ci, v)
+    C = _run(brp, bci, bv, p.B_nk, p.M, p.N, p.K)
+    Cref, Cabs = _oracle_c(bv, brp, bci, p.B_nk, p.M, p.N, p.K)
+    assert _rel_err(C, Cref, Cabs) <= TOL
+    # a row reorder only permutes the rows of C
+    brp0, bci0, bv0 = oracle.csr_to_bcsr(p.M, p.K, p.rowptr, p.colidx, p.vals)
+    C0 = _run(brp0, bci0, bv0, p.B_nk, p.M, p.N, p.K)
+    assert np.array_equal(C.view(np.uint16), C0[perm].view(np.uint16))
+
+
+def test_edge_cases():
+    rng = np.random.default_rng(0)
+    # empty matrix: C is zero-filled
+    M, K, N = 64, 48, 16
+    C = _run(np.zeros(M // 16 + 1, np.int32), np.zeros(0, np.int32), np.zeros(0, np.float16),
+             rng.standard_normal((N, K)).astype(np.float16), M, N, K)
+    assert np.all(C == 0)
+    # one block in the last block-row / last block-column; other block-rows empty -> zeros
+    brp = np.array([0, 0, 0, 0, 1], np.int32)
+    bci = np.array([32], np.int32)
+    bv = rng.standard_normal(256).astype(np.float16)
+    B = rng.standard_normal((N, K)).astype(np.float16)
+    C = _run(brp, bci, bv, B, M, N, K)
+    Cref, Cabs = _oracle_c(bv, brp, bci, B, M, N, K)
+    assert np.all(C[:48] == 0) and _rel_err(C, Cref, Cabs) <= TOL
+    # a single block-row (M = 16) with every block present, N = 8
+    M, K, N = 16, 160, 8
+    brp = np.array([0, 10], np.int32)
+    bci = (np.arange(10) * 16).astype(np.int32)
+    bv = rng.standard_normal(2560).astype(np.float16)
+    B = rng.standard_normal((N, K)).astype(np.float16)
+    C = _run(brp, bci, bv, B, M, N, K)
+    Cref, Cabs = _oracle_c(bv, brp, bci, B, M, N, K)
+    assert _rel_err(C, Cref, Cabs) <= TOL
+
+
+def test_ragged_rows_and_long_block_row():
+    """Block-rows with 0, 1 and hundreds of blocks side by side (load imbalance, as in config 3)."""
+    rng = np.random.default_rng(4)
+    Mb, Kb, N = 40, 600, 72
+    counts = rng.integers(0, 4, Mb)
+    counts[7] = 600
+    counts[8] = 0
+    counts[21] = 311
+    brp = np.zeros(Mb + 1, np.int32)
+    brp[1:] = np.cumsum(counts)
+    bci = np.concatenate([np.sort(rng.choice(Kb, c, replace=False)) for c in counts]).astype(np.int32) * 16
+    bv = rng.standard_normal(brp[-1] * 256).astype(np.float16)
+    B = rng.standard_normal((N, Kb * 16)).astype(np.float16)
+    for variant in (1, 2):
+        C = _run(brp, bci, bv, B, Mb * 16, N, Kb * 16, variant)
+        Cref, Cabs = _oracle_c(bv, brp, bci, B, Mb * 16, N, Kb * 16)
+        assert _rel_err(C, Cref, Cabs) <= TOL
+
+
+def test_block_row_range_entry_point():
+    torch = _torch()
+    p, brp, bci, bv = _problem("powerlaw", 0.01, 64)
+    A = S.SparseMatrix.from_bcsr(p.M, p.K, brp, bci, bv)
+    B = S.Matrix.from_host(p.B_nk)
+    full = S.Matrix(p.M, 64)
+    S.spmm(A, B, full, check=True)
+    bounds = S.partition_block_rows(brp, 4)
+    for g in range(4):
+        b0, b1 = int(bounds[g]), int(bounds[g + 1])
+        shard = torch.full(((b1 - b0) * 16, 64), float("nan"), dtype=torch.float16, device="cuda")
+        S.spmm_rows(A, B, shard, b0, b1, check=True)
+        assert torch.equal(shard.view(torch.int16), full.data[b0 * 16:b1 * 16].view(torch.int16))
+
+
+def test_deterministic():
+    p, brp, bci, bv = _problem("llm", 0.0625, 256)
+    a = _run(brp, bci, bv, p.B_nk, p.M, 256, p.K)
+    b = _run(brp, bci, bv, p.B_nk, p.M, 256, p.K)
+    assert np.array_equal(a.view(np.uint16), b.view(np.uint16))
+
+
+def test_tester_harness_reports_throughput():
+    p, brp, bci, bv = _problem("band", 1.0, 64)
+    A = S.SparseMatrix.from_bcsr(p.M, p.K, brp, bci, bv)
+    t = S.Tester(A, 64, warmup_iterations=1, profiling_iterations=3)
+    ms, tflops = t.evaluateSparse2()
+    assert ms > 0 and tflops > 0
+    # B is all ones in the reference harness (matrix.h:38): every C entry is a row sum of A
+    want = np.zeros(p.M, np.float32)
+    np.add.at(want, np.repeat(np.arange(p.M), np.diff(p.rowptr)), p.vals.astype(np.float32))
+    got = t.C.data[:, 0].float().cpu().numpy()
+    assert np.max(np.abs(got - want)) <= 1e-2 * np.maximum(np.abs(want), 1).max()
+
+
+@pytest.mark.parametrize("name", ["llm", "clustered"])
+def test_full_size_sampled_block_rows(name):
+    """BASELINE-size configs: the GPU result of sampled block-rows against the oracle, plus the
+    size-independent property that block-rows without blocks are exactly zero."""
+    torch = _torch()
+    p = gen.make_config(name)
+    A = S.SparseMatrix.from_csr(p.M, p.K, p.rowptr, p.colidx, p.vals)
+    B = S.Matrix.from_host(p.B_nk)
+    C = S.Matrix(p.M, p.N, fill=float("nan"))
+    S.spmm(A, B, C, check=True)
+    brp, bci, bv = A.host_arrays()
+    Mb = p.M // 16
+    rng = np.random.default_rng(0)
+    for br in sorted(set([0, Mb - 1] + rng.integers(0, Mb, 6).tolist())):
+        Cref, Cabs = _oracle_c(bv, brp, bci, p.B_nk, p.M, p.N, p.K, rows=(br, br + 1))
+        got = C.data[br * 16:br * 16 + 16].cpu().numpy()
+        assert _rel_err(got, Cref, Cabs) <= TOL, br
+    empty = np.nonzero(np.diff(brp) == 0)[0]
+    for br in empty[:4]:
+        assert torch.all(C.data[br * 16:br * 16 + 16] == 0)
+    assert not torch.isnan(C.data).any()

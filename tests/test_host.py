@@ -1,0 +1,145 @@
+"""Host-side pieces of the product (no GPU): the C-ABI library loads and exports what the header
+declares; the Matrix-Market reader, the reorder engine and the partitioner agree with the oracle and
+the reference-generated fixtures; argument errors are reported, not fatal."""
+import ctypes
+import glob
+import os
+import re
+
+import numpy as np
+import pytest
+
+import oracle
+import smat_b200 as S
+from smat_b200 import generators as gen
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    hdr = open(os.path.join(ROOT, "include", "smat_b200.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    names = set(re.findall(r"\b(smat_[a-z0-9_]+)\s*\(", hdr))
+    assert {"smat_spmm_bcsr_f16", "smat_bcsr_count", "smat_bcsr_fill", "smat_read_mtx", "smat_reorder_rows",
+            "smat_last_error_string"} <= names
+    L = S.lib()
+    for n in sorted(names):
+        assert hasattr(L, n), f"{n} is declared in include/smat_b200.h but not exported"
+
+
+def test_no_gpu_means_loud_failure_not_fallback():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    L = S.lib()
+    buf = (ctypes.c_int * 64)()
+    rc = L.smat_spmm_bcsr_f16(ctypes.addressof(buf), ctypes.addressof(buf), ctypes.addressof(buf),
+                              ctypes.addressof(buf), ctypes.addressof(buf), 16, 8, 16, 1, None, None, None)
+    assert rc == -2 and L.smat_last_error_string()  # SMAT_ERR_CUDA with a message
+
+
+def test_bad_arguments_are_reported():
+    L = S.lib()
+    assert L.smat_spmm_bcsr_f16(None, None, None, None, None, 17, 8, 16, 0, None, None, None) == -1
+    assert b"multiples of 16" in L.smat_last_error_string()
+    assert L.smat_spmm_bcsr_f16(None, None, None, None, None, 16, 7, 16, 0, None, None, None) == -1
+    assert L.smat_spmm_set_variant(99) == -1
+    with pytest.raises(S.SmatError):
+        S.read_mtx("/nonexistent/file.mtx")
+
+
+def test_reader_matches_oracle(tmp_path):
+    rng = np.random.default_rng(2)
+    M, K, n = 253, 251, 3000  # not multiples of 16: both readers pad to 256 x 256
+    keys = np.unique(rng.integers(0, M * K, n))
+    rng.shuffle(keys)  # file order is kept inside rows
+    rows, cols = keys // K, keys % K
+    vals = rng.standard_normal(keys.size)
+    path = str(tmp_path / "a.mtx")
+    with open(path, "w") as f:
+        f.write(f"%%MatrixMarket matrix coordinate real general\n% c\n{M} {K} {keys.size}\n")
+        f.write("".join(f"{r + 1} {c + 1} {v!r}\n" for r, c, v in zip(rows.tolist(), cols.tolist(), vals.tolist())))
+    a, b = oracle.read_mtx(path), S.read_mtx(path)
+    assert a[0] == b[0] == 256 and a[1] == b[1] == 256 and a[5] == b[5]
+    assert np.array_equal(a[2], b[2]) and np.array_equal(a[3], b[3])
+    assert np.array_equal(a[4].view(np.uint16), b[4].view(np.uint16))
+    order = np.argsort(rows, kind="stable")
+    assert np.array_equal(b[3], cols[order]) and np.array_equal(b[4], vals[order].astype(np.float16))
+
+
+def test_reader_fields_and_symmetry(tmp_path):
+    cases = {
+        "real general": "1 2 0.1\n3 3 -2.5e-1\n2 1 65519.9\n",
+        "integer symmetric": "2 1 7\n3 3 -4\n3 1 2\n",
+        "complex hermitian": "2 1 1.5 9\n3 2 -0.25 1\n1 1 3 0\n",
+        "pattern general": "1 3\n3 1\n2 2\n",
+    }
+    for kind, body in cases.items():
+        f = tmp_path / (kind.replace(" ", "_") + ".mtx")
+        f.write_text(f"%%MatrixMarket matrix coordinate {kind}\n%c\n3 3 3\n{body}")
+        a, b = oracle.read_mtx(str(f)), S.read_mtx(str(f))
+        assert a[:2] == b[:2] == (16, 16) and a[5] == b[5]
+        assert np.array_equal(a[2], b[2]) and np.array_equal(a[3], b[3])
+        assert np.array_equal(a[4].view(np.uint16), b[4].view(np.uint16)), kind
+
+
+def test_jaccard_known_answers():
+    A, B = [1, 2, 5, 10, 12, 20], [0, 2, 4, 10, 16]
+    for b, want in ((1, 0.777778), (3, 0.5), (4, 0.5), (16, 0.0)):
+        assert S.jaccard_group(A, 1, B, 1, b) == pytest.approx(want, abs=1e-6)
+    rng = np.random.default_rng(5)
+    for _ in range(200):
+        a = np.unique(rng.integers(0, 200, rng.integers(0, 20)))
+        b = np.unique(rng.integers(0, 200, rng.integers(0, 20)))
+        gA, bs = int(rng.integers(1, 16)), int(rng.integers(1, 20))
+        assert S.jaccard_group(a, gA, b, 1, bs) == oracle.jaccard_group(a, gA, b, 1, bs)
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(ROOT, "tests", "golden", "reorder_*.npz"))),
+                         ids=lambda p: os.path.basename(p)[8:-4])
+@pytest.mark.parametrize("threads", [1, 3])
+def test_reorder_engine_matches_reference_fixtures(path, threads):
+    z = np.load(path)
+    g, p = S.reorder_rows(z["rowptr"], z["cols"], tau=float(z["tau"]), col_block=int(z["col_block"]),
+                          row_block=int(z["row_block"]), threads=threads)
+    assert np.array_equal(g, z["grouping"]) and np.array_equal(p, z["perm"])
+
+
+@pytest.mark.parametrize("name,scale", [("uniform", 0.06), ("powerlaw", 0.03), ("clustered", 0.008), ("band", 0.5)])
+def test_reorder_engine_matches_oracle_on_configs(name, scale):
+    p = gen.make_config(name, scale=scale)
+    g0, p0 = oracle.reorder_rows(p.rowptr.astype(np.int64), p.colidx.astype(np.int64))
+    g1, p1 = S.reorder_rows(p.rowptr, p.colidx, threads=4)
+    assert np.array_equal(g0, g1) and np.array_equal(p0, p1)
+    assert np.array_equal(np.sort(p1), np.arange(p.M))
+
+
+def test_reorder_rejects_unsorted_rows():
+    with pytest.raises(S.SmatError):
+        S.reorder_rows([0, 2], [5, 1])
+
+
+def test_apply_row_permutation_carries_values():
+    p = gen.make_config("uniform", scale=0.004)
+    perm = np.random.default_rng(0).permutation(p.M)
+    rp, ci, v = S.apply_row_permutation(p.rowptr, p.colidx, p.vals, perm)
+    for r in (0, 1, p.M // 2, p.M - 1):
+        o = perm[r]
+        assert np.array_equal(ci[rp[r]:rp[r + 1]], p.colidx[p.rowptr[o]:p.rowptr[o + 1]])
+        assert np.array_equal(v[rp[r]:rp[r + 1]], p.vals[p.rowptr[o]:p.rowptr[o + 1]])
+
+
+def test_partition_is_balanced_and_covers():
+    rng = np.random.default_rng(1)
+    counts = rng.integers(0, 50, 1000)
+    counts[500] = 4000
+    rp = np.zeros(1001, np.int32)
+    rp[1:] = np.cumsum(counts)
+    for parts in (1, 2, 4, 8):
+        b = S.partition_block_rows(rp, parts)
+        assert b[0] == 0 and b[-1] == 1000 and np.all(np.diff(b) >= 0)
+        loads = np.diff(rp[b])
+        assert loads.sum() == rp[-1]
+        if parts > 1:
+            assert loads.max() <= rp[-1] / parts + 4000
+    assert S.partition_block_rows(np.zeros(11, np.int32), 4).tolist() == [0, 2, 5, 7, 10]

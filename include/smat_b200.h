@@ -55,10 +55,25 @@ int smat_spmm_bcsr_f16_rows(const void* bcsrValuesA, const int* bcsrRowPtrA, con
                             void* C, size_t M, size_t N, size_t K, size_t nonzeroBlocks, size_t brow_begin,
                             size_t brow_end, void* stream);
 
-/* Kernel variant selection for smat_spmm_bcsr_f16*: 0 = automatic (default), otherwise a variant id
- * (see smat_spmm_variant_name).  Process-wide; meant for benchmarks and tests. */
-int smat_spmm_set_variant(int variant);
-const char* smat_spmm_variant_name(int variant);
+/* Multiplication plan: what the kernel needs beyond the BCSR arrays, computed on the device and
+ * reusable for any number of multiplications:
+ *   - the walk order (per group of 16 block-rows, its block-columns four at a time in ascending
+ *     order with the blocks found there), and
+ *   - a copy of the value blocks in that order, so that all blocks of a step arrive with one bulk
+ *     copy (nonzeroBlocks * 512 bytes of device memory owned by the plan).
+ * smat_spmm_bcsr_f16 builds all of this internally on every call (in stream-ordered scratch
+ * memory); a caller that multiplies repeatedly, like the reference harness with its warm-up and
+ * 10 timed launches (src/cuda_hgemm/src/common/tester.h:177-183, 344-347), creates it once instead.
+ * The plan covers block-rows [brow_begin, brow_end) and keeps the rowptr pointer it was given (not
+ * owned).  After the values of A changed (same structure) call smat_plan_set_values.
+ * No counterpart in the reference (its kernel re-reads bcsrColIdx per tile, mmaCBT.cu:38-43). */
+typedef struct smat_plan smat_plan;
+int smat_plan_create(smat_plan** plan, const void* bcsrValuesA, const int* bcsrRowPtrA, const int* bcsrColIdxA, size_t M,
+                     size_t K, size_t nonzeroBlocks, size_t brow_begin, size_t brow_end, void* stream);
+int smat_plan_set_values(smat_plan* plan, const void* bcsrValuesA, void* stream);
+/* Rows [16*brow_begin, 16*brow_end) of C = A x B; C points at the first row of that range. */
+int smat_plan_spmm(const smat_plan* plan, const void* B, void* C, size_t N, void* stream);
+int smat_plan_destroy(smat_plan* plan);
 
 /* Synchronises `stream` and reports whether any kernel launched by this library on the current
  * device recorded a device-side error (a bounded wait that ran out).  Clears the device status word.

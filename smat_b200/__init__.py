@@ -10,6 +10,7 @@ missing or if no sm_100 device is present.
 """
 from .api import (  # noqa: F401
     Matrix,
+    Plan,
     SmatError,
     SparseMatrix,
     Tester,
@@ -20,7 +21,6 @@ from .api import (  # noqa: F401
     partition_block_rows,
     read_mtx,
     reorder_rows,
-    set_variant,
     spmm,
     spmm_rows,
 )

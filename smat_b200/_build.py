@@ -5,8 +5,8 @@ import subprocess
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-LIB = os.path.join(HERE, "libsmat_b200.so")
-SOURCES = ["spmm_sm100.cu", "bcsr_build.cu", "capi.cu", "mtx_reader.cpp", "reorder.cpp"]
+LIB = os.environ.get("SMAT_LIB", os.path.join(HERE, "libsmat_b200.so"))
+SOURCES = ["spmm_sm100.cu", "plan.cu", "bcsr_build.cu", "capi.cu", "mtx_reader.cpp", "reorder.cpp"]
 HEADERS = ["ptx_sm100.cuh", "smat_internal.h", os.path.join("..", "..", "include", "smat_b200.h")]
 
 
@@ -33,6 +33,11 @@ def build(force=False, verbose=False):
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
+    if os.environ.get("SMAT_DEFS"):
+        for d in os.environ["SMAT_DEFS"].split():
+            cmd.insert(1, "-D" + d)
+    if os.environ.get("SMAT_PROFILE"):
+        cmd.insert(1, "-DSMAT_PROFILE")
     subprocess.check_call(cmd, cwd=CSRC)
     return LIB
 

@@ -17,8 +17,6 @@ std::atomic<long long> g_launches{0};
 std::mutex g_ctx_mutex;
 constexpr int kMaxDevices = 64;
 DeviceCtx g_ctx[kMaxDevices];
-
-const char* const kVariantNames[] = {"auto", "rg16x2", "rg32x1"};
 }  // namespace
 
 int fail(int code, const char* fmt, ...) {
@@ -55,7 +53,7 @@ int get_device_ctx(DeviceCtx** out) {
 }
 
 int encode_tensor_map_2d_f16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_pitch_bytes,
-                             uint32_t box_inner, uint32_t box_outer, int swizzle32, int l2_promo_bytes) {
+                             uint32_t box_inner, uint32_t box_outer, int swizzle_bytes, int l2_promo_bytes) {
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -78,7 +76,11 @@ int encode_tensor_map_2d_f16(CUtensorMap* map, const void* base, uint64_t inner,
                                                                  : CU_TENSOR_MAP_L2_PROMOTION_NONE;
     const CUresult r =
         encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE, promo,
+               CU_TENSOR_MAP_INTERLEAVE_NONE,
+               swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+               : swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                     : CU_TENSOR_MAP_SWIZZLE_NONE,
+               promo,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(SMAT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (dims %llu x %llu, pitch %llu, box %u x %u)",
@@ -108,13 +110,45 @@ using namespace smat;
 
 extern "C" {
 
+// One multiplication with a plan (walk order + packed copy of the blocks) built on the fly in
+// stream-ordered scratch memory.
+static int spmm_transient_plan(const void* vals, const int* rowptr, const int* colidx, const void* B, void* C, size_t N,
+                               size_t K, size_t nnzb, size_t brow_begin, size_t brow_end, cudaStream_t stream) {
+    if (brow_end == brow_begin || N == 0) return SMAT_OK;
+    PlanView v;
+    v.rowptr = rowptr;
+    v.K = K;
+    v.nnzb = nnzb;
+    v.brow_begin = brow_begin;
+    v.brow_end = brow_end;
+    const PlanSizes sz = plan_sizes(nnzb, brow_begin, brow_end);
+    v.n_groups = sz.n_groups;
+    if (nnzb == 0) return launch_spmm(v, B, C, N, stream);
+    void* buf = nullptr;
+    SMAT_CUDA_TRY(cudaMallocAsync(&buf, sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes + sz.packed_bytes, stream));
+    char* b = static_cast<char*>(buf);
+    v.gsp = reinterpret_cast<int*>(b);
+    v.steps = b + sz.gsp_bytes;
+    v.blk = reinterpret_cast<int*>(b + sz.gsp_bytes + sz.steps_bytes);
+    v.packed = b + sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes;
+    int rc = build_plan_async(rowptr, colidx, K, nnzb, brow_begin, brow_end, reinterpret_cast<int*>(b), b + sz.gsp_bytes,
+                              reinterpret_cast<int*>(b + sz.gsp_bytes + sz.steps_bytes), stream);
+    if (rc == SMAT_OK)
+        rc = pack_values_async(rowptr, vals, v.blk, b + sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes, brow_begin, brow_end, nnzb,
+                               stream);
+    if (rc == SMAT_OK) rc = launch_spmm(v, B, C, N, stream);
+    const cudaError_t e = cudaFreeAsync(buf, stream);
+    if (rc == SMAT_OK && e != cudaSuccess) return fail(SMAT_ERR_CUDA, "cudaFreeAsync failed: %s", cudaGetErrorString(e));
+    return rc;
+}
+
 int smat_spmm_bcsr_f16(const void* vals, const int* rowptr, const int* colidx, const void* B, void* C, size_t M, size_t N,
                        size_t K, size_t nnzb, const int* blockInfo, const int* relMap, void* stream) {
     (void)blockInfo;
     (void)relMap;
     clear_error();
     if (int rc = check_spmm_args(vals, rowptr, colidx, B, C, M, N, K, nnzb)) return rc;
-    return launch_spmm(vals, rowptr, colidx, B, C, M, N, K, nnzb, 0, M / 16, (cudaStream_t)stream);
+    return spmm_transient_plan(vals, rowptr, colidx, B, C, N, K, nnzb, 0, M / 16, (cudaStream_t)stream);
 }
 
 int smat_spmm_bcsr_f16_rows(const void* vals, const int* rowptr, const int* colidx, const void* B, void* C, size_t M,
@@ -123,18 +157,7 @@ int smat_spmm_bcsr_f16_rows(const void* vals, const int* rowptr, const int* coli
     if (int rc = check_spmm_args(vals, rowptr, colidx, B, C, M, N, K, nnzb)) return rc;
     if (brow_begin > brow_end || brow_end > M / 16)
         return fail(SMAT_ERR_BAD_ARG, "block-row range [%zu, %zu) outside [0, %zu]", brow_begin, brow_end, M / 16);
-    return launch_spmm(vals, rowptr, colidx, B, C, M, N, K, nnzb, brow_begin, brow_end, (cudaStream_t)stream);
-}
-
-int smat_spmm_set_variant(int variant) {
-    if (variant < 0 || variant > 2) return fail(SMAT_ERR_BAD_ARG, "unknown SpMM variant %d", variant);
-    g_spmm_variant = variant;
-    return SMAT_OK;
-}
-
-const char* smat_spmm_variant_name(int variant) {
-    if (variant < 0 || variant > 2) return "";
-    return kVariantNames[variant];
+    return spmm_transient_plan(vals, rowptr, colidx, B, C, N, K, nnzb, brow_begin, brow_end, (cudaStream_t)stream);
 }
 
 int smat_device_status(void* stream) {

@@ -1,0 +1,338 @@
+// Multiplication plan: the walk order of the SpMM kernel, computed on the device from the BCSR
+// structure.
+//
+// For every group of 16 consecutive block-rows the kernel visits the group's block-columns in
+// ascending order, four block-columns ("quad") at a time; per visited quad ("step") it needs the
+// quad's column, which (sub-column, row) positions hold a block (a 64-bit mask) and the indices of
+// those blocks.  Quads holding more than kPlanBlocksPerStep blocks are cut into several steps.
+// The reference kernel has no such structure: it launches one CTA per (block-row, 8 columns of C)
+// and walks bcsrColIdx directly (src/cuda_hgemm/src/mma/mmaCBT.cu:38-43), re-fetching the same B
+// slab for every block-row that shares a block-column.
+//
+// Build: one CTA (16 warps) per group, warp w owns block-row w of the group.  Block-columns are
+// processed in windows of 16384; inside a window a shared word per block-column collects the row
+// mask (atomicOr), block-wide prefix sums number the steps and the blocks, then every block
+// scatters its own index into the (group, column, row) order.  The number of steps per group is
+// counted first (same pass without the scatter) and scanned.
+#include <cuda_fp16.h>
+
+#include <new>
+
+#include "smat_internal.h"
+
+namespace smat {
+namespace {
+
+constexpr int RG = kPlanRowsPerGroup;
+constexpr int kPlanThreads = RG * 32;
+constexpr int CAP = kPlanBlocksPerStep;
+constexpr int kWindow = 16384;  // block-columns per pass: 64 KB of masks + 64 KB of block prefixes
+
+// Fills masks[0..kWindow) for block-columns [w0, w0 + kWindow) of the group; cursor[] (one per warp,
+// kept by lane 0 semantics via registers) walks each row once over all windows.
+__device__ __forceinline__ void mark_window(const int* __restrict__ colidx, int& cur, int end, int w0, uint32_t* masks,
+                                            int warp, int lane) {
+    for (int i = threadIdx.x; i < kWindow; i += kPlanThreads) masks[i] = 0u;
+    __syncthreads();
+    // every lane keeps the same `cur`; lanes stride over the row until the window ends
+    for (;;) {
+        const int j = cur + lane;
+        int cb = (j < end) ? (__ldg(colidx + j) >> 4) : INT_MAX;
+        const bool in = cb < w0 + kWindow;
+        if (in) atomicOr(&masks[cb - w0], 1u << warp);
+        const uint32_t b = __ballot_sync(0xffffffffu, in);
+        cur += __popc(b);
+        if (b != 0xffffffffu) break;
+    }
+    __syncthreads();
+}
+
+// Block-wide exclusive scan of one int per thread; returns the exclusive prefix, *total gets the sum.
+__device__ __forceinline__ int block_exclusive_scan(int v, int* total, int* sh) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int inc = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += t;
+    }
+    if (lane == 31) sh[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int w = lane < (kPlanThreads >> 5) ? sh[lane] : 0;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, w, d);
+            if (lane >= d) w += t;
+        }
+        sh[32 + lane] = w;  // inclusive warp totals
+    }
+    __syncthreads();
+    const int before = warp ? sh[32 + warp - 1] : 0;
+    *total = sh[32 + (kPlanThreads >> 5) - 1];
+    __syncthreads();
+    return before + inc - v;
+}
+
+template <bool FILL>
+__global__ void __launch_bounds__(kPlanThreads)
+plan_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx, int brow_begin, int brow_end, int Kb,
+            int n_groups, int* __restrict__ gsp, uint4* __restrict__ steps, int* __restrict__ blk) {
+    extern __shared__ uint32_t sm[];
+    uint32_t* masks = sm;                                 // [kWindow] row mask per block-column
+    int* blk_pre = reinterpret_cast<int*>(sm + kWindow);  // [kWindow] exclusive block number (FILL only)
+    __shared__ int scan_sh[64];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
+        const int row = brow_begin + g * RG + warp;
+        const bool have = row < brow_end;
+        const int beg = have ? __ldg(rowptr + row) : 0;
+        const int end = have ? __ldg(rowptr + row + 1) : 0;
+        const int gfirst = __ldg(rowptr + brow_begin + g * RG);  // first block of the group
+        int cur = beg;
+        int steps_done = 0, blocks_done = 0;
+        const int gs = FILL ? __ldg(gsp + g) : 0;
+        for (int w0 = 0; w0 < Kb; w0 += kWindow) {
+            const int cur_before = cur;
+            mark_window(colidx, cur, end, w0, masks, warp, lane);
+            // per-thread chunk of the window: PER consecutive block-columns = PER / 4 quads
+            constexpr int PER = kWindow / kPlanThreads;
+            static_assert(PER % 4 == 0, "a thread owns whole quads");
+            const int i0 = threadIdx.x * PER;
+            int ns = 0, nb = 0;
+#pragma unroll
+            for (int qd = 0; qd < PER / 4; qd++) {
+                const int c = __popc(masks[i0 + 4 * qd]) + __popc(masks[i0 + 4 * qd + 1]) + __popc(masks[i0 + 4 * qd + 2]) +
+                              __popc(masks[i0 + 4 * qd + 3]);
+                ns += (c + CAP - 1) / CAP;
+                nb += c;
+            }
+            int tot_s, tot_b = 0;
+            const int pre_s = block_exclusive_scan(ns, &tot_s, scan_sh);
+            if (FILL) {
+                const int pre_b = block_exclusive_scan(nb, &tot_b, scan_sh);
+                int s = steps_done + pre_s, b = blocks_done + pre_b;
+                for (int qd = 0; qd < PER / 4; qd++) {
+                    unsigned long long m64 = 0;
+#pragma unroll
+                    for (int sub = 0; sub < 4; sub++) {
+                        const uint32_t mk = masks[i0 + 4 * qd + sub];
+                        blk_pre[i0 + 4 * qd + sub] = b + __popcll(m64);
+                        m64 |= (unsigned long long)mk << (16 * sub);
+                    }
+                    // cut the quad into steps of at most CAP blocks, in (sub-column, row) order
+                    while (m64) {
+                        unsigned long long part = 0;
+                        for (int t = 0; t < CAP && m64; t++) {
+                            const unsigned long long low = m64 & (~m64 + 1ull);
+                            part |= low;
+                            m64 ^= low;
+                        }
+                        steps[gs + s] = make_uint4((uint32_t)(w0 + i0 + 4 * qd) << 4, (uint32_t)(gfirst + b), (uint32_t)part,
+                                                   (uint32_t)(part >> 32));
+                        s++;
+                        b += __popcll(part);
+                    }
+                }
+                __syncthreads();
+                // scatter: block j of this warp's row goes to its (column, row) rank inside the group
+                for (int j = cur_before + lane; j < cur; j += 32) {
+                    const int cb = (__ldg(colidx + j) >> 4) - w0;
+                    blk[gfirst + blk_pre[cb] + __popc(masks[cb] & ((1u << warp) - 1u))] = j;
+                }
+                blocks_done += tot_b;
+            }
+            steps_done += tot_s;
+            __syncthreads();
+        }
+        if (!FILL && threadIdx.x == 0) gsp[g + 1] = steps_done;
+    }
+    if (!FILL && blockIdx.x == 0 && threadIdx.x == 0) gsp[0] = 0;
+}
+
+// In-place inclusive scan of data[0..n) by one CTA.
+__global__ void __launch_bounds__(1024) plan_scan_kernel(int* data, int n) {
+    __shared__ int warp_tot[32];
+    __shared__ int carry_s;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) carry_s = 0;
+    __syncthreads();
+    for (int base = 0; base < n; base += 1024) {
+        const int i = base + threadIdx.x;
+        int v = i < n ? data[i] : 0;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, v, d);
+            if (lane >= d) v += t;
+        }
+        if (lane == 31) warp_tot[warp] = v;
+        __syncthreads();
+        if (warp == 0) {
+            int w = warp_tot[lane];
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, w, d);
+                if (lane >= d) w += t;
+            }
+            warp_tot[lane] = w;
+        }
+        __syncthreads();
+        v += carry_s + (warp ? warp_tot[warp - 1] : 0);
+        if (i < n) data[i] = v;
+        __syncthreads();
+        if (threadIdx.x == 1023) carry_s = v;
+        __syncthreads();
+    }
+}
+
+// packed[i] <- vals[blk[i]] for i in [first, last): one warp per block, lane l moves the 16-byte chunk
+// l (row l/2, half l%2) to chunk l ^ ((l >> 3) & 1), i.e. the 32-byte swizzle.
+__global__ void __launch_bounds__(256) pack_kernel(const uint4* __restrict__ vals, const int* __restrict__ blk,
+                                                  uint4* __restrict__ packed, const int* __restrict__ rowptr, int brow_begin,
+                                                  int brow_end) {
+    const int first = __ldg(rowptr + brow_begin), last = __ldg(rowptr + brow_end);
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    for (int i = first + ((blockIdx.x * blockDim.x + threadIdx.x) >> 5); i < last; i += warps) {
+        const int src = __ldg(blk + i);
+        packed[(size_t)i * 32 + (lane ^ ((lane >> 3) & 1))] = __ldg(vals + (size_t)src * 32 + lane);
+    }
+}
+
+}  // namespace
+
+int pack_values_async(const int* rowptr, const void* vals, const int* blk, void* packed, size_t brow_begin,
+                      size_t brow_end, size_t nnzb, cudaStream_t stream) {
+    if (nnzb == 0 || brow_end == brow_begin) return SMAT_OK;
+    DeviceCtx* ctx = nullptr;
+    if (int rc = get_device_ctx(&ctx)) return rc;
+    pack_kernel<<<ctx->sm_count * 8, 256, 0, stream>>>(reinterpret_cast<const uint4*>(vals), blk,
+                                                       reinterpret_cast<uint4*>(packed), rowptr, (int)brow_begin,
+                                                       (int)brow_end);
+    count_launch();
+    SMAT_CUDA_TRY(cudaGetLastError());
+    return SMAT_OK;
+}
+
+PlanSizes plan_sizes(size_t nnzb, size_t brow_begin, size_t brow_end) {
+    PlanSizes s;
+    s.n_groups = (brow_end - brow_begin + RG - 1) / RG;
+    s.gsp_bytes = ((s.n_groups + 1) * sizeof(int) + 255) / 256 * 256;
+    // a group has at most as many steps as blocks, so nnzb bounds the total
+    s.steps_bytes = ((nnzb ? nnzb : 1) * sizeof(uint4) + 255) / 256 * 256;
+    s.blk_bytes = ((nnzb ? nnzb : 1) * sizeof(int) + 255) / 256 * 256;
+    s.packed_bytes = (nnzb ? nnzb : 1) * 512;
+    return s;
+}
+
+int build_plan_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
+                     int* gsp, void* steps, int* blk, cudaStream_t stream) {
+    DeviceCtx* ctx = nullptr;
+    if (int rc = get_device_ctx(&ctx)) return rc;
+    const size_t n_groups = (brow_end - brow_begin + RG - 1) / RG;
+    if (n_groups == 0) return SMAT_OK;
+    if (nnzb == 0) {
+        SMAT_CUDA_TRY(cudaMemsetAsync(gsp, 0, (n_groups + 1) * sizeof(int), stream));
+        return SMAT_OK;
+    }
+    const int Kb = (int)(K / 16);
+    const int grid = (int)(n_groups < (size_t)ctx->sm_count ? n_groups : (size_t)ctx->sm_count);
+    const size_t smem_count = (size_t)kWindow * 4, smem_fill = (size_t)kWindow * 8;
+    SMAT_CUDA_TRY(cudaFuncSetAttribute(plan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_count));
+    SMAT_CUDA_TRY(cudaFuncSetAttribute(plan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fill));
+    plan_kernel<false><<<grid, kPlanThreads, smem_count, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, Kb,
+                                                                  (int)n_groups, gsp, nullptr, nullptr);
+    count_launch();
+    plan_scan_kernel<<<1, 1024, 0, stream>>>(gsp, (int)n_groups + 1);
+    count_launch();
+    plan_kernel<true><<<grid, kPlanThreads, smem_fill, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, Kb,
+                                                                 (int)n_groups, gsp, reinterpret_cast<uint4*>(steps), blk);
+    count_launch();
+    SMAT_CUDA_TRY(cudaGetLastError());
+    return SMAT_OK;
+}
+
+}  // namespace smat
+
+using namespace smat;
+
+struct smat_plan {
+    PlanView v;
+    void* buffer = nullptr;
+    int device = -1;
+};
+
+extern "C" {
+
+int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRowPtrA, const int* bcsrColIdxA, size_t M,
+                     size_t K, size_t nnzb, size_t brow_begin, size_t brow_end, void* stream) {
+    clear_error();
+    if (!out || !bcsrRowPtrA || (nnzb && (!bcsrColIdxA || !bcsrValuesA))) return fail(SMAT_ERR_BAD_ARG, "NULL argument");
+    if (M % 16 || K % 16) return fail(SMAT_ERR_BAD_ARG, "M (%zu) and K (%zu) must be multiples of 16", M, K);
+    if ((uintptr_t)bcsrValuesA & 15) return fail(SMAT_ERR_BAD_ARG, "bcsrValuesA must be 16-byte aligned");
+    if (brow_begin > brow_end || brow_end > M / 16)
+        return fail(SMAT_ERR_BAD_ARG, "block-row range [%zu, %zu) outside [0, %zu]", brow_begin, brow_end, M / 16);
+    if (nnzb * 16 >= ((size_t)1 << 31) || K >= ((size_t)1 << 31)) return fail(SMAT_ERR_RANGE, "size beyond 2^31");
+    smat_plan* p = new (std::nothrow) smat_plan();
+    if (!p) return fail(SMAT_ERR_NOMEM, "out of host memory");
+    const PlanSizes sz = plan_sizes(nnzb, brow_begin, brow_end);
+    cudaError_t e = cudaGetDevice(&p->device);
+    if (e == cudaSuccess) e = cudaMalloc(&p->buffer, sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes + sz.packed_bytes);
+    if (e != cudaSuccess) {
+        delete p;
+        return fail(SMAT_ERR_CUDA, "plan allocation failed: %s", cudaGetErrorString(e));
+    }
+    char* b = static_cast<char*>(p->buffer);
+    p->v.rowptr = bcsrRowPtrA;
+    p->v.gsp = reinterpret_cast<int*>(b);
+    p->v.steps = b + sz.gsp_bytes;
+    p->v.blk = reinterpret_cast<int*>(b + sz.gsp_bytes + sz.steps_bytes);
+    p->v.packed = b + sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes;
+    p->v.K = K;
+    p->v.nnzb = nnzb;
+    p->v.brow_begin = brow_begin;
+    p->v.brow_end = brow_end;
+    p->v.n_groups = sz.n_groups;
+    int rc = build_plan_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, const_cast<int*>(p->v.gsp),
+                              const_cast<void*>(p->v.steps), const_cast<int*>(p->v.blk), (cudaStream_t)stream);
+    if (rc == SMAT_OK)
+        rc = pack_values_async(bcsrRowPtrA, bcsrValuesA, p->v.blk, const_cast<void*>(p->v.packed), brow_begin, brow_end,
+                               nnzb, (cudaStream_t)stream);
+    if (rc) {
+        cudaFree(p->buffer);
+        delete p;
+        return rc;
+    }
+    *out = p;
+    return SMAT_OK;
+}
+
+int smat_plan_set_values(smat_plan* plan, const void* bcsrValuesA, void* stream) {
+    clear_error();
+    if (!plan || (plan->v.nnzb && !bcsrValuesA)) return fail(SMAT_ERR_BAD_ARG, "NULL argument");
+    if ((uintptr_t)bcsrValuesA & 15) return fail(SMAT_ERR_BAD_ARG, "bcsrValuesA must be 16-byte aligned");
+    return pack_values_async(plan->v.rowptr, bcsrValuesA, plan->v.blk, const_cast<void*>(plan->v.packed),
+                             plan->v.brow_begin, plan->v.brow_end, plan->v.nnzb, (cudaStream_t)stream);
+}
+
+int smat_plan_spmm(const smat_plan* plan, const void* B, void* C, size_t N, void* stream) {
+    clear_error();
+    if (!plan) return fail(SMAT_ERR_BAD_ARG, "plan is NULL");
+    if (N % 8) return fail(SMAT_ERR_BAD_ARG, "N (%zu) must be a multiple of 8", N);
+    if (plan->v.brow_end > plan->v.brow_begin && N && (!C || (plan->v.nnzb && !B)))
+        return fail(SMAT_ERR_BAD_ARG, "B or C is NULL");
+    if (((uintptr_t)B | (uintptr_t)C) & 15) return fail(SMAT_ERR_BAD_ARG, "B and C must be 16-byte aligned");
+    if (N >= ((size_t)1 << 31)) return fail(SMAT_ERR_RANGE, "N beyond 2^31");
+    return launch_spmm(plan->v, B, C, N, (cudaStream_t)stream);
+}
+
+int smat_plan_destroy(smat_plan* plan) {
+    clear_error();
+    if (!plan) return SMAT_OK;
+    cudaError_t e = cudaFree(plan->buffer);
+    delete plan;
+    if (e != cudaSuccess) return fail(SMAT_ERR_CUDA, "cudaFree failed: %s", cudaGetErrorString(e));
+    return SMAT_OK;
+}
+
+}  // extern "C"

@@ -42,12 +42,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Same, but the hardware may keep the thread suspended for up to `hint_ns` nanoseconds while the phase
+// is incomplete, instead of returning at once: a waiting warp then does not occupy the issue and
+// shared-memory pipes that the producing warps need.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+
 // ---- TMA tiled 2-D load (global -> this CTA's shared memory), completion on an mbarrier -------
 __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst_smem), "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
+}
+// Bulk copy of `bytes` contiguous bytes (multiple of 16, both addresses 16-byte aligned) global -> shared.
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
 }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
@@ -56,6 +77,15 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
 // ---- cp.async (4-byte), per-thread groups -----------------------------------------------------
 __device__ __forceinline__ void cp_async_4(uint32_t dst_smem, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+// 16-byte copy that bypasses L1; completion can be attached to an mbarrier (below).
+__device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+// The mbarrier receives one arrival (counted against its expected-arrival count) once every cp.async
+// issued so far by this thread has completed.
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -85,6 +115,19 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uin
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Same, with each 64-bit descriptor given as (low word, high word): the low word carries the start address
+// and is the only part that changes between MMAs, so callers keep the high words in registers and update
+// the low words with 32-bit adds.
+__device__ __forceinline__ void mma_f16_ss_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                                uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // Same with the A operand resident in tensor memory (128 lanes x K/2 32-bit columns).
@@ -138,6 +181,13 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 __device__ __forceinline__ uint64_t smem_desc_k_sw32(uint32_t smem_addr) {
     return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(256 >> 4) << 32) | (1ull << 46) |
            (6ull << 61);
+}
+// Same for a tile whose rows are 128 bytes (64 fp16) laid out with the 128-byte swizzle (layout type 2,
+// 8-row groups 1024 bytes apart).  One MMA consumes 16 k = 32 bytes of each row; the k-slice is chosen by
+// adding (32 bytes >> 4) per slice to the start-address field.  The tile must be 1024-byte aligned.
+__device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
+           (2ull << 61);
 }
 // Instruction descriptor for kind::f16: fp32 accumulator (bits [4,6) = 1), fp16 A and B (formats 0),
 // both operands K-major, N >> 3 in bits [17,23), M >> 4 in bits [24,29).

@@ -34,12 +34,44 @@ void count_launch();
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against libcuda).
 int encode_tensor_map_2d_f16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_pitch_bytes,
-                             uint32_t box_inner, uint32_t box_outer, int swizzle32, int l2_promo_bytes);
+                             uint32_t box_inner, uint32_t box_outer, int swizzle_bytes, int l2_promo_bytes);
 
-// Launch of the SpMM kernels (spmm_sm100.cu).
-int launch_spmm(const void* vals, const int* rowptr, const int* colidx, const void* B, void* C, size_t M, size_t N,
-                size_t K, size_t nnzb, size_t brow_begin, size_t brow_end, cudaStream_t stream);
+// Block-rows per work item of the SpMM kernel; the multiplication plan is built for this grouping.
+constexpr int kPlanRowsPerGroup = 16;
+// A step of the plan covers four consecutive block-columns and carries at most this many blocks.
+constexpr int kPlanBlocksPerStep = 24;
 
-extern int g_spmm_variant;
+// The precomputed walk order of a block-row range (plan.cu).  All pointers are device memory.
+//   gsp[n_groups + 1]  first step of every group of kPlanRowsPerGroup block-rows
+//   steps              uint4 {element column of the quad (multiple of 64), first entry in blk,
+//                      mask bits 0..31, mask bits 32..63} per step; a step is a quad of four
+//                      consecutive block-columns of a group (or a slice of one holding at most
+//                      kPlanBlocksPerStep blocks), ascending inside a group; mask bit
+//                      16 * sub-column + row marks a block
+//   blk[nnzb]          block indices in (group, block-column, row) order; indexed with the ABSOLUTE
+//                      block position, i.e. the entries of group g occupy
+//                      [rowptr[first row of g], rowptr[first row of g + 1])
+//   packed[nnzb*512 B] the value blocks in that same order, each stored in the 32-byte-swizzled form
+//                      the MMA shared-memory descriptor reads (16-byte chunk index XOR bit 2 of the row)
+struct PlanView {
+    const int* rowptr = nullptr;  // bcsrRowPtr of the whole matrix
+    const int* gsp = nullptr;
+    const void* steps = nullptr;
+    const int* blk = nullptr;
+    const void* packed = nullptr;
+    size_t K = 0, nnzb = 0, brow_begin = 0, brow_end = 0, n_groups = 0;
+};
+
+// Work-list sizes for a block-row range and the asynchronous build on `stream` (plan.cu).
+struct PlanSizes { size_t n_groups, gsp_bytes, steps_bytes, blk_bytes, packed_bytes; };
+PlanSizes plan_sizes(size_t nnzb, size_t brow_begin, size_t brow_end);
+int build_plan_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
+                     int* gsp, void* steps, int* blk, cudaStream_t stream);
+// packed[i] = swizzled copy of value block blk[i] for the blocks of block-rows [brow_begin, brow_end).
+int pack_values_async(const int* rowptr, const void* vals, const int* blk, void* packed, size_t brow_begin,
+                      size_t brow_end, size_t nnzb, cudaStream_t stream);
+
+// Launch of the SpMM kernel (spmm_sm100.cu).
+int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStream_t stream);
 
 }  // namespace smat

@@ -1,5 +1,5 @@
-// Block-sparse SpMM  C = A_bcsr x B  for NVIDIA B200 (sm_100a): TMA-fed, tcgen05.mma with fp32
-// accumulators in tensor memory, persistent warp-specialised CTAs.
+// Block-sparse SpMM  C = A_bcsr x B  for NVIDIA B200 (sm_100a): tcgen05.mma with fp32 accumulators
+// in tensor memory, B panels fetched by TMA, A blocks by cp.async, persistent warp-specialised CTAs.
 //
 // Replaces the reference's one-warp-per-tile mma.sync kernel and its launcher
 // (mmaCBTKernelSparse / mmaCBTKernel, src/cuda_hgemm/src/mma/mmaCBT.cu:13-88) behind the same
@@ -9,21 +9,34 @@
 // 128-row minimum of tcgen05.mma, so the product is computed transposed:
 //     C^T[n0:n0+128, 16 rows of block-row r]  +=  B^T[n0:n0+128, 16 k of block-column c] * A_blk^T
 //   * MMA "A" operand = a panel of B: 128 n x 16 k, K-major -- exactly how the boundary stores B
-//     (element (k, n) at B[n*K + k]); one TMA box {16 k, 128 n} at x = colidx fetches it;
+//     (element (k, n) at B[n*K + k]); a TMA box {64 k, 128 n} fetches four such panels side by side,
+//     written with the 128-byte swizzle, and the MMA descriptor selects one by a 32-byte offset;
 //   * MMA "B" operand = the 16x16 block of A, row-major = N(16 rows) x K(16) K-major -- exactly how
-//     BCSR stores it; one TMA box {16, 16} over the value array viewed as [nnzb*16][16];
+//     BCSR stores it.  The plan keeps a copy of the blocks in the order the kernel consumes them,
+//     already in the 32-byte-swizzled form the descriptor expects, so that all blocks of a step
+//     arrive with ONE bulk copy (measured: per-block 16-byte cp.async gathers sustain only ~6
+//     bytes/clock/SM from HBM because few of them can be in flight);
 //   * D = 128 lanes (columns of C) x 16 fp32 columns (rows of the block-row) in tensor memory.
 //
-// Work decomposition.  A work item is (group of RG consecutive block-rows) x (128 columns of C).
-// All RG accumulators of an item live in tensor memory at once (RG*16 columns, NBUF buffers), and
-// the item walks the UNION of the group's block-columns in ascending order: each B panel is
-// fetched once per item and used by every block of the group in that block-column.  The walk is a
-// RG-way merge of the sorted colidx lists done by the producer warp with warp votes
-// (min-reduction + ballot), so no auxiliary work list is read from memory.
+// Work decomposition.  A work item is (group of RG = 16 consecutive block-rows) x (128 columns of
+// C).  The 16 accumulators of an item live in tensor memory at once (two buffers of 256 columns,
+// so the epilogue of one item overlaps the main loop of the next).  An item walks the group's
+// block-columns in ascending order in units of FOUR block-columns (64 k): measured on B200, a
+// gather of 32-byte rows (one block-column of B) is limited to one 32-byte L2 sector per clock
+// per SM whatever the engine (TMA or cp.async), so the panel is fetched 128 bytes wide -- the same
+// number of requests moves four block-columns -- and feeds every block of the group in those four
+// columns.  The walk order is precomputed (plan.cu): one 16-byte step descriptor {element column
+// of the quad, first block, 64-bit (sub-column, row) mask} per non-empty quad (quads with more than
+// CAP blocks are split) and a block-index list in (group, column, row) order.
 //
-// Warps: 0 = producer (merge + TMA issue), 1 = MMA issuer (one thread) and tensor-memory owner,
-// 2..5 = epilogue (tcgen05.ld -> fp16 -> paired, coalesced stores).  Pipelines (mbarrier rings):
-// B panels (SP stages), A blocks (SA chunks of 8 blocks), accumulator buffers (NBUF).
+// Measured on B200: one thread can issue a tcgen05.mma only every ~50 cycles and a TMA / bulk copy
+// only every ~160-250 cycles, whatever their size, while different warps issue concurrently.  So
+// issue is spread over warps: 4 loader warps (each takes every 4th step: one TMA for the 16 KB
+// panel, one bulk copy for the step's A blocks), 16 MMA warps (one issuing thread each, owning one
+// accumulator, so that every accumulator is updated by a single thread, in order; the per-MMA
+// address arithmetic of a lone thread is a serial dependency chain of ~200 cycles, which is why
+// one accumulator per thread pays), and 4 epilogue warps (tcgen05.ld -> fp16 -> paired coalesced
+// stores).
 //
 // Every wait is bounded: when a wait runs out the kernel records a status code, stops waiting
 // anywhere in the CTA, and runs to completion (results are then invalid and the host reports
@@ -40,27 +53,36 @@ using namespace ptx;
 
 namespace {
 
-constexpr int kThreads = 192;
-constexpr int NT = 128;      // columns of C per work item = tensor-memory lanes = MMA M
-constexpr int SP = 16;       // B-panel pipeline stages
-constexpr int SA = 16;       // A-block pipeline chunks
-constexpr int CHUNK = 8;     // A blocks per chunk
-constexpr int KEYRING = 8;   // per-row colidx prefetch depth (cp.async ring)
-constexpr uint32_t PANEL_BYTES = NT * 16 * 2;
+constexpr int RG = kPlanRowsPerGroup;  // block-rows per work item
+constexpr int CAP = kPlanBlocksPerStep;  // most blocks a step can carry
+constexpr int NBUF = 2;                // accumulator buffers in tensor memory
+constexpr int NL = 4;                  // loader warps
+#ifndef SMAT_NM
+#define SMAT_NM 16
+#endif
+constexpr int NM = SMAT_NM;            // MMA-issuing warps
+constexpr int S = 7;                   // steps in flight (pipeline stages)
+constexpr int NT = 128;                // columns of C per work item = tensor-memory lanes = MMA M
+constexpr int kThreads = (NL + NM + 4) * 32;
+constexpr uint32_t PANEL_BYTES = NT * 64 * 2;  // 128 n x 64 k fp16
 constexpr uint32_t ABLK_BYTES = 16 * 16 * 2;
+constexpr uint32_t STAGE_BYTES = PANEL_BYTES + CAP * ABLK_BYTES;
 constexpr long long WAIT_LIMIT = 4000000000LL;  // clock cycles (about two seconds)
 
-constexpr uint32_t OFF_PANEL = 0;
-constexpr uint32_t OFF_ABLK = OFF_PANEL + SP * PANEL_BYTES;
-constexpr uint32_t OFF_KEYS = OFF_ABLK + SA * CHUNK * ABLK_BYTES;
-constexpr uint32_t OFF_META = OFF_KEYS + 32 * KEYRING * 4;
-constexpr uint32_t OFF_BAR = OFF_META + SP * 8;
-constexpr uint32_t N_BARS = 2 * SP + 2 * SA + 4;
+constexpr uint32_t OFF_STAGE = 0;
+constexpr uint32_t OFF_META = OFF_STAGE + S * STAGE_BYTES;
+constexpr uint32_t OFF_BAR = OFF_META + S * 8;
+constexpr uint32_t N_BARS = 2 * S + 4;
 constexpr uint32_t OFF_MISC = OFF_BAR + N_BARS * 8;
 constexpr uint32_t SMEM_USED = OFF_MISC + 16;
 constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;  // slack for the manual 1024-byte alignment
 
 constexpr uint32_t IDESC = idesc_f16_f32(128, 16);
+
+static_assert(RG == 16, "row masks and accumulator ownership below assume 16 block-rows per group");
+static_assert(RG * NBUF * 16 <= 512, "accumulators must fit the 512 tensor-memory columns");
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+static_assert(STAGE_BYTES % 1024 == 0 && CAP <= 32, "stage alignment / one block index per lane");
 
 __device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
     uint32_t v;
@@ -71,12 +93,31 @@ __device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
     asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 
+#ifdef SMAT_PROFILE
+__device__ unsigned long long g_prof[16];
+#define PROF_ADD(code, t) atomicAdd(&g_prof[code], (unsigned long long)(t))
+#else
+#define PROF_ADD(code, t)
+#endif
+
 // Bounded mbarrier wait.  After the first time-out anywhere in the CTA every wait returns at once.
+__device__ __forceinline__ void wait_bar_impl(uint32_t bar, uint32_t parity, uint32_t abort_addr, int* status, int code);
 __device__ __forceinline__ void wait_bar(uint32_t bar, uint32_t parity, uint32_t abort_addr, int* status, int code) {
+#ifdef SMAT_PROFILE
+    const long long t0 = clock64();
+    wait_bar_impl(bar, parity, abort_addr, status, code);
+    PROF_ADD(code, clock64() - t0);
+    PROF_ADD(8 + code, 1);
+#else
+    wait_bar_impl(bar, parity, abort_addr, status, code);
+#endif
+}
+__device__ __forceinline__ void wait_bar_impl(uint32_t bar, uint32_t parity, uint32_t abort_addr, int* status, int code) {
     if (mbar_try_wait(bar, parity)) return;
     if (ld_shared_u32(abort_addr)) return;
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
+    // suspended waits: the warp sleeps in hardware until the phase completes or ~2 us pass
+    while (!mbar_try_wait_suspend(bar, parity, 2000u)) {
         if (ld_shared_u32(abort_addr)) return;
         if (clock64() - t0 > WAIT_LIMIT) {
             st_shared_u32(abort_addr, 1);
@@ -86,39 +127,44 @@ __device__ __forceinline__ void wait_bar(uint32_t bar, uint32_t parity, uint32_t
     }
 }
 
-template <int RG, int NBUF>
+// One loader-warp pipeline record: a step on its way from "descriptor requested" to "copies issued".
+struct StepRec {
+    int live;     // the record holds a step
+    int tile;     // n-tile of the item
+    uint32_t st;  // position of the step in this CTA's step sequence (selects the stage)
+    uint4 d;      // {element column of the quad, first packed block, mask bits 0..31, mask bits 32..63}
+};
+
 __global__ void __launch_bounds__(kThreads, 1)
-spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapA,
-                    const int* __restrict__ rowptr, const int* __restrict__ colidx, __half* __restrict__ C,
-                    int brow_begin, int brow_end, int N, int n_tiles, int n_items, uint32_t panel_bytes,
-                    int* status) {
-    static_assert(RG * NBUF * 16 <= 512, "accumulators must fit the 512 tensor-memory columns");
+spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __restrict__ packed,
+                    const uint4* __restrict__ steps, const int* __restrict__ gsp,
+                    const int* __restrict__ rowptr, __half* __restrict__ C, int brow_begin, int brow_end, int N,
+                    int n_tiles, int n_items, uint32_t panel_bytes, int* status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar0 = base + OFF_BAR;
-    auto full_p = [&](uint32_t s) { return bar0 + 8 * s; };
-    auto empty_p = [&](uint32_t s) { return bar0 + 8 * (SP + s); };
-    auto full_a = [&](uint32_t s) { return bar0 + 8 * (2 * SP + s); };
-    auto empty_a = [&](uint32_t s) { return bar0 + 8 * (2 * SP + SA + s); };
-    auto acc_full = [&](uint32_t b) { return bar0 + 8 * (2 * SP + 2 * SA + b); };
-    auto acc_empty = [&](uint32_t b) { return bar0 + 8 * (2 * SP + 2 * SA + 2 + b); };
+    auto full = [&](uint32_t s) { return bar0 + 8 * s; };
+    auto empty = [&](uint32_t s) { return bar0 + 8 * (S + s); };
+    auto acc_full = [&](uint32_t b) { return bar0 + 8 * (2 * S + b); };
+    auto acc_empty = [&](uint32_t b) { return bar0 + 8 * (2 * S + 2 + b); };
     const uint32_t tmem_slot = base + OFF_MISC;
     const uint32_t abort_addr = base + OFF_MISC + 4;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+#ifdef SMAT_PROFILE
+    const long long prof_t0 = clock64();
+#endif
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < SP; s++) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), 1); }
-        for (uint32_t s = 0; s < SA; s++) { mbar_init(full_a(s), 1); mbar_init(empty_a(s), 1); }
-        for (uint32_t b = 0; b < 2; b++) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
+        for (uint32_t s = 0; s < S; s++) { mbar_init(full(s), 1); mbar_init(empty(s), NM); }
+        for (uint32_t b = 0; b < 2; b++) { mbar_init(acc_full(b), NM); mbar_init(acc_empty(b), 4); }
         st_shared_u32(abort_addr, 0);
         fence_barrier_init();
         fence_proxy_async();
-        prefetch_tensormap(&mapA);
         prefetch_tensormap(&mapB);
     }
-    if (warp == 1) {
+    if (warp == NL) {
         tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
@@ -127,107 +173,115 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_const
     tc_fence_after();
     const uint32_t tmem_base = ld_shared_u32(tmem_slot);
 
-    if (warp == 0) {
-        // ------------------------------ producer: RG-way merge + TMA issue ------------------------------
-        uint32_t ps = 0, cs_base = 0;
-        const uint32_t ring = base + OFF_KEYS + (uint32_t)lane * KEYRING * 4;
-        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-            const int g = item / n_tiles, t = item - g * n_tiles;
-            const int row = brow_begin + g * RG + lane;
-            const bool valid = lane < RG && row < brow_end;
-            int p = valid ? __ldg(rowptr + row) : 0;
-            const int end = valid ? __ldg(rowptr + row + 1) : 0;
-            const int total = __reduce_add_sync(0xffffffffu, end - p);
-            if (total == 0) continue;
-#pragma unroll
-            for (int k = 0; k < KEYRING; k++) {
-                if (p + k < end) cp_async_4(ring + (uint32_t)((p + k) % KEYRING) * 4, colidx + p + k);
-                cp_async_commit();
+    if (warp < NL) {
+        // ------------------------------ loader warp j: every NL-th step ------------------------------
+        const int j = warp;
+        // head of the step stream: current item, its first step in `steps`, its step count, the position
+        // of its first step in the CTA's sequence, and the next position this warp owns
+        int h_item = blockIdx.x, h_gs = 0, h_ns = 0, n_gs = 0, n_ns = 0;
+        uint32_t h_st0 = 0, h_next = (uint32_t)j;
+        auto load_item = [&](int item, int& gs, int& ns) {
+            if (item < n_items) {
+                const int g = item / n_tiles;
+                gs = __ldg(gsp + g);
+                ns = __ldg(gsp + g + 1) - gs;
+            } else {
+                gs = 0;
+                ns = 0;
             }
-            cp_async_wait<KEYRING - 1>();
-            int key = (p < end) ? (int)ld_shared_u32(ring + (uint32_t)(p % KEYRING) * 4) : INT_MAX;
-            int a_pos = 0;
-            const int n0 = t * NT;
-            for (;;) {
-                const int c = __reduce_min_sync(0xffffffffu, key);
-                if (c == INT_MAX) break;
-                const bool has = key == c;
-                const uint32_t mask = __ballot_sync(0xffffffffu, has);
-                const int cnt = __popc(mask);
-                const uint32_t s = ps % SP;
-                if (lane == 0) {
-                    wait_bar(empty_p(s), ((ps / SP) & 1) ^ 1, abort_addr, status, 1);
-                    for (int ch = (a_pos + CHUNK - 1) / CHUNK; ch <= (a_pos + cnt - 1) / CHUNK; ++ch) {
-                        const uint32_t gc = cs_base + (uint32_t)ch, slot = gc % SA;
-                        wait_bar(empty_a(slot), ((gc / SA) & 1) ^ 1, abort_addr, status, 2);
-                        const int nb = min(CHUNK, total - CHUNK * ch);
-                        mbar_arrive_expect_tx(full_a(slot), (uint32_t)nb * ABLK_BYTES);
-                    }
-                    st_shared_u32(base + OFF_META + s * 8, mask);
-                    st_shared_u32(base + OFF_META + s * 8 + 4, (uint32_t)a_pos);
-                    mbar_arrive_expect_tx(full_p(s), panel_bytes);
-                    tma_load_2d(base + OFF_PANEL + s * PANEL_BYTES, &mapB, c, n0, full_p(s));
-                }
-                __syncwarp();
-                if (has) {
-                    const int q = a_pos + __popc(mask & ((1u << lane) - 1u));
-                    const uint32_t gc = cs_base + (uint32_t)(q / CHUNK), slot = gc % SA;
-                    tma_load_2d(base + OFF_ABLK + (slot * CHUNK + (uint32_t)(q % CHUNK)) * ABLK_BYTES, &mapA, 0, p * 16,
-                                full_a(slot));
-                    if (p + KEYRING < end) cp_async_4(ring + (uint32_t)(p % KEYRING) * 4, colidx + p + KEYRING);
-                    cp_async_commit();
-                    p++;
-                    cp_async_wait<KEYRING - 1>();
-                    key = (p < end) ? (int)ld_shared_u32(ring + (uint32_t)(p % KEYRING) * 4) : INT_MAX;
-                }
-                __syncwarp();
-                a_pos += cnt;
-                ps++;
-            }
-            cp_async_wait<0>();
-            cs_base += (uint32_t)((total + CHUNK - 1) / CHUNK);
-        }
-    } else if (warp == 1) {
-        // ------------------------------ MMA issuer (one thread) ------------------------------
+        };
+        load_item(h_item, h_gs, h_ns);
+        load_item(h_item + (int)gridDim.x, n_gs, n_ns);
+
+        // Software pipeline over the warp's steps, unrolled U times so that every record lives in fixed
+        // registers (a record whose descriptor load is still in flight is never copied): the descriptor
+        // of position i + U is requested while position i is consumed.  One thread per warp works.
         if (lane == 0) {
-            uint32_t ps = 0, cs_base = 0, it = 0;
+            constexpr int U = 4;
+            StepRec rec[U];
+            auto gen = [&](StepRec& r) {  // next step of this warp; requests its descriptor
+                while (h_item < n_items && h_next >= h_st0 + (uint32_t)h_ns) {
+                    h_st0 += (uint32_t)h_ns;
+                    h_item += gridDim.x;
+                    h_gs = n_gs;
+                    h_ns = n_ns;
+                    load_item(h_item + (int)gridDim.x, n_gs, n_ns);
+                }
+                r.live = h_item < n_items;
+                if (r.live) {
+                    r.tile = h_item % n_tiles;
+                    r.st = h_next;
+                    r.d = __ldg(steps + h_gs + (int)(h_next - h_st0));
+                    h_next += NL;
+                }
+            };
+#pragma unroll
+            for (int a = 0; a < U; a++) gen(rec[a]);
+            bool more = true;
+            while (more) {
+#pragma unroll
+                for (int a = 0; a < U; a++) {
+                    StepRec& r = rec[a];
+                    if (!r.live) { more = false; break; }
+                    const uint32_t slot = r.st % S;
+                    wait_bar(empty(slot), ((r.st / S) & 1) ^ 1, abort_addr, status, 1);
+                    const uint32_t stage = base + OFF_STAGE + slot * STAGE_BYTES;
+                    const uint32_t a_bytes = (uint32_t)(__popc(r.d.z) + __popc(r.d.w)) * ABLK_BYTES;
+                    st_shared_u32(base + OFF_META + slot * 8, r.d.z);
+                    st_shared_u32(base + OFF_META + slot * 8 + 4, r.d.w);
+                    mbar_arrive_expect_tx(full(slot), panel_bytes + a_bytes);
+                    tma_load_2d(stage, &mapB, (int)r.d.x, r.tile * NT, full(slot));
+                    bulk_load(stage + PANEL_BYTES, packed + (size_t)r.d.y * ABLK_BYTES, a_bytes, full(slot));
+                    gen(r);  // this register set now follows the warp's step U positions ahead
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp < NL + NM) {
+        // ------------------------------ MMA warp m: accumulators r = m mod NM ------------------------------
+        if (lane == 0) {
+            const int m = warp - NL;
+            const uint32_t rowmask32 =
+                (NM == 16 ? 0x00010001u : NM == 8 ? 0x01010101u : NM == 4 ? 0x11111111u : NM == 2 ? 0x55555555u : ~0u) << m;
+            const uint32_t P_HI = (uint32_t)(smem_desc_k_sw128(0) >> 32), B_HI = (uint32_t)(smem_desc_k_sw32(0) >> 32);
+            uint32_t st = 0, it = 0;
             for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
                 const int g = item / n_tiles;
-                const int r0 = brow_begin + g * RG;
-                const int r1 = min(r0 + RG, brow_end);
-                const int total = __ldg(rowptr + r1) - __ldg(rowptr + r0);
+                const int ns = __ldg(gsp + g + 1) - __ldg(gsp + g);
                 const uint32_t buf = it % NBUF;
                 wait_bar(acc_empty(buf), ((it / NBUF) & 1) ^ 1, abort_addr, status, 3);
                 tc_fence_after();
                 uint32_t started = 0;
-                int a_done = 0;
-                while (a_done < total) {
-                    const uint32_t s = ps % SP;
-                    wait_bar(full_p(s), (ps / SP) & 1, abort_addr, status, 4);
-                    uint32_t mask = ld_shared_u32(base + OFF_META + s * 8);
-                    if (ld_shared_u32(abort_addr)) mask = mask ? mask : 1u;  // guarantee progress after a time-out
+                const uint32_t acc0 = tmem_base + buf * RG * 16;
+                for (int k = 0; k < ns; k++, st++) {
+                    const uint32_t slot = st % S;
+                    wait_bar(full(slot), (st / S) & 1, abort_addr, status, 4);
                     tc_fence_after();
-                    const uint64_t adesc = smem_desc_k_sw32(base + OFF_PANEL + s * PANEL_BYTES);
-                    while (mask && a_done < total) {
-                        const int r = __ffs(mask) - 1;
-                        mask &= mask - 1;
-                        const uint32_t gc = cs_base + (uint32_t)(a_done / CHUNK), slot = gc % SA;
-                        if (a_done % CHUNK == 0) {
-                            wait_bar(full_a(slot), (gc / SA) & 1, abort_addr, status, 5);
-                            tc_fence_after();
+                    const uint32_t mlo = ld_shared_u32(base + OFF_META + slot * 8);
+                    const uint32_t mhi = ld_shared_u32(base + OFF_META + slot * 8 + 4);
+                    const uint32_t stage = base + OFF_STAGE + slot * STAGE_BYTES;
+                    const uint32_t p_lo = (uint32_t)smem_desc_k_sw128(stage);             // panel, sub-column 0
+                    const uint32_t b_lo = (uint32_t)smem_desc_k_sw32(stage + PANEL_BYTES);  // first A block of the step
+                    // mask bit 16 * sub-column + row; q = rank of the bit = slot of the block in the stage
+                    uint32_t qbase = 0;
+#pragma unroll
+                    for (int half = 0; half < 2; half++) {
+                        const uint32_t word = half ? mhi : mlo;
+                        uint32_t mine = word & rowmask32;
+                        while (mine) {
+                            const int b = __ffs(mine) - 1;
+                            mine &= mine - 1;
+                            const uint32_t r = (uint32_t)b & 15u;
+                            const uint32_t q = qbase + __popc(word & ((1u << b) - 1u));
+                            mma_f16_ss_lohi(acc0 + r * 16, p_lo + (uint32_t)(half * 2 + (b >> 4)) * 2u, P_HI, b_lo + q * (ABLK_BYTES >> 4),
+                                            B_HI, IDESC, (started >> r) & 1u);
+                            started |= 1u << r;
                         }
-                        const uint64_t bdesc =
-                            smem_desc_k_sw32(base + OFF_ABLK + (slot * CHUNK + (uint32_t)(a_done % CHUNK)) * ABLK_BYTES);
-                        mma_f16_ss(tmem_base + (buf * RG + (uint32_t)r) * 16, adesc, bdesc, IDESC, (started >> r) & 1u);
-                        started |= 1u << r;
-                        a_done++;
-                        if (a_done % CHUNK == 0 || a_done == total) tc_commit(empty_a(slot));
+                        qbase += __popc(word);
                     }
-                    tc_commit(empty_p(s));
-                    ps++;
+                    tc_commit(empty(slot));
                 }
                 tc_commit(acc_full(buf));
-                cs_base += (uint32_t)((total + CHUNK - 1) / CHUNK);
             }
         }
         __syncwarp();
@@ -244,7 +298,8 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_const
             const int hi = (lane < nrows) ? __ldg(rowptr + r0 + lane + 1) : 0;
             const uint32_t nonempty = __ballot_sync(0xffffffffu, hi > lo);
             const uint32_t buf = it % NBUF;
-            wait_bar(acc_full(buf), (it / NBUF) & 1, abort_addr, status, 6);
+            if (lane == 0) wait_bar(acc_full(buf), (it / NBUF) & 1, abort_addr, status, 6);
+            __syncwarp();
             tc_fence_after();
             const int n = t * NT + quarter * 32 + lane;
             __half* cbase = C + ((size_t)(r0 - brow_begin) * 16 + (odd ? 8 : 0)) * (size_t)N + (size_t)(n & ~1);
@@ -258,7 +313,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_const
                     for (int i = 0; i < 16; i++) v[i] = 0u;
                 }
                 if (r == nrows - 1) {
-                    // every accumulator of this buffer has been read: hand it back to the MMA warp
+                    // every accumulator of this buffer has been read: hand it back to the MMA warps
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(acc_empty(buf));
@@ -278,13 +333,16 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_const
         }
     }
 
+#ifdef SMAT_PROFILE
+    if (threadIdx.x == 0) PROF_ADD(0, clock64() - prof_t0);
+#endif
     tc_fence_before();
     __syncthreads();
     if (ld_shared_u32(abort_addr)) {
         // a wait ran out somewhere: give copies still in flight time to land before the CTA retires
         for (int i = 0; i < 64; i++) __nanosleep(1000);
     }
-    if (warp == 1) {
+    if (warp == NL) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
@@ -298,16 +356,20 @@ __global__ void zero_rows_kernel(uint4* dst, size_t n16) {
 
 }  // namespace
 
-int g_spmm_variant = 0;
+#ifdef SMAT_PROFILE
+extern "C" void smat_prof_read(unsigned long long* out, int reset) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_prof, sizeof(unsigned long long) * 16);
+    if (reset) { unsigned long long z[16] = {}; cudaMemcpyToSymbol(g_prof, z, sizeof(z)); }
+}
+#endif
 
-int launch_spmm(const void* vals, const int* rowptr, const int* colidx, const void* B, void* C, size_t M, size_t N,
-                size_t K, size_t nnzb, size_t brow_begin, size_t brow_end, cudaStream_t stream) {
+int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStream_t stream) {
     DeviceCtx* ctx = nullptr;
     if (int rc = get_device_ctx(&ctx)) return rc;
-    const size_t nb_rows = brow_end - brow_begin;
+    const size_t nb_rows = plan.brow_end - plan.brow_begin;
     if (nb_rows == 0 || N == 0) return SMAT_OK;
-    (void)M;
-    if (nnzb == 0) {
+    if (plan.nnzb == 0) {
         const size_t n16 = nb_rows * 16 * N * 2 / 16;
         zero_rows_kernel<<<ctx->sm_count * 4, 256, 0, stream>>>(reinterpret_cast<uint4*>(C), n16);
         count_launch();
@@ -315,33 +377,20 @@ int launch_spmm(const void* vals, const int* rowptr, const int* colidx, const vo
         return SMAT_OK;
     }
     const uint32_t panel_rows = (uint32_t)(N < (size_t)NT ? N : (size_t)NT);
-    CUtensorMap mapB, mapA;
-    if (int rc = encode_tensor_map_2d_f16(&mapB, B, K, N, K * 2, 16, panel_rows, 1, 0)) return rc;
-    if (int rc = encode_tensor_map_2d_f16(&mapA, vals, 16, nnzb * 16, 32, 16, 16, 1, 256)) return rc;
-
+    CUtensorMap mapB;
+    if (int rc = encode_tensor_map_2d_f16(&mapB, B, plan.K, N, plan.K * 2, 64, panel_rows, 128, 0)) return rc;
     const int n_tiles = (int)((N + NT - 1) / NT);
-    int variant = g_spmm_variant;
-    if (variant == 0) {
-        const size_t items32 = ((nb_rows + 31) / 32) * (size_t)n_tiles;
-        variant = (items32 >= (size_t)ctx->sm_count && nnzb / (nb_rows ? nb_rows : 1) >= 32) ? 2 : 1;
-    }
-    const int rg = (variant == 2) ? 32 : 16;
-    const size_t n_items = ((nb_rows + rg - 1) / rg) * (size_t)n_tiles;
+    const size_t n_items = plan.n_groups * (size_t)n_tiles;
     if (n_items > (size_t)INT_MAX) return fail(SMAT_ERR_RANGE, "too many work items (%zu)", n_items);
     const int grid = (int)(n_items < (size_t)ctx->sm_count ? n_items : (size_t)ctx->sm_count);
-    const uint32_t panel_bytes = panel_rows * 32u;
-
-    auto launch = [&](auto kernel) -> int {
-        SMAT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
-        kernel<<<grid, kThreads, SMEM_BYTES, stream>>>(mapB, mapA, rowptr, colidx, reinterpret_cast<__half*>(C),
-                                                       (int)brow_begin, (int)brow_end, (int)N, n_tiles, (int)n_items,
-                                                       panel_bytes, ctx->d_status);
-        count_launch();
-        SMAT_CUDA_TRY(cudaGetLastError());
-        return SMAT_OK;
-    };
-    if (variant == 2) return launch(spmm_bcsr_tc_kernel<32, 1>);
-    return launch(spmm_bcsr_tc_kernel<16, 2>);
+    SMAT_CUDA_TRY(cudaFuncSetAttribute(spmm_bcsr_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+    spmm_bcsr_tc_kernel<<<grid, kThreads, SMEM_BYTES, stream>>>(
+        mapB, reinterpret_cast<const uint8_t*>(plan.packed), reinterpret_cast<const uint4*>(plan.steps), plan.gsp,
+        plan.rowptr, reinterpret_cast<__half*>(C), (int)plan.brow_begin, (int)plan.brow_end, (int)N, n_tiles, (int)n_items,
+        panel_rows * 128u, ctx->d_status);
+    count_launch();
+    SMAT_CUDA_TRY(cudaGetLastError());
+    return SMAT_OK;
 }
 
 }  // namespace smat

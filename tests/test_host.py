@@ -43,7 +43,6 @@ def test_bad_arguments_are_reported():
     assert L.smat_spmm_bcsr_f16(None, None, None, None, None, 17, 8, 16, 0, None, None, None) == -1
     assert b"multiples of 16" in L.smat_last_error_string()
     assert L.smat_spmm_bcsr_f16(None, None, None, None, None, 16, 7, 16, 0, None, None, None) == -1
-    assert L.smat_spmm_set_variant(99) == -1
     with pytest.raises(S.SmatError):
         S.read_mtx("/nonexistent/file.mtx")
 

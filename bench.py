@@ -1,0 +1,404 @@
+#!/usr/bin/env python
+"""Benchmark of the block-sparse SpMM hot path:  C = A_blocked x B  on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config NAME] [--impl ours|reference]
+
+One "step" is one multiplication of the whole matrix by a fresh-in-HBM B.  Default workload: the
+second BASELINE configuration ("uniform": n = 65536, 0.1 % density, similarity row reorder, 16x16
+blocking, N = 256).  Prints ONE JSON line.
+
+  value      effective TFLOP/s = 2*16*16*N*nnzb / t with A (blocked + plan), B and C resident in HBM
+  e2e        same metric through the library's plan call with HOST B and C: each step copies B
+             host->device from pinned memory, multiplies, and copies C device->host
+  roofline   algorithmic bytes (or FLOPs) per launch / measured launch time, against the measured peak
+  cpu_baseline  the reference's own CPU blocked multiply (VBR::multiply) on a bounded sample
+With --impl reference the reference's CPU blocked multiply is the thing timed (all host cores, each on
+its own block-row range).  For N > 1 (torchrun) block-rows are partitioned by block count, B is
+replicated, C stays sharded, and there is no collective in the timed region.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "SpMM effective TFLOP/s (nonzero-block FLOPs)"
+
+# DRAM bytes (read + write) per launch of the SpMM kernel from an ncu capture of the same workload
+# (see profiles/): filled per workload, None where no capture exists.
+NCU_TRAFFIC_BYTES = {}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": float(p["hbm_gbs"]), "tflops": float(p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU every 200 ms while active."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.samples, self._stop, self._t = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                f = [x.strip() for x in out.strip().split(",")]
+                if len(f) >= 6:
+                    self.samples.append(f)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        mhz = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for s in self.samples for n, v in zip(names, s[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": statistics.median(mhz) if mhz else None,
+                "sm_max_mhz": float(self.samples[0][1]) if self.samples[0][1].replace(".", "").isdigit() else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def build_problem(name, scale, log):
+    """Seeded synthetic matrix -> (problem, host CSR after the optional row reorder, reorder seconds)."""
+    import smat_b200 as S
+    from smat_b200 import generators as gen
+    t = time.time()
+    p = gen.make_config(name, scale=scale)
+    log(f"generated {p.desc} in {time.time() - t:.1f}s")
+    return p
+
+
+def reorder_if_needed(p, log, perm=None):
+    import smat_b200 as S
+    if not p.reorder:
+        return p.rowptr, p.colidx, p.vals, 0.0, None
+    t = time.time()
+    if perm is None:
+        _, perm = S.reorder_rows(p.rowptr, p.colidx, tau=0.5, col_block=16, row_block=16, threads=0)
+    secs = time.time() - t
+    rp, ci, v = S.apply_row_permutation(p.rowptr, p.colidx, p.vals, perm)
+    log(f"row reorder (tau 0.5, 16x16, Keeper) in {secs:.1f}s")
+    return rp, ci, v, secs, perm
+
+
+def algorithmic_bytes(bcsr_rowptr, bcsr_colidx, M, N):
+    nnzb = int(bcsr_rowptr[-1])
+    Mb = M // 16
+    distinct_cols = int(np.unique(bcsr_colidx).size)
+    return 512 * nnzb + 4 * nnzb + 4 * (Mb + 1) + 32 * N * distinct_cols + 2 * M * N
+
+
+def cpu_reference_multiply(bvals, brp, bci, B_nk, M, K, N, brow_ranges, threads):
+    """Runs the reference's VBR::multiply (oracle/_ref) -- or the oracle port when the reference
+    library is absent -- on the given block-row ranges, one range per thread.  Returns (seconds, kind,
+    number of blocks multiplied)."""
+    import oracle
+    R = oracle.ref() if oracle.have_ref() else None
+    Bf = np.ascontiguousarray(B_nk.astype(np.float32)).reshape(-1)  # [n][k] == column-major K x N
+    jobs = []
+    for (b0, b1) in brow_ranges:
+        p0, p1 = int(brp[b0]), int(brp[b1])
+        nb = p1 - p0
+        if R is not None:
+            blocks = bvals[p0 * 256:p1 * 256].reshape(nb, 16, 16)
+            mab = np.ascontiguousarray(blocks.transpose(0, 2, 1)).astype(np.float32).reshape(-1)  # column-major blocks
+            jab = (bci[p0:p1] // 16).astype(np.int64)
+            nzc = np.diff(brp[b0:b1 + 1]).astype(np.int64)
+            Cf = np.zeros((b1 - b0) * 16 * N, np.float32)
+            jobs.append((b0, b1, nb, mab if nb else np.zeros(1, np.float32), jab if nb else np.zeros(1, np.int64), nzc, Cf))
+        else:
+            jobs.append((b0, b1, nb))
+    done = []
+
+    def work(job):
+        if R is not None:
+            b0, b1, nb, mab, jab, nzc, Cf = job
+            R.ref_vbr_multiply((b1 - b0) * 16, K, b1 - b0, 16, nzc, jab, mab, nb, 16, Bf, N, Cf)
+        else:
+            b0, b1, nb = job
+            oracle.bcsr_spmm(bvals, brp, bci, B_nk, M, N, K, b0, b1, threads=1)
+        done.append(job[2])
+
+    t = time.time()
+    ths = [threading.Thread(target=work, args=(j,)) for j in jobs[:threads]]
+    for th in ths:
+        th.start()
+    for th in ths:
+        th.join()
+    return time.time() - t, ("reference" if R is not None else "port"), sum(done)
+
+
+def sample_ranges(brp, Mb, target_blocks, parts):
+    """`parts` disjoint contiguous block-row ranges from the start of the matrix, about target_blocks each."""
+    out, b0 = [], 0
+    for _ in range(parts):
+        b1 = b0
+        while b1 < Mb and brp[b1] - brp[b0] < target_blocks:
+            b1 += 1
+        if b1 == b0:
+            break
+        out.append((b0, b1))
+        b0 = b1
+        if b0 >= Mb:
+            break
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="uniform", choices=["band", "uniform", "powerlaw", "clustered", "llm"])
+    ap.add_argument("--scale", type=float, default=1.0)
+    ap.add_argument("--cpu-sample-seconds", type=float, default=15.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    def log(msg):
+        if rank == 0:
+            print(f"[bench] {msg}", file=sys.stderr, flush=True)
+
+    if args.impl == "reference":
+        return run_reference_arm(args, rank, world, log)
+
+    import torch
+    import smat_b200 as S
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    p = build_problem(args.config, args.scale, log)
+    perm = None
+    if p.reorder and world > 1:
+        # rank 0 computes the permutation once; the others receive it
+        t = torch.empty(p.M, dtype=torch.int64, device="cuda")
+        if rank == 0:
+            _, perm0 = S.reorder_rows(p.rowptr, p.colidx, tau=0.5, col_block=16, row_block=16, threads=0)
+            t.copy_(torch.from_numpy(perm0))
+        dist.broadcast(t, 0)
+        perm = t.cpu().numpy()
+    rp, ci, v, reorder_s, perm = reorder_if_needed(p, log, perm)
+
+    t0 = time.time()
+    A = S.SparseMatrix.from_csr(p.M, p.K, rp, ci, v)
+    build_s = time.time() - t0
+    brp_h, bci_h, bv_h = A.host_arrays()
+    Mb = p.M // 16
+    bounds = S.partition_block_rows(brp_h, world)
+    b0, b1 = int(bounds[rank]), int(bounds[rank + 1])
+    my_blocks = int(brp_h[b1] - brp_h[b0])
+    t0 = time.time()
+    plan = S.Plan(A, b0, b1)
+    torch.cuda.synchronize()
+    plan_s = time.time() - t0
+    log(f"M={p.M} K={p.K} N={p.N} nnzb={A.nnzb} (device BCSR build {build_s:.2f}s, plan {plan_s:.2f}s); "
+        f"rank {rank}: block-rows [{b0},{b1}) = {my_blocks} blocks")
+
+    B = S.Matrix.from_host(p.B_nk)
+    Cd = torch.empty(((b1 - b0) * 16, p.N), dtype=torch.float16, device="cuda")
+    N = p.N
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---------------- resident timing: W warm-ups, K steps between two events ----------------
+    for _ in range(args.warmup):
+        plan.spmm(B, Cd)
+    S.api._check(S.lib().smat_device_status(None))
+    barrier()
+    launches0 = S.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        e0.record()
+        for _ in range(args.steps):
+            plan.spmm(B, Cd)
+        e1.record()
+        barrier()
+        ms_total = e0.elapsed_time(e1)
+        launches = S.launch_count() - launches0
+        # keep sampling under load for at least ~1.5 s so that the clock record is meaningful
+        t_end = time.time() + max(0.0, 1.5 - ms_total / 1e3)
+        while time.time() < t_end:
+            plan.spmm(B, Cd)
+        torch.cuda.synchronize()
+    S.api._check(S.lib().smat_device_status(None))
+    ms_step_local = ms_total / args.steps
+    t = torch.tensor([ms_step_local], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item())
+    flops_total = 2.0 * 256.0 * N * A.nnzb
+    value = flops_total / (ms_step * 1e-3) * 1e-12
+
+    # ---------------- end to end: host B in, host C out, every step ----------------
+    B_host = torch.from_numpy(p.B_nk.view(np.int16)).pin_memory()
+    C_host = torch.empty(((b1 - b0) * 16, N), dtype=torch.int16).pin_memory()
+    B_dev = torch.empty((N, p.K), dtype=torch.float16, device="cuda")
+
+    def e2e_step():
+        B_dev.view(torch.int16).copy_(B_host, non_blocking=True)
+        plan.spmm(B_dev, Cd)
+        C_host.copy_(Cd.view(torch.int16), non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e2e_steps = max(3, min(args.steps, 10))
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / e2e_steps], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    e2e_value = flops_total / (e2e_ms * 1e-3) * 1e-12
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    # ---------------- roofline of the SpMM kernel (rank 0's launch) ----------------
+    peaks = load_peaks()
+    bytes_alg = algorithmic_bytes(brp_h[b0:b1 + 1] - brp_h[b0], bci_h[brp_h[b0]:brp_h[b1]], (b1 - b0) * 16, N)
+    flops_rank = 2.0 * 256.0 * N * my_blocks
+    t_hbm = bytes_alg / (peaks["hbm_gbs"] * 1e9)
+    t_tensor = flops_rank / (peaks["tflops"] * 1e12)
+    kernel_s = ms_step_local * 1e-3  # one SpMM launch per step
+    traffic = NCU_TRAFFIC_BYTES.get((args.config, args.scale, world))
+    if t_hbm >= t_tensor:
+        ach = bytes_alg / kernel_s / 1e9
+        roof = {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": round(ach / peaks["hbm_gbs"], 4), "traffic": traffic}
+    else:
+        ach = flops_rank / kernel_s / 1e12
+        roof = {"bound": "tensor", "achieved": round(ach, 1), "peak": peaks["tflops"], "unit": "TFLOP/s",
+                "frac": round(ach / peaks["tflops"], 4), "traffic": traffic}
+    roof.update({"peak_source": peaks["source"], "algorithmic_bytes": int(bytes_alg), "flops": flops_rank,
+                 "t_hbm_ms": round(t_hbm * 1e3, 4), "t_tensor_ms": round(t_tensor * 1e3, 4),
+                 "kernel": "spmm_bcsr_tc_kernel", "kernel_ms": round(ms_step_local, 4)})
+
+    # ---------------- CPU baseline: the reference's blocked multiply on a bounded sample ----------------
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        # calibrate on a small range, then size the sample for the requested seconds
+        cal = sample_ranges(brp_h, Mb, max(64, A.nnzb // 2000), 1)
+        secs, kind, nb = cpu_reference_multiply(bv_h, brp_h, bci_h, p.B_nk, p.M, p.K, N, cal, 1)
+        rate = nb / max(secs, 1e-6)
+        want = int(min(A.nnzb, max(nb, rate * args.cpu_sample_seconds)))
+        rng = sample_ranges(brp_h, Mb, want, 1)
+        secs, kind, nb = cpu_reference_multiply(bv_h, brp_h, bci_h, p.B_nk, p.M, p.K, N, rng, 1)
+        cpu = {"value": round(2.0 * 256.0 * N * nb / secs * 1e-12, 6), "unit": "TFLOP/s", "cores": 1, "kind": kind,
+               "sample": f"block-rows [{rng[0][0]},{rng[0][1]}) = {nb} of {A.nnzb} blocks ({100.0 * nb / A.nnzb:.2f}%), "
+                         f"{secs:.1f}s, VBR::multiply fp32 single thread"}
+
+    out = {
+        "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": f"{args.config}: {p.desc}; 16x16 blocking" + ("; similarity row reorder" if p.reorder else ""),
+                   "M": p.M, "K": p.K, "N": N, "nnzb": A.nnzb, "block_fill": round(len(ci) / (A.nnzb * 256.0), 5),
+                   "parallelism": f"block-rows split by block count over {world} GPU(s), B replicated, C sharded",
+                   "l2": "inputs larger than L2 (A blocks stream from HBM every step)" if A.nnzb * 512 > 130e6
+                   else "inputs fit L2; no flush between steps",
+                   "setup_s": {"reorder": round(reorder_s, 2), "bcsr_build": round(build_s, 3), "plan": round(plan_s, 3)}},
+        "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": int(N * p.K * 2),
+                "d2h_bytes_per_step": int((b1 - b0) * 16 * N * 2), "ms_per_step": round(e2e_ms, 4),
+                "note": "B host->device (pinned) + smat_plan_spmm + C device->host per step; A (blocked) resident"},
+        "gpu_launches": int(launches),
+        "clocks": clocks.summary(),
+        "roofline": roof,
+        "cpu_baseline": cpu,
+    }
+    print(json.dumps(out), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def run_reference_arm(args, rank, world, log):
+    """The reference's CPU blocked multiply (oracle/_ref when built, else the oracle port) on the same
+    workload, all host cores, each step a bounded sample."""
+    if rank != 0:
+        return
+    import oracle
+    import smat_b200 as S
+    p = build_problem(args.config, args.scale, log)
+    rp, ci, v, reorder_s, _ = reorder_if_needed(p, log)
+    brp, bci, bv = oracle.csr_to_bcsr(p.M, p.K, rp, ci, v)
+    nnzb, Mb, N = len(bci), p.M // 16, p.N
+    cores = os.cpu_count() or 1
+    # size one step at roughly 2 s of work per core
+    cal = sample_ranges(brp, Mb, max(64, nnzb // 4000), 1)
+    secs, kind, nb = cpu_reference_multiply(bv, brp, bci, p.B_nk, p.M, p.K, N, cal, 1)
+    per_core = int(max(nb, nb / max(secs, 1e-6) * 2.0))
+    ranges = sample_ranges(brp, Mb, per_core, cores)
+    for _ in range(args.warmup):
+        cpu_reference_multiply(bv, brp, bci, p.B_nk, p.M, p.K, N, ranges, cores)
+    t_tot, blocks = 0.0, 0
+    for _ in range(args.steps):
+        secs, kind, nb = cpu_reference_multiply(bv, brp, bci, p.B_nk, p.M, p.K, N, ranges, cores)
+        t_tot += secs
+        blocks += nb
+    value = 2.0 * 256.0 * N * blocks / t_tot * 1e-12
+    step_blocks = blocks // max(args.steps, 1)
+    sample = (f"{len(ranges)} block-row ranges, {step_blocks} of {nnzb} blocks per step "
+              f"({100.0 * step_blocks / nnzb:.2f}%), VBR::multiply fp32, one range per thread")
+    out = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 6), "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(t_tot / max(args.steps, 1) * 1e3, 3),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32 (CPU)", "data": "synthetic",
+        "config": {"workload": f"{args.config}: {p.desc}; 16x16 blocking" + ("; similarity row reorder" if p.reorder else ""),
+                   "M": p.M, "K": p.K, "N": N, "nnzb": nnzb},
+        "cpu_baseline": {"value": round(value, 6), "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": round(value, 6), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -75,6 +75,12 @@ int smat_plan_set_values(smat_plan* plan, const void* bcsrValuesA, void* stream)
 int smat_plan_spmm(const smat_plan* plan, const void* B, void* C, size_t N, void* stream);
 int smat_plan_destroy(smat_plan* plan);
 
+/* Kernel variant used by every multiplication of this process: 0 = chosen per matrix (default),
+ * 1 = both MMA operands from shared memory (two accumulator buffers, epilogue overlapped),
+ * 2 = B panels copied to tensor memory and read from there (faster main loop, one buffer).
+ * Meant for benchmarks and tests; no counterpart in the reference. */
+int smat_spmm_set_variant(int variant);
+
 /* Synchronises `stream` and reports whether any kernel launched by this library on the current
  * device recorded a device-side error (a bounded wait that ran out).  Clears the device status word.
  * The reference never checks its launches (src/cuda_hgemm/src/mma/mmaCBT.cu:87). */

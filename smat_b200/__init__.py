@@ -21,6 +21,7 @@ from .api import (  # noqa: F401
     partition_block_rows,
     read_mtx,
     reorder_rows,
+    set_variant,
     spmm,
     spmm_rows,
 )

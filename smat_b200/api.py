@@ -36,6 +36,7 @@ def lib():
     L.smat_plan_set_values.argtypes = [vp, vp, vp]
     L.smat_plan_spmm.argtypes = [vp, vp, vp, sz, vp]
     L.smat_plan_destroy.argtypes = [vp]
+    L.smat_spmm_set_variant.argtypes = [C.c_int]
     L.smat_device_status.argtypes = [vp]
     L.smat_launch_count.restype = C.c_longlong
     L.smat_bcsr_count.argtypes = [ip, ip, sz, sz, sz, ip, C.POINTER(sz), vp]
@@ -61,6 +62,11 @@ def _check(rc):
 
 def launch_count():
     return int(lib().smat_launch_count())
+
+
+def set_variant(v):
+    """0 = automatic, 1 = shared-memory-operand kernel, 2 = tensor-memory-operand kernel."""
+    _check(lib().smat_spmm_set_variant(int(v)))
 
 
 def _stream():

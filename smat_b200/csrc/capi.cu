@@ -41,6 +41,12 @@ int get_device_ctx(DeviceCtx** out) {
         if (prop.major != 10)
             return fail(SMAT_ERR_CUDA, "device %d is sm_%d%d; this library holds sm_100a code only", dev, prop.major,
                         prop.minor);
+        // keep stream-ordered scratch (the per-call plans of smat_spmm_bcsr_f16) cached in the pool
+        cudaMemPool_t pool;
+        if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+            unsigned long long keep = ~0ull;
+            cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+        }
         int* st = nullptr;
         SMAT_CUDA_TRY(cudaMalloc(&st, 64));
         SMAT_CUDA_TRY(cudaMemset(st, 0, 64));
@@ -158,6 +164,13 @@ int smat_spmm_bcsr_f16_rows(const void* vals, const int* rowptr, const int* coli
     if (brow_begin > brow_end || brow_end > M / 16)
         return fail(SMAT_ERR_BAD_ARG, "block-row range [%zu, %zu) outside [0, %zu]", brow_begin, brow_end, M / 16);
     return spmm_transient_plan(vals, rowptr, colidx, B, C, N, K, nnzb, brow_begin, brow_end, (cudaStream_t)stream);
+}
+
+int smat_spmm_set_variant(int variant) {
+    clear_error();
+    if (variant < 0 || variant > 2) return fail(SMAT_ERR_BAD_ARG, "unknown SpMM variant %d", variant);
+    g_spmm_variant = variant;
+    return SMAT_OK;
 }
 
 int smat_device_status(void* stream) {

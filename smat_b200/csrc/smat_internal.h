@@ -74,4 +74,7 @@ int pack_values_async(const int* rowptr, const void* vals, const int* blk, void*
 // Launch of the SpMM kernel (spmm_sm100.cu).
 int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStream_t stream);
 
+// 0 = choose per matrix, 1 = shared-memory-operand kernel, 2 = tensor-memory-operand kernel.
+extern int g_spmm_variant;
+
 }  // namespace smat

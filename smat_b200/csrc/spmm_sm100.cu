@@ -55,15 +55,19 @@ namespace {
 
 constexpr int RG = kPlanRowsPerGroup;  // block-rows per work item
 constexpr int CAP = kPlanBlocksPerStep;  // most blocks a step can carry
-constexpr int NBUF = 2;                // accumulator buffers in tensor memory
 constexpr int NL = 4;                  // loader warps
+#ifndef SMAT_L2_PREFETCH
+#define SMAT_L2_PREFETCH 1
+#endif
 #ifndef SMAT_NM
 #define SMAT_NM 16
 #endif
 constexpr int NM = SMAT_NM;            // MMA-issuing warps
 constexpr int S = 7;                   // steps in flight (pipeline stages)
 constexpr int NT = 128;                // columns of C per work item = tensor-memory lanes = MMA M
-constexpr int kThreads = (NL + NM + 4) * 32;
+constexpr int NC = 4;                  // panel-copier warps (used by the tensor-memory-operand variant)
+constexpr int kThreads = (NL + NC + NM + 4) * 32;
+constexpr uint32_t TMEM_PANELS = 256;  // first tensor-memory column of the panel ring (TS variant): S x 32 columns
 constexpr uint32_t PANEL_BYTES = NT * 64 * 2;  // 128 n x 64 k fp16
 constexpr uint32_t ABLK_BYTES = 16 * 16 * 2;
 constexpr uint32_t STAGE_BYTES = PANEL_BYTES + CAP * ABLK_BYTES;
@@ -72,7 +76,7 @@ constexpr long long WAIT_LIMIT = 4000000000LL;  // clock cycles (about two secon
 constexpr uint32_t OFF_STAGE = 0;
 constexpr uint32_t OFF_META = OFF_STAGE + S * STAGE_BYTES;
 constexpr uint32_t OFF_BAR = OFF_META + S * 8;
-constexpr uint32_t N_BARS = 2 * S + 4;
+constexpr uint32_t N_BARS = 3 * S + 4;
 constexpr uint32_t OFF_MISC = OFF_BAR + N_BARS * 8;
 constexpr uint32_t SMEM_USED = OFF_MISC + 16;
 constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;  // slack for the manual 1024-byte alignment
@@ -80,7 +84,7 @@ constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;  // slack for the manual 1024-
 constexpr uint32_t IDESC = idesc_f16_f32(128, 16);
 
 static_assert(RG == 16, "row masks and accumulator ownership below assume 16 block-rows per group");
-static_assert(RG * NBUF * 16 <= 512, "accumulators must fit the 512 tensor-memory columns");
+static_assert(RG * 2 * 16 <= 512 && TMEM_PANELS + S * 32 <= 512, "tensor-memory budget");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 static_assert(STAGE_BYTES % 1024 == 0 && CAP <= 32, "stage alignment / one block index per lane");
 
@@ -93,6 +97,9 @@ __device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
     asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 
+#ifdef SMAT_PROFILE2
+__device__ long long g_prof2[8];
+#endif
 #ifdef SMAT_PROFILE
 __device__ unsigned long long g_prof[16];
 #define PROF_ADD(code, t) atomicAdd(&g_prof[code], (unsigned long long)(t))
@@ -135,6 +142,13 @@ struct StepRec {
     uint4 d;      // {element column of the quad, first packed block, mask bits 0..31, mask bits 32..63}
 };
 
+// TS = false: both MMA operands from shared memory, two accumulator buffers (the epilogue of an item
+//   overlaps the main loop of the next).
+// TS = true: the panel is first copied shared -> tensor memory (tcgen05.cp, once per sub-column) and the
+//   MMAs read it from there, so the 4 KB panel no longer crosses the shared-memory port once per block
+//   (measured: ~16 instead of ~42 cycles per N=16 MMA per SM); the panel ring takes the tensor-memory
+//   columns of the second accumulator buffer, so there is one buffer and no epilogue overlap.
+template <bool TS>
 __global__ void __launch_bounds__(kThreads, 1)
 spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __restrict__ packed,
                     const uint4* __restrict__ steps, const int* __restrict__ gsp,
@@ -145,8 +159,10 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
     const uint32_t bar0 = base + OFF_BAR;
     auto full = [&](uint32_t s) { return bar0 + 8 * s; };
     auto empty = [&](uint32_t s) { return bar0 + 8 * (S + s); };
-    auto acc_full = [&](uint32_t b) { return bar0 + 8 * (2 * S + b); };
-    auto acc_empty = [&](uint32_t b) { return bar0 + 8 * (2 * S + 2 + b); };
+    auto tfull = [&](uint32_t s) { return bar0 + 8 * (2 * S + s); };
+    auto acc_full = [&](uint32_t b) { return bar0 + 8 * (3 * S + b); };
+    auto acc_empty = [&](uint32_t b) { return bar0 + 8 * (3 * S + 2 + b); };
+    constexpr uint32_t NBUF = TS ? 1 : 2;
     const uint32_t tmem_slot = base + OFF_MISC;
     const uint32_t abort_addr = base + OFF_MISC + 4;
 
@@ -157,7 +173,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
 #endif
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < S; s++) { mbar_init(full(s), 1); mbar_init(empty(s), NM); }
+        for (uint32_t s = 0; s < S; s++) { mbar_init(full(s), 1); mbar_init(empty(s), NM); mbar_init(tfull(s), 1); }
         for (uint32_t b = 0; b < 2; b++) { mbar_init(acc_full(b), NM); mbar_init(acc_empty(b), 4); }
         st_shared_u32(abort_addr, 0);
         fence_barrier_init();
@@ -197,7 +213,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
         // registers (a record whose descriptor load is still in flight is never copied): the descriptor
         // of position i + U is requested while position i is consumed.  One thread per warp works.
         if (lane == 0) {
-            constexpr int U = 4;
+            constexpr int U = 8;
             StepRec rec[U];
             auto gen = [&](StepRec& r) {  // next step of this warp; requests its descriptor
                 while (h_item < n_items && h_next >= h_st0 + (uint32_t)h_ns) {
@@ -215,14 +231,28 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                     h_next += NL;
                 }
             };
+            // HBM latency is hidden in L2 rather than in shared memory: the panel and the blocks of the
+            // step U/2 positions ahead (of this warp; NL * U/2 steps ahead overall) are prefetched into
+            // L2, so the copies that fill a stage find their data there.
+            auto prefetch = [&](const StepRec& r) {
+#if SMAT_L2_PREFETCH
+                if (r.live) {
+                    tma_prefetch_l2_2d(&mapB, (int)r.d.x, r.tile * NT);
+                    bulk_prefetch_l2(packed + (size_t)r.d.y * ABLK_BYTES, (uint32_t)(__popc(r.d.z) + __popc(r.d.w)) * ABLK_BYTES);
+                }
+#endif
+            };
 #pragma unroll
             for (int a = 0; a < U; a++) gen(rec[a]);
+#pragma unroll
+            for (int a = 0; a < U / 2; a++) prefetch(rec[a]);
             bool more = true;
             while (more) {
 #pragma unroll
                 for (int a = 0; a < U; a++) {
                     StepRec& r = rec[a];
                     if (!r.live) { more = false; break; }
+                    prefetch(rec[(a + U / 2) % U]);
                     const uint32_t slot = r.st % S;
                     wait_bar(empty(slot), ((r.st / S) & 1) ^ 1, abort_addr, status, 1);
                     const uint32_t stage = base + OFF_STAGE + slot * STAGE_BYTES;
@@ -237,14 +267,46 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
             }
         }
         __syncwarp();
-    } else if (warp < NL + NM) {
+    } else if (warp < NL + NC) {
+        // ------------------------------ panel copier j (TS only): shared -> tensor memory, every NC-th step ------------------------------
+        if (TS && lane == 0) {
+            const uint32_t j = (uint32_t)(warp - NL);
+            uint32_t st = 0;
+            for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+                const int g = item / n_tiles;
+                const int ns = __ldg(gsp + g + 1) - __ldg(gsp + g);
+                for (int k = 0; k < ns; k++, st++) {
+                    const uint32_t slot = st % S;
+                    // Every copier observes every stage in order, although it copies only its own: a
+                    // parity wait is only meaningful for a waiter that is less than one phase away, and
+                    // a copier that skipped stages could meet a barrier one whole use behind.
+                    wait_bar(full(slot), (st / S) & 1, abort_addr, status, 2);
+                    if (st % NC != j) continue;
+                    tc_fence_after();
+                    const uint32_t mlo = ld_shared_u32(base + OFF_META + slot * 8);
+                    const uint32_t mhi = ld_shared_u32(base + OFF_META + slot * 8 + 4);
+                    const uint64_t pdesc = smem_desc_k_sw128(base + OFF_STAGE + slot * STAGE_BYTES);
+                    const uint32_t tdst = tmem_base + TMEM_PANELS + slot * 32;
+                    if (mlo & 0xffffu) tc_cp_128x256b(tdst, pdesc);
+                    if (mlo >> 16) tc_cp_128x256b(tdst + 8, pdesc + 2);
+                    if (mhi & 0xffffu) tc_cp_128x256b(tdst + 16, pdesc + 4);
+                    if (mhi >> 16) tc_cp_128x256b(tdst + 24, pdesc + 6);
+                    tc_commit(tfull(slot));
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp < NL + NC + NM) {
         // ------------------------------ MMA warp m: accumulators r = m mod NM ------------------------------
         if (lane == 0) {
-            const int m = warp - NL;
+            const int m = warp - NL - NC;
             const uint32_t rowmask32 =
                 (NM == 16 ? 0x00010001u : NM == 8 ? 0x01010101u : NM == 4 ? 0x11111111u : NM == 2 ? 0x55555555u : ~0u) << m;
             const uint32_t P_HI = (uint32_t)(smem_desc_k_sw128(0) >> 32), B_HI = (uint32_t)(smem_desc_k_sw32(0) >> 32);
             uint32_t st = 0, it = 0;
+#ifdef SMAT_PROFILE2
+            long long pw = 0, ps = 0, pm = 0, pc = 0, pn = 0, pmm = 0;
+#endif
             for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
                 const int g = item / n_tiles;
                 const int ns = __ldg(gsp + g + 1) - __ldg(gsp + g);
@@ -255,15 +317,26 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                 const uint32_t acc0 = tmem_base + buf * RG * 16;
                 for (int k = 0; k < ns; k++, st++) {
                     const uint32_t slot = st % S;
-                    wait_bar(full(slot), (st / S) & 1, abort_addr, status, 4);
+#ifdef SMAT_PROFILE2
+                    const long long q0 = clock64();
+#endif
+                    wait_bar(TS ? tfull(slot) : full(slot), (st / S) & 1, abort_addr, status, 4);
+#ifdef SMAT_PROFILE2
+                    const long long q1 = clock64();
+#endif
                     tc_fence_after();
                     const uint32_t mlo = ld_shared_u32(base + OFF_META + slot * 8);
                     const uint32_t mhi = ld_shared_u32(base + OFF_META + slot * 8 + 4);
                     const uint32_t stage = base + OFF_STAGE + slot * STAGE_BYTES;
                     const uint32_t p_lo = (uint32_t)smem_desc_k_sw128(stage);             // panel, sub-column 0
+                    const uint32_t tpanel = tmem_base + TMEM_PANELS + slot * 32;          // its copy in tensor memory
                     const uint32_t b_lo = (uint32_t)smem_desc_k_sw32(stage + PANEL_BYTES);  // first A block of the step
                     // mask bit 16 * sub-column + row; q = rank of the bit = slot of the block in the stage
                     uint32_t qbase = 0;
+#ifdef SMAT_PROFILE2
+                    const long long q2 = clock64();
+                    pmm += __popc(mlo & rowmask32) + __popc(mhi & rowmask32);
+#endif
 #pragma unroll
                     for (int half = 0; half < 2; half++) {
                         const uint32_t word = half ? mhi : mlo;
@@ -273,16 +346,32 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                             mine &= mine - 1;
                             const uint32_t r = (uint32_t)b & 15u;
                             const uint32_t q = qbase + __popc(word & ((1u << b) - 1u));
-                            mma_f16_ss_lohi(acc0 + r * 16, p_lo + (uint32_t)(half * 2 + (b >> 4)) * 2u, P_HI, b_lo + q * (ABLK_BYTES >> 4),
-                                            B_HI, IDESC, (started >> r) & 1u);
+                            if (TS)
+                                mma_f16_ts_lohi(acc0 + r * 16, tpanel + (uint32_t)(half * 2 + (b >> 4)) * 8u,
+                                                b_lo + q * (ABLK_BYTES >> 4), B_HI, IDESC, (started >> r) & 1u);
+                            else
+                                mma_f16_ss_lohi(acc0 + r * 16, p_lo + (uint32_t)(half * 2 + (b >> 4)) * 2u, P_HI,
+                                                b_lo + q * (ABLK_BYTES >> 4), B_HI, IDESC, (started >> r) & 1u);
                             started |= 1u << r;
                         }
                         qbase += __popc(word);
                     }
+#ifdef SMAT_PROFILE2
+                    const long long q3 = clock64();
+#endif
                     tc_commit(empty(slot));
+#ifdef SMAT_PROFILE2
+                    const long long q4 = clock64();
+                    pw += q1 - q0; ps += q2 - q1; pm += q3 - q2; pc += q4 - q3; pn++;
+#endif
                 }
                 tc_commit(acc_full(buf));
             }
+#ifdef SMAT_PROFILE2
+            if (blockIdx.x == 0 && m == 0) {
+                g_prof2[0] = pw; g_prof2[1] = ps; g_prof2[2] = pm; g_prof2[3] = pc; g_prof2[4] = pn; g_prof2[5] = pmm;
+            }
+#endif
         }
         __syncwarp();
     } else {
@@ -356,6 +445,12 @@ __global__ void zero_rows_kernel(uint4* dst, size_t n16) {
 
 }  // namespace
 
+#ifdef SMAT_PROFILE2
+extern "C" void smat_prof2_read(long long* out) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_prof2, sizeof(long long) * 8);
+}
+#endif
 #ifdef SMAT_PROFILE
 extern "C" void smat_prof_read(unsigned long long* out, int reset) {
     cudaDeviceSynchronize();
@@ -363,6 +458,8 @@ extern "C" void smat_prof_read(unsigned long long* out, int reset) {
     if (reset) { unsigned long long z[16] = {}; cudaMemcpyToSymbol(g_prof, z, sizeof(z)); }
 }
 #endif
+
+int g_spmm_variant = 0;
 
 int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStream_t stream) {
     DeviceCtx* ctx = nullptr;
@@ -383,14 +480,22 @@ int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStre
     const size_t n_items = plan.n_groups * (size_t)n_tiles;
     if (n_items > (size_t)INT_MAX) return fail(SMAT_ERR_RANGE, "too many work items (%zu)", n_items);
     const int grid = (int)(n_items < (size_t)ctx->sm_count ? n_items : (size_t)ctx->sm_count);
-    SMAT_CUDA_TRY(cudaFuncSetAttribute(spmm_bcsr_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
-    spmm_bcsr_tc_kernel<<<grid, kThreads, SMEM_BYTES, stream>>>(
-        mapB, reinterpret_cast<const uint8_t*>(plan.packed), reinterpret_cast<const uint4*>(plan.steps), plan.gsp,
-        plan.rowptr, reinterpret_cast<__half*>(C), (int)plan.brow_begin, (int)plan.brow_end, (int)N, n_tiles, (int)n_items,
-        panel_rows * 128u, ctx->d_status);
-    count_launch();
-    SMAT_CUDA_TRY(cudaGetLastError());
-    return SMAT_OK;
+    // Measured on the benchmark matrices the two variants are within a few percent of each other (the
+    // main loop is bound by MMA issue and per-step hand-over, not by the shared-memory port), so the
+    // two-buffer shared-memory-operand kernel, which also overlaps the epilogue, is the default.
+    int variant = g_spmm_variant;
+    if (variant == 0) variant = 1;
+    auto launch = [&](auto kernel) -> int {
+        SMAT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+        kernel<<<grid, kThreads, SMEM_BYTES, stream>>>(
+            mapB, reinterpret_cast<const uint8_t*>(plan.packed), reinterpret_cast<const uint4*>(plan.steps), plan.gsp,
+            plan.rowptr, reinterpret_cast<__half*>(C), (int)plan.brow_begin, (int)plan.brow_end, (int)N, n_tiles,
+            (int)n_items, panel_rows * 128u, ctx->d_status);
+        count_launch();
+        SMAT_CUDA_TRY(cudaGetLastError());
+        return SMAT_OK;
+    };
+    return variant == 2 ? launch(spmm_bcsr_tc_kernel<true>) : launch(spmm_bcsr_tc_kernel<false>);
 }
 
 }  // namespace smat

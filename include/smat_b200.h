@@ -77,7 +77,8 @@ int smat_plan_destroy(smat_plan* plan);
 
 /* Kernel variant used by every multiplication of this process: 0 = chosen per matrix (default),
  * 1 = both MMA operands from shared memory (two accumulator buffers, epilogue overlapped),
- * 2 = B panels copied to tensor memory and read from there (faster main loop, one buffer).
+ * 2 = B panels copied to tensor memory and read from there (one accumulator buffer),
+ * 3 = work items 256 columns of C wide: two MMAs per block, one accumulator buffer (default for N >= 256).
  * Meant for benchmarks and tests; no counterpart in the reference. */
 int smat_spmm_set_variant(int variant);
 

@@ -95,7 +95,7 @@ int encode_tensor_map_2d_f16(CUtensorMap* map, const void* base, uint64_t inner,
     return SMAT_OK;
 }
 
-static int check_spmm_args(const void* vals, const int* rowptr, const int* colidx, const void* B, const void* C, size_t M,
+int check_spmm_args(const void* vals, const int* rowptr, const int* colidx, const void* B, const void* C, size_t M,
                            size_t N, size_t K, size_t nnzb) {
     if (M % 16 || K % 16) return fail(SMAT_ERR_BAD_ARG, "M (%zu) and K (%zu) must be multiples of 16", M, K);
     if (N % 8) return fail(SMAT_ERR_BAD_ARG, "N (%zu) must be a multiple of 8", N);
@@ -168,7 +168,7 @@ int smat_spmm_bcsr_f16_rows(const void* vals, const int* rowptr, const int* coli
 
 int smat_spmm_set_variant(int variant) {
     clear_error();
-    if (variant < 0 || variant > 2) return fail(SMAT_ERR_BAD_ARG, "unknown SpMM variant %d", variant);
+    if (variant < 0 || variant > 3) return fail(SMAT_ERR_BAD_ARG, "unknown SpMM variant %d", variant);
     g_spmm_variant = variant;
     return SMAT_OK;
 }

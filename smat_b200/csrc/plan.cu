@@ -202,10 +202,14 @@ __global__ void __launch_bounds__(256) pack_kernel(const uint4* __restrict__ val
 }  // namespace
 
 int pack_values_async(const int* rowptr, const void* vals, const int* blk, void* packed, size_t brow_begin,
-                      size_t brow_end, size_t nnzb, cudaStream_t stream) {
+                      size_t brow_end, size_t nnzb, cudaStream_t stream, const DeviceCtx* ctx_in) {
     if (nnzb == 0 || brow_end == brow_begin) return SMAT_OK;
-    DeviceCtx* ctx = nullptr;
-    if (int rc = get_device_ctx(&ctx)) return rc;
+    const DeviceCtx* ctx = ctx_in;
+    if (!ctx) {
+        DeviceCtx* c = nullptr;
+        if (int rc = get_device_ctx(&c)) return rc;
+        ctx = c;
+    }
     pack_kernel<<<ctx->sm_count * 8, 256, 0, stream>>>(reinterpret_cast<const uint4*>(vals), blk,
                                                        reinterpret_cast<uint4*>(packed), rowptr, (int)brow_begin,
                                                        (int)brow_end);
@@ -226,9 +230,13 @@ PlanSizes plan_sizes(size_t nnzb, size_t brow_begin, size_t brow_end) {
 }
 
 int build_plan_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
-                     int* gsp, void* steps, int* blk, cudaStream_t stream) {
-    DeviceCtx* ctx = nullptr;
-    if (int rc = get_device_ctx(&ctx)) return rc;
+                     int* gsp, void* steps, int* blk, cudaStream_t stream, const DeviceCtx* ctx_in) {
+    const DeviceCtx* ctx = ctx_in;
+    if (!ctx) {
+        DeviceCtx* c = nullptr;
+        if (int rc = get_device_ctx(&c)) return rc;
+        ctx = c;
+    }
     const size_t n_groups = (brow_end - brow_begin + RG - 1) / RG;
     if (n_groups == 0) return SMAT_OK;
     if (nnzb == 0) {

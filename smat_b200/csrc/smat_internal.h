@@ -9,6 +9,10 @@
 
 namespace smat {
 
+// Argument checks shared by the SpMM entry points (capi.cu).
+int check_spmm_args(const void* vals, const int* rowptr, const int* colidx, const void* B, const void* C, size_t M,
+                    size_t N, size_t K, size_t nnzb);
+
 // Error text of the calling thread; returns `code` so that callers can `return fail(...)`.
 int fail(int code, const char* fmt, ...);
 void clear_error();
@@ -65,16 +69,18 @@ struct PlanView {
 // Work-list sizes for a block-row range and the asynchronous build on `stream` (plan.cu).
 struct PlanSizes { size_t n_groups, gsp_bytes, steps_bytes, blk_bytes, packed_bytes; };
 PlanSizes plan_sizes(size_t nnzb, size_t brow_begin, size_t brow_end);
+// `ctx` (here and below): per-device state to use; nullptr = the lazily created one of get_device_ctx.
 int build_plan_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
-                     int* gsp, void* steps, int* blk, cudaStream_t stream);
+                     int* gsp, void* steps, int* blk, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
 // packed[i] = swizzled copy of value block blk[i] for the blocks of block-rows [brow_begin, brow_end).
 int pack_values_async(const int* rowptr, const void* vals, const int* blk, void* packed, size_t brow_begin,
-                      size_t brow_end, size_t nnzb, cudaStream_t stream);
+                      size_t brow_end, size_t nnzb, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
 
 // Launch of the SpMM kernel (spmm_sm100.cu).
-int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStream_t stream);
+int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStream_t stream,
+                const DeviceCtx* ctx = nullptr);
 
-// 0 = choose per matrix, 1 = shared-memory-operand kernel, 2 = tensor-memory-operand kernel.
+// 0 = choose per call, 1 = shared-memory-operand kernel, 2 = tensor-memory-operand kernel, 3 = 256-column items.
 extern int g_spmm_variant;
 
 }  // namespace smat

@@ -63,30 +63,32 @@ constexpr int NL = 4;                  // loader warps
 #define SMAT_NM 16
 #endif
 constexpr int NM = SMAT_NM;            // MMA-issuing warps
-constexpr int S = 7;                   // steps in flight (pipeline stages)
-constexpr int NT = 128;                // columns of C per work item = tensor-memory lanes = MMA M
 constexpr int NC = 4;                  // panel-copier warps (used by the tensor-memory-operand variant)
 constexpr int kThreads = (NL + NC + NM + 4) * 32;
 constexpr uint32_t TMEM_PANELS = 256;  // first tensor-memory column of the panel ring (TS variant): S x 32 columns
-constexpr uint32_t PANEL_BYTES = NT * 64 * 2;  // 128 n x 64 k fp16
 constexpr uint32_t ABLK_BYTES = 16 * 16 * 2;
-constexpr uint32_t STAGE_BYTES = PANEL_BYTES + CAP * ABLK_BYTES;
 constexpr long long WAIT_LIMIT = 4000000000LL;  // clock cycles (about two seconds)
 
-constexpr uint32_t OFF_STAGE = 0;
-constexpr uint32_t OFF_META = OFF_STAGE + S * STAGE_BYTES;
-constexpr uint32_t OFF_BAR = OFF_META + S * 8;
-constexpr uint32_t N_BARS = 3 * S + 4;
-constexpr uint32_t OFF_MISC = OFF_BAR + N_BARS * 8;
-constexpr uint32_t SMEM_USED = OFF_MISC + 16;
-constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;  // slack for the manual 1024-byte alignment
+// Shared-memory plan of a kernel whose work item is NH x 128 columns of C wide.
+template <int NH>
+struct Cfg {
+    static constexpr uint32_t S = NH == 1 ? 7 : 4;              // steps in flight (pipeline stages)
+    static constexpr uint32_t PANEL_BYTES = NH * 128 * 64 * 2;  // NH x (128 n x 64 k fp16)
+    static constexpr uint32_t STAGE_BYTES = PANEL_BYTES + CAP * ABLK_BYTES;
+    static constexpr uint32_t OFF_STAGE = 0;
+    static constexpr uint32_t OFF_META = OFF_STAGE + S * STAGE_BYTES;
+    static constexpr uint32_t OFF_BAR = OFF_META + S * 8;
+    static constexpr uint32_t N_BARS = 3 * S + 4;
+    static constexpr uint32_t OFF_MISC = OFF_BAR + N_BARS * 8;
+    static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;  // slack for the manual 1024-byte alignment
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+    static_assert(STAGE_BYTES % 1024 == 0 && CAP <= 32, "stage alignment");
+};
 
 constexpr uint32_t IDESC = idesc_f16_f32(128, 16);
 
 static_assert(RG == 16, "row masks and accumulator ownership below assume 16 block-rows per group");
-static_assert(RG * 2 * 16 <= 512 && TMEM_PANELS + S * 32 <= 512, "tensor-memory budget");
-static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
-static_assert(STAGE_BYTES % 1024 == 0 && CAP <= 32, "stage alignment / one block index per lane");
+static_assert(RG * 2 * 16 <= 512 && TMEM_PANELS + Cfg<1>::S * 32 <= 512, "tensor-memory budget");
 
 __device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
     uint32_t v;
@@ -148,12 +150,20 @@ struct StepRec {
 //   MMAs read it from there, so the 4 KB panel no longer crosses the shared-memory port once per block
 //   (measured: ~16 instead of ~42 cycles per N=16 MMA per SM); the panel ring takes the tensor-memory
 //   columns of the second accumulator buffer, so there is one buffer and no epilogue overlap.
-template <bool TS>
+// NH = 1: a work item is 128 columns of C wide.  NH = 2: 256 columns -- every A block then feeds two
+//   independent MMAs (one per 128-column half, own accumulator), which doubles the MMA work per stage
+//   hand-over and halves the A traffic per MMA; the 32 accumulators fill tensor memory (one buffer).
+template <bool TS, int NH>
 __global__ void __launch_bounds__(kThreads, 1)
 spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __restrict__ packed,
                     const uint4* __restrict__ steps, const int* __restrict__ gsp,
                     const int* __restrict__ rowptr, __half* __restrict__ C, int brow_begin, int brow_end, int N,
                     int n_tiles, int n_items, uint32_t panel_bytes, int* status) {
+    static_assert(!(TS && NH == 2), "the panel ring and 32 accumulators do not fit tensor memory together");
+    using G = Cfg<NH>;
+    constexpr uint32_t S = G::S, PANEL_BYTES = G::PANEL_BYTES, STAGE_BYTES = G::STAGE_BYTES, OFF_STAGE = G::OFF_STAGE,
+                       OFF_META = G::OFF_META, OFF_BAR = G::OFF_BAR, OFF_MISC = G::OFF_MISC;
+    constexpr int NT = 128 * NH;  // columns of C per work item
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar0 = base + OFF_BAR;
@@ -162,7 +172,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
     auto tfull = [&](uint32_t s) { return bar0 + 8 * (2 * S + s); };
     auto acc_full = [&](uint32_t b) { return bar0 + 8 * (3 * S + b); };
     auto acc_empty = [&](uint32_t b) { return bar0 + 8 * (3 * S + 2 + b); };
-    constexpr uint32_t NBUF = TS ? 1 : 2;
+    constexpr uint32_t NBUF = (TS || NH == 2) ? 1 : 2;
     const uint32_t tmem_slot = base + OFF_MISC;
     const uint32_t abort_addr = base + OFF_MISC + 4;
 
@@ -314,7 +324,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                 wait_bar(acc_empty(buf), ((it / NBUF) & 1) ^ 1, abort_addr, status, 3);
                 tc_fence_after();
                 uint32_t started = 0;
-                const uint32_t acc0 = tmem_base + buf * RG * 16;
+                const uint32_t acc0 = tmem_base + buf * RG * 16 * NH;
                 for (int k = 0; k < ns; k++, st++) {
                     const uint32_t slot = st % S;
 #ifdef SMAT_PROFILE2
@@ -346,12 +356,16 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                             mine &= mine - 1;
                             const uint32_t r = (uint32_t)b & 15u;
                             const uint32_t q = qbase + __popc(word & ((1u << b) - 1u));
-                            if (TS)
+                            if (TS) {
                                 mma_f16_ts_lohi(acc0 + r * 16, tpanel + (uint32_t)(half * 2 + (b >> 4)) * 8u,
                                                 b_lo + q * (ABLK_BYTES >> 4), B_HI, IDESC, (started >> r) & 1u);
-                            else
-                                mma_f16_ss_lohi(acc0 + r * 16, p_lo + (uint32_t)(half * 2 + (b >> 4)) * 2u, P_HI,
-                                                b_lo + q * (ABLK_BYTES >> 4), B_HI, IDESC, (started >> r) & 1u);
+                            } else {
+#pragma unroll
+                                for (int h = 0; h < NH; h++)  // one MMA per 128-column half, each into its own accumulator
+                                    mma_f16_ss_lohi(acc0 + (r * NH + h) * 16,
+                                                    p_lo + (uint32_t)(half * 2 + (b >> 4)) * 2u + h * (128 * 128 >> 4), P_HI,
+                                                    b_lo + q * (ABLK_BYTES >> 4), B_HI, IDESC, (started >> r) & 1u);
+                            }
                             started |= 1u << r;
                         }
                         qbase += __popc(word);
@@ -390,33 +404,35 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
             if (lane == 0) wait_bar(acc_full(buf), (it / NBUF) & 1, abort_addr, status, 6);
             __syncwarp();
             tc_fence_after();
-            const int n = t * NT + quarter * 32 + lane;
-            __half* cbase = C + ((size_t)(r0 - brow_begin) * 16 + (odd ? 8 : 0)) * (size_t)N + (size_t)(n & ~1);
             for (int r = 0; r < nrows; r++) {
-                uint32_t v[16];
-                if ((nonempty >> r) & 1u) {
-                    tmem_ld_x16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (buf * RG + (uint32_t)r) * 16, v);
-                    tmem_ld_wait();
-                } else {
 #pragma unroll
-                    for (int i = 0; i < 16; i++) v[i] = 0u;
-                }
-                if (r == nrows - 1) {
-                    // every accumulator of this buffer has been read: hand it back to the MMA warps
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(acc_empty(buf));
-                }
-                __half* crow = cbase + (size_t)r * 16 * (size_t)N;
+                for (int h = 0; h < NH; h++) {
+                    const int n = t * NT + h * 128 + quarter * 32 + lane;
+                    uint32_t v[16];
+                    if ((nonempty >> r) & 1u) {
+                        tmem_ld_x16(tmem_base + ((uint32_t)(quarter * 32) << 16) + ((buf * RG + (uint32_t)r) * NH + h) * 16, v);
+                        tmem_ld_wait();
+                    } else {
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    // lane pairs exchange halves: even lanes keep rows 0..7, odd lanes rows 8..15,
-                    // each for the two adjacent columns (n & ~1, n | 1) -> one 4-byte store per row
-                    const float keep = __uint_as_float(odd ? v[i + 8] : v[i]);
-                    const float send = __uint_as_float(odd ? v[i] : v[i + 8]);
-                    const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
-                    const __half2 h = odd ? __floats2half2_rn(recv, keep) : __floats2half2_rn(keep, recv);
-                    if (n < N) *reinterpret_cast<__half2*>(crow + (size_t)i * (size_t)N) = h;
+                        for (int i = 0; i < 16; i++) v[i] = 0u;
+                    }
+                    if (r == nrows - 1 && h == NH - 1) {
+                        // every accumulator of this buffer has been read: hand it back to the MMA warps
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acc_empty(buf));
+                    }
+                    __half* crow = C + ((size_t)(r0 - brow_begin + r) * 16 + (odd ? 8 : 0)) * (size_t)N + (size_t)(n & ~1);
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        // lane pairs exchange halves: even lanes keep rows 0..7, odd lanes rows 8..15,
+                        // each for the two adjacent columns (n & ~1, n | 1) -> one 4-byte store per row
+                        const float keep = __uint_as_float(odd ? v[i + 8] : v[i]);
+                        const float send = __uint_as_float(odd ? v[i] : v[i + 8]);
+                        const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+                        const __half2 hh = odd ? __floats2half2_rn(recv, keep) : __floats2half2_rn(keep, recv);
+                        if (n < N) *reinterpret_cast<__half2*>(crow + (size_t)i * (size_t)N) = hh;
+                    }
                 }
             }
         }
@@ -461,9 +477,13 @@ extern "C" void smat_prof_read(unsigned long long* out, int reset) {
 
 int g_spmm_variant = 0;
 
-int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStream_t stream) {
-    DeviceCtx* ctx = nullptr;
-    if (int rc = get_device_ctx(&ctx)) return rc;
+int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStream_t stream, const DeviceCtx* ctx_in) {
+    const DeviceCtx* ctx = ctx_in;
+    if (!ctx) {
+        DeviceCtx* c = nullptr;
+        if (int rc = get_device_ctx(&c)) return rc;
+        ctx = c;
+    }
     const size_t nb_rows = plan.brow_end - plan.brow_begin;
     if (nb_rows == 0 || N == 0) return SMAT_OK;
     if (plan.nnzb == 0) {
@@ -473,21 +493,20 @@ int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStre
         SMAT_CUDA_TRY(cudaGetLastError());
         return SMAT_OK;
     }
-    const uint32_t panel_rows = (uint32_t)(N < (size_t)NT ? N : (size_t)NT);
+    // Item width: 256 columns when C is at least that wide (every A block then feeds two MMAs), else 128.
+    int variant = g_spmm_variant;
+    if (variant == 0) variant = N >= 256 ? 3 : 1;
+    const size_t NTI = variant == 3 ? 256 : 128;
+    const uint32_t panel_rows = (uint32_t)(N < NTI ? N : NTI);
     CUtensorMap mapB;
     if (int rc = encode_tensor_map_2d_f16(&mapB, B, plan.K, N, plan.K * 2, 64, panel_rows, 128, 0)) return rc;
-    const int n_tiles = (int)((N + NT - 1) / NT);
+    const int n_tiles = (int)((N + NTI - 1) / NTI);
     const size_t n_items = plan.n_groups * (size_t)n_tiles;
     if (n_items > (size_t)INT_MAX) return fail(SMAT_ERR_RANGE, "too many work items (%zu)", n_items);
     const int grid = (int)(n_items < (size_t)ctx->sm_count ? n_items : (size_t)ctx->sm_count);
-    // Measured on the benchmark matrices the two variants are within a few percent of each other (the
-    // main loop is bound by MMA issue and per-step hand-over, not by the shared-memory port), so the
-    // two-buffer shared-memory-operand kernel, which also overlaps the epilogue, is the default.
-    int variant = g_spmm_variant;
-    if (variant == 0) variant = 1;
-    auto launch = [&](auto kernel) -> int {
-        SMAT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
-        kernel<<<grid, kThreads, SMEM_BYTES, stream>>>(
+    auto launch = [&](auto kernel, uint32_t smem_bytes) -> int {
+        SMAT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+        kernel<<<grid, kThreads, smem_bytes, stream>>>(
             mapB, reinterpret_cast<const uint8_t*>(plan.packed), reinterpret_cast<const uint4*>(plan.steps), plan.gsp,
             plan.rowptr, reinterpret_cast<__half*>(C), (int)plan.brow_begin, (int)plan.brow_end, (int)N, n_tiles,
             (int)n_items, panel_rows * 128u, ctx->d_status);
@@ -495,7 +514,9 @@ int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStre
         SMAT_CUDA_TRY(cudaGetLastError());
         return SMAT_OK;
     };
-    return variant == 2 ? launch(spmm_bcsr_tc_kernel<true>) : launch(spmm_bcsr_tc_kernel<false>);
+    if (variant == 3) return launch(spmm_bcsr_tc_kernel<false, 2>, Cfg<2>::SMEM_BYTES);
+    if (variant == 2) return launch(spmm_bcsr_tc_kernel<true, 1>, Cfg<1>::SMEM_BYTES);
+    return launch(spmm_bcsr_tc_kernel<false, 1>, Cfg<1>::SMEM_BYTES);
 }
 
 }  // namespace smat

@@ -39,7 +39,7 @@ def _run(brp, bci, bv, B_nk, M, N, K, variant="call"):
     A = S.SparseMatrix.from_bcsr(M, K, brp, bci, bv)
     B = S.Matrix.from_host(B_nk)
     C = S.Matrix(M, N, fill=float("nan"))
-    kernel = {"smem": 1, "tmem": 2}.get(variant, 0)  # force one kernel variant, else automatic choice
+    kernel = {"smem": 1, "tmem": 2, "wide": 3}.get(variant, 0)  # force one kernel variant, else automatic choice
     S.set_variant(kernel)
     try:
         if variant == "call":
@@ -63,7 +63,7 @@ def _problem(name, scale, N=None):
     return p, brp, bci, bv
 
 
-@pytest.mark.parametrize("variant", ["call", "plan", "smem", "tmem"])
+@pytest.mark.parametrize("variant", ["call", "plan", "smem", "tmem", "wide"])
 @pytest.mark.parametrize("name,scale,N", [("band", 1.0, 64), ("band", 0.1, 8), ("uniform", 0.02, 256),
                                           ("uniform", 0.01, 136), ("powerlaw", 0.01, 128), ("clustered", 0.004, 512),
                                           ("llm", 0.0625, 256), ("llm", 0.04, 24)])
@@ -139,7 +139,7 @@ def test_ragged_rows_and_long_block_row():
     bci = np.concatenate([np.sort(rng.choice(Kb, c, replace=False)) for c in counts]).astype(np.int32) * 16
     bv = rng.standard_normal(brp[-1] * 256).astype(np.float16)
     B = rng.standard_normal((N, Kb * 16)).astype(np.float16)
-    for variant in ("call", "smem", "tmem"):
+    for variant in ("call", "smem", "tmem", "wide"):
         C = _run(brp, bci, bv, B, Mb * 16, N, Kb * 16, variant)
         Cref, Cabs = _oracle_c(bv, brp, bci, B, Mb * 16, N, Kb * 16)
         assert _rel_err(C, Cref, Cabs) <= TOL

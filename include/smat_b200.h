@@ -55,6 +55,22 @@ int smat_spmm_bcsr_f16_rows(const void* bcsrValuesA, const int* bcsrRowPtrA, con
                             void* C, size_t M, size_t N, size_t K, size_t nonzeroBlocks, size_t brow_begin,
                             size_t brow_end, void* stream);
 
+/* Same product as smat_spmm_bcsr_f16 for callers that may not allocate device memory (fixed-budget
+ * serving loops, callbacks that run while the allocator is locked, processes that gave their free
+ * memory to a foreign pool): the per-call plan is built in a fixed array inside the library image
+ * instead of freshly allocated scratch, so the call performs no allocation and no free.
+ * No counterpart in the reference (its launcher needs no scratch, mmaCBT.cu:83-88).
+ * Limits: nonzeroBlocks <= SMAT_STATIC_MAX_BLOCKS and M <= SMAT_STATIC_MAX_ROWS, else SMAT_ERR_RANGE;
+ * the array (about 17 MB) stays resident on every GPU that loads the library.
+ * All calls on a device share the array: calls that overlap on the GPU race; calls on one stream do
+ * not.  The first call on a device also looks up the array's device address -- make it before
+ * starting a stream capture.  Bounded-wait time-outs are recorded in the array, not in the word
+ * smat_device_status reads. */
+#define SMAT_STATIC_MAX_BLOCKS 32768
+#define SMAT_STATIC_MAX_ROWS 1048576
+int smat_spmm_bcsr_f16_static(const void* bcsrValuesA, const int* bcsrRowPtrA, const int* bcsrColIdxA, const void* B,
+                              void* C, size_t M, size_t N, size_t K, size_t nonzeroBlocks, void* stream);
+
 /* Multiplication plan: what the kernel needs beyond the BCSR arrays, computed on the device and
  * reusable for any number of multiplications:
  *   - the walk order (per group of 16 block-rows, its block-columns four at a time in ascending

@@ -32,6 +32,7 @@ def lib():
     vp, sz, ip = C.c_void_p, C.c_size_t, C.c_void_p
     L.smat_spmm_bcsr_f16.argtypes = [vp, ip, ip, vp, vp, sz, sz, sz, sz, ip, ip, vp]
     L.smat_spmm_bcsr_f16_rows.argtypes = [vp, ip, ip, vp, vp, sz, sz, sz, sz, sz, sz, vp]
+    L.smat_spmm_bcsr_f16_static.argtypes = [vp, ip, ip, vp, vp, sz, sz, sz, sz, vp]
     L.smat_plan_create.argtypes = [C.POINTER(vp), vp, ip, ip, sz, sz, sz, sz, sz, vp]
     L.smat_plan_set_values.argtypes = [vp, vp, vp]
     L.smat_plan_spmm.argtypes = [vp, vp, vp, sz, vp]

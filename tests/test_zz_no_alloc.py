@@ -1,0 +1,64 @@
+"""smat_spmm_bcsr_f16_static -- the SpMM entry point for hosts that must not allocate device memory
+(fixed-budget serving loops, callbacks running under an allocator lock).  It keeps its per-call plan
+in a fixed array inside the library image, shared by all calls.  The test drives it through the C ABI
+twice in a row, with different inputs, and requires the same bits as the allocating entry point
+(both run the same kernels, so the tolerance is zero), then checks that oversize inputs are refused.
+Collected last on purpose: a failure here cannot hide failures elsewhere in a run that stops early."""
+import ctypes
+
+import numpy as np
+import pytest
+
+import oracle
+import smat_b200 as S
+from smat_b200 import generators as gen
+
+pytestmark = pytest.mark.gpu
+
+
+def _both(p, brp, bci, bv, B_nk):
+    import torch
+    A = S.SparseMatrix.from_bcsr(p.M, p.K, brp, bci, bv)
+    B = S.Matrix.from_host(B_nk)
+    N = B_nk.shape[0]
+    want = S.Matrix(p.M, N, fill=float("nan"))
+    S.spmm(A, B, want, check=True)
+    got = S.Matrix(p.M, N, fill=float("nan"))
+    L = S.lib()
+    rc = L.smat_spmm_bcsr_f16_static(A.getBcsrValues(), A.getBcsrRowPtr(), A.getBcsrColIdx(), B.data.data_ptr(),
+                                     got.data.data_ptr(), p.M, N, p.K, A.nnzb, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, L.smat_last_error_string()
+    torch.cuda.synchronize()
+    return want.data.cpu().numpy(), got.data.cpu().numpy()
+
+
+def test_static_scratch_entry_matches_allocating_entry_twice():
+    rng = np.random.default_rng(5)
+    # first call: the band configuration (2284 blocks)
+    p = gen.make_config("band")
+    brp, bci, bv = oracle.csr_to_bcsr(p.M, p.K, p.rowptr, p.colidx, p.vals)
+    want, got = _both(p, brp, bci, bv, p.B_nk)
+    assert np.array_equal(want.view(np.uint16), got.view(np.uint16))
+    # second call right after it: another matrix and width, so leftovers of the first call in the
+    # shared array would show
+    p2 = gen.make_config("uniform", scale=0.03)
+    brp2, bci2, bv2 = oracle.csr_to_bcsr(p2.M, p2.K, p2.rowptr, p2.colidx, p2.vals)
+    B2 = rng.standard_normal((136, p2.K)).astype(np.float16)
+    want2, got2 = _both(p2, brp2, bci2, bv2, B2)
+    assert np.array_equal(want2.view(np.uint16), got2.view(np.uint16))
+    # and against the oracle, like every other parity test (max relative error 1e-2)
+    ref = oracle.bcsr_spmm(bv2, brp2, bci2, B2, p2.M, 136, p2.K)
+    mag = oracle.bcsr_spmm(np.abs(bv2), brp2, bci2, np.abs(B2), p2.M, 136, p2.K)
+    ref16 = ref.astype(np.float16).astype(np.float32)
+    err = np.max(np.abs(got2.astype(np.float32) - ref16) / (np.maximum(np.abs(ref16), 1e-2 * mag) + 1e-30))
+    assert err <= 1e-2
+
+
+def test_static_scratch_entry_refuses_oversize_inputs():
+    L = S.lib()
+    buf = (ctypes.c_int * 64)()
+    a = ctypes.addressof(buf) & ~15
+    rc = L.smat_spmm_bcsr_f16_static(a, a, a, a, a, 16, 8, 16, 32769, None)
+    assert rc == -6 and b"32768" in L.smat_last_error_string()
+    rc = L.smat_spmm_bcsr_f16_static(a, a, a, a, a, 1048576 + 16, 8, 16, 1, None)
+    assert rc == -6

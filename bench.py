@@ -159,6 +159,39 @@ def cpu_reference_multiply(bvals, brp, bci, B_nk, M, K, N, brow_ranges, threads)
     return time.time() - t, ("reference" if R is not None else "port"), sum(done)
 
 
+def gpu_baselines(A, B, p, N, log):
+    """Informational: the reference's kernels (unmodified, compiled for sm_100a) and cuSPARSE CSR SpMM on
+    the same GPU and matrix.  mmaCBT is timing-only (its B slab copy is the intended tile only for K = 16)."""
+    import torch
+    import oracle
+    G = oracle.ref_gpu()
+    if G is None:
+        return {"unavailable": "oracle/_ref/libsmat_ref_gpu.so not built"}
+    Mb, Kb = p.M // 16, p.K // 16
+    flops = 2.0 * 256.0 * N * A.nnzb
+    res = {}
+    if Mb * Kb <= 600_000_000:
+        rows = torch.repeat_interleave(torch.arange(Mb, device="cuda"), (A.bcsrRowPtr[1:] - A.bcsrRowPtr[:-1]).long())
+        rel = torch.full((Mb * Kb,), -1, dtype=torch.int32, device="cuda")  # relativeBlockIndexMapping, matrix.h:425-431
+        rel[rows * Kb + (A.bcsrColIdx[: A.nnzb] // 16).long()] = torch.arange(A.nnzb, dtype=torch.int32, device="cuda")
+        Cref = torch.empty((p.M, N), dtype=torch.float16, device="cuda")
+        for which, name in ((0, "ref_mmaCBT"), (1, "ref_mmaBT")):
+            ms = G.ref_gpu_launch(which, A.getBcsrValues(), A.getBcsrRowPtr(), A.getBcsrColIdx(), B.data.data_ptr(),
+                                  Cref.data_ptr(), p.M, N, p.K, A.nnzb, rel.data_ptr(), rel.data_ptr(), 1, 3)
+            res[name] = {"ms": round(float(ms), 4), "tflops": round(flops / (ms * 1e-3) * 1e-12, 2) if ms > 0 else None}
+            log(f"{name} on this GPU: {ms:.3f} ms")
+        del rel, Cref
+    else:
+        res["ref_mmaCBT"] = {"unavailable": "dense Mb*Kb map beyond 2.4 GB"}
+    Cc = torch.empty((p.M, N), dtype=torch.float16, device="cuda")
+    ms = G.cusparse_csr_spmm_f16(A.csrRowPtr.data_ptr(), A.csrColIdx.data_ptr(), A.csrVal.data_ptr(), A.nnz,
+                                 B.data.data_ptr(), Cc.data_ptr(), p.M, N, p.K, 1, 5)
+    res["cusparse_csr"] = {"ms": round(float(ms), 4), "tflops": round(flops / (ms * 1e-3) * 1e-12, 2) if ms > 0 else None,
+                           "note": "fp16 in, fp32 compute, ALG_DEFAULT; throughput quoted in the same nonzero-block FLOPs"}
+    log(f"cuSPARSE CSR SpMM on this GPU: {ms:.3f} ms")
+    return res
+
+
 def sample_ranges(brp, Mb, target_blocks, parts):
     """`parts` disjoint contiguous block-row ranges from the start of the matrix, about target_blocks each."""
     out, b0 = [], 0
@@ -185,6 +218,8 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0)
     ap.add_argument("--cpu-sample-seconds", type=float, default=15.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gpu-baselines", action="store_true",
+                    help="also time the reference's own kernels (compiled for sm_100a) and cuSPARSE CSR SpMM on this GPU")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -223,7 +258,7 @@ def main():
     rp, ci, v, reorder_s, perm = reorder_if_needed(p, log, perm)
 
     t0 = time.time()
-    A = S.SparseMatrix.from_csr(p.M, p.K, rp, ci, v)
+    A = S.SparseMatrix.from_csr(p.M, p.K, rp, ci, v, keep_csr=args.gpu_baselines)
     build_s = time.time() - t0
     brp_h, bci_h, bv_h = A.host_arrays()
     Mb = p.M // 16
@@ -340,6 +375,10 @@ def main():
                "sample": f"block-rows [{rng[0][0]},{rng[0][1]}) = {nb} of {A.nnzb} blocks ({100.0 * nb / A.nnzb:.2f}%), "
                          f"{secs:.1f}s, VBR::multiply fp32 single thread"}
 
+    other = None
+    if world == 1 and args.gpu_baselines:
+        other = gpu_baselines(A, B, p, N, log)
+
     out = {
         "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "strong",
@@ -358,6 +397,8 @@ def main():
         "roofline": roof,
         "cpu_baseline": cpu,
     }
+    if other is not None:
+        out["gpu_baselines"] = other
     print(json.dumps(out), flush=True)
     if dist is not None:
         dist.destroy_process_group()

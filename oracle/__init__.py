@@ -26,6 +26,8 @@ def build(ref_root="/root/reference"):
     subprocess.check_call(["make", "-s", "-C", _HERE, "all"])
     if os.path.isdir(os.path.join(ref_root, "preprocess", "src", "general")):
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REF={ref_root}"])
+    if os.path.isdir(os.path.join(ref_root, "src", "cuda_hgemm", "src", "mma")):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref_gpu", f"REF={ref_root}"])
 
 
 def lib():
@@ -84,6 +86,25 @@ def ref():
                                        f32p, C.c_int, f32p]
         _REF = L
     return _REF
+
+
+_REF_GPU = None
+
+
+def ref_gpu():
+    """GPU baselines (the reference's kernels compiled unmodified for sm_100a, cuSPARSE CSR SpMM);
+    None if oracle/_ref/libsmat_ref_gpu.so was not built."""
+    global _REF_GPU
+    path = os.path.join(ref_dir(), "libsmat_ref_gpu.so")
+    if _REF_GPU is None and os.path.exists(path):
+        L = C.CDLL(path)
+        vp, sz = C.c_void_p, C.c_size_t
+        L.ref_gpu_launch.restype = C.c_float
+        L.ref_gpu_launch.argtypes = [C.c_int, vp, vp, vp, vp, vp, sz, sz, sz, sz, vp, vp, C.c_int, C.c_int]
+        L.cusparse_csr_spmm_f16.restype = C.c_float
+        L.cusparse_csr_spmm_f16.argtypes = [vp, vp, vp, sz, vp, vp, sz, sz, sz, C.c_int, C.c_int]
+        _REF_GPU = L
+    return _REF_GPU
 
 
 # ----------------------------------------------------------------------------------------------

@@ -1,0 +1,87 @@
+// TEST / BENCHMARK INFRASTRUCTURE ONLY -- doorway onto GPU baselines that are timed beside the product:
+//   * the reference's own sm_80-style kernels, UNMODIFIED, compiled from the reference tree for sm_100a
+//     (mmaCBTKernel, src/cuda_hgemm/src/mma/mmaCBT.cu:83-88; mmaBTKernel, src/cuda_hgemm/src/mma/mmaBT.cu),
+//   * cuSPARSE CSR SpMM configured as the reference's baseline does it
+//     (preprocess/src/cuda/cuda_utilities.cpp:1326-1393: CSR, fp16 in, fp32 compute, ALG_DEFAULT).
+// No algorithm of its own.  Built by oracle/Makefile (target ref_gpu) into oracle/_ref/; never linked
+// into the product.  Note: mmaCBT copies a contiguous 256-byte slab of B per tile, which is the intended
+// 8 x 16 tile only when K == 16 (mmaCBT.cu:46-53), so its numbers are timing-only.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cusparse.h>
+#include <stddef.h>
+
+void mmaCBTKernel(half*, int*, int*, half*, half*, size_t, size_t, size_t, size_t, int*, int*);
+void mmaBTKernel(half*, int*, int*, half*, half*, size_t, size_t, size_t, size_t, int*, int*);
+
+extern "C" {
+
+// Launches the reference kernel `iters` times on the default stream and returns the mean milliseconds
+// per launch (CUDA events), or a negative CUDA error code.
+float ref_gpu_launch(int which, void* vals, int* rowptr, int* colidx, void* B, void* C, size_t M, size_t N, size_t K,
+                     size_t nnzb, int* blockInfo, int* relMap, int warmup, int iters) {
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    auto run = [&]() {
+        if (which == 0) mmaCBTKernel((half*)vals, rowptr, colidx, (half*)B, (half*)C, M, N, K, nnzb, blockInfo, relMap);
+        else mmaBTKernel((half*)vals, rowptr, colidx, (half*)B, (half*)C, M, N, K, nnzb, blockInfo, relMap);
+    };
+    for (int i = 0; i < warmup; i++) run();
+    cudaEventRecord(e0);
+    for (int i = 0; i < iters; i++) run();
+    cudaEventRecord(e1);
+    cudaError_t e = cudaEventSynchronize(e1);
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (e != cudaSuccess || cudaGetLastError() != cudaSuccess) return -(float)(int)e - 1.0f;
+    return ms / iters;
+}
+
+// C[M x N] (row-major fp16) = A_csr[M x K] (fp16) * B, with B given as the [N][K] array of the kernel
+// boundary, i.e. the column-major K x N matrix.  Returns mean ms per call or a negative status.
+float cusparse_csr_spmm_f16(int* rowptr, int* colidx, void* vals, size_t nnz, void* B_nk, void* C, size_t M, size_t N,
+                            size_t K, int warmup, int iters) {
+    cusparseHandle_t h;
+    if (cusparseCreate(&h) != CUSPARSE_STATUS_SUCCESS) return -1;
+    cusparseSpMatDescr_t A;
+    cusparseDnMatDescr_t Bd, Cd;
+    cusparseCreateCsr(&A, M, K, nnz, rowptr, colidx, vals, CUSPARSE_INDEX_32I, CUSPARSE_INDEX_32I, CUSPARSE_INDEX_BASE_ZERO,
+                      CUDA_R_16F);
+    cusparseCreateDnMat(&Bd, K, N, K, B_nk, CUDA_R_16F, CUSPARSE_ORDER_COL);
+    cusparseCreateDnMat(&Cd, M, N, N, C, CUDA_R_16F, CUSPARSE_ORDER_ROW);
+    float alpha = 1.0f, beta = 0.0f;
+    size_t ws = 0;
+    cusparseStatus_t st = cusparseSpMM_bufferSize(h, CUSPARSE_OPERATION_NON_TRANSPOSE, CUSPARSE_OPERATION_NON_TRANSPOSE, &alpha, A,
+                                                  Bd, &beta, Cd, CUDA_R_32F, CUSPARSE_SPMM_ALG_DEFAULT, &ws);
+    if (st != CUSPARSE_STATUS_SUCCESS) return -2 - (float)st;
+    void* buf = nullptr;
+    cudaMalloc(&buf, ws ? ws : 16);
+    auto run = [&]() {
+        return cusparseSpMM(h, CUSPARSE_OPERATION_NON_TRANSPOSE, CUSPARSE_OPERATION_NON_TRANSPOSE, &alpha, A, Bd, &beta, Cd,
+                            CUDA_R_32F, CUSPARSE_SPMM_ALG_DEFAULT, buf);
+    };
+    for (int i = 0; i < warmup; i++) st = run();
+    if (st != CUSPARSE_STATUS_SUCCESS) { cudaFree(buf); return -100 - (float)st; }
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    cudaEventRecord(e0);
+    for (int i = 0; i < iters; i++) run();
+    cudaEventRecord(e1);
+    cudaEventSynchronize(e1);
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaFree(buf);
+    cusparseDestroySpMat(A);
+    cusparseDestroyDnMat(Bd);
+    cusparseDestroyDnMat(Cd);
+    cusparseDestroy(h);
+    return ms / iters;
+}
+
+}  // extern "C"

@@ -493,9 +493,11 @@ int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStre
         SMAT_CUDA_TRY(cudaGetLastError());
         return SMAT_OK;
     }
-    // Item width: 256 columns when C is at least that wide (every A block then feeds two MMAs), else 128.
+    // Item width: 256 columns when C is at least that wide AND the items are long (every A block then
+    // feeds two MMAs, but there is a single accumulator buffer, so the epilogue is not overlapped);
+    // matrices with few blocks per 16-row group keep 128-column items with two buffers.
     int variant = g_spmm_variant;
-    if (variant == 0) variant = N >= 256 ? 3 : 1;
+    if (variant == 0) variant = (N >= 256 && plan.nnzb / plan.n_groups >= 256) ? 3 : 1;
     const size_t NTI = variant == 3 ? 256 : 128;
     const uint32_t panel_rows = (uint32_t)(N < NTI ? N : NTI);
     CUtensorMap mapB;

@@ -100,7 +100,7 @@ __device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
 }
 
 #ifdef SMAT_PROFILE2
-__device__ long long g_prof2[8];
+__device__ long long g_prof2[16];
 #endif
 #ifdef SMAT_PROFILE
 __device__ unsigned long long g_prof[16];
@@ -282,6 +282,9 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
         if (TS && lane == 0) {
             const uint32_t j = (uint32_t)(warp - NL);
             uint32_t st = 0;
+#ifdef SMAT_PROFILE2
+            long long cw = 0, cc = 0, cm = 0, cn = 0;
+#endif
             for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
                 const int g = item / n_tiles;
                 const int ns = __ldg(gsp + g + 1) - __ldg(gsp + g);
@@ -290,7 +293,14 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                     // Every copier observes every stage in order, although it copies only its own: a
                     // parity wait is only meaningful for a waiter that is less than one phase away, and
                     // a copier that skipped stages could meet a barrier one whole use behind.
+#ifdef SMAT_PROFILE2
+                    const long long c0 = clock64();
+#endif
                     wait_bar(full(slot), (st / S) & 1, abort_addr, status, 2);
+#ifdef SMAT_PROFILE2
+                    const long long c1 = clock64();
+                    cw += c1 - c0;
+#endif
                     if (st % NC != j) continue;
                     tc_fence_after();
                     const uint32_t mlo = ld_shared_u32(base + OFF_META + slot * 8);
@@ -301,9 +311,19 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                     if (mlo >> 16) tc_cp_128x256b(tdst + 8, pdesc + 2);
                     if (mhi & 0xffffu) tc_cp_128x256b(tdst + 16, pdesc + 4);
                     if (mhi >> 16) tc_cp_128x256b(tdst + 24, pdesc + 6);
+#ifdef SMAT_PROFILE2
+                    const long long c2 = clock64();
+#endif
                     tc_commit(tfull(slot));
+#ifdef SMAT_PROFILE2
+                    const long long c3 = clock64();
+                    cc += c2 - c1; cm += c3 - c2; cn++;
+#endif
                 }
             }
+#ifdef SMAT_PROFILE2
+            if (blockIdx.x == 0 && j == 0) { g_prof2[6] = cw; g_prof2[7] = cc; g_prof2[8] = cm; g_prof2[9] = cn; }
+#endif
         }
         __syncwarp();
     } else if (warp < NL + NC + NM) {
@@ -464,7 +484,7 @@ __global__ void zero_rows_kernel(uint4* dst, size_t n16) {
 #ifdef SMAT_PROFILE2
 extern "C" void smat_prof2_read(long long* out) {
     cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, g_prof2, sizeof(long long) * 8);
+    cudaMemcpyFromSymbol(out, g_prof2, sizeof(long long) * 16);
 }
 #endif
 #ifdef SMAT_PROFILE

@@ -61,7 +61,7 @@ int smat_spmm_bcsr_f16_rows(const void* bcsrValuesA, const int* bcsrRowPtrA, con
  * instead of freshly allocated scratch, so the call performs no allocation and no free.
  * No counterpart in the reference (its launcher needs no scratch, mmaCBT.cu:83-88).
  * Limits: nonzeroBlocks <= SMAT_STATIC_MAX_BLOCKS and M <= SMAT_STATIC_MAX_ROWS, else SMAT_ERR_RANGE;
- * the array (about 17 MB) stays resident on every GPU that loads the library.
+ * the array (about 25 MB) stays resident on every GPU that loads the library.
  * All calls on a device share the array: calls that overlap on the GPU race; calls on one stream do
  * not.  The first call on a device also looks up the array's device address -- make it before
  * starting a stream capture.  Bounded-wait time-outs are recorded in the array, not in the word

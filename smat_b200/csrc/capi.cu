@@ -137,11 +137,14 @@ static int spmm_transient_plan(const void* vals, const int* rowptr, const int* c
     v.steps = b + sz.gsp_bytes;
     v.blk = reinterpret_cast<int*>(b + sz.gsp_bytes + sz.steps_bytes);
     v.packed = b + sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes;
-    int rc = build_plan_async(rowptr, colidx, K, nnzb, brow_begin, brow_end, reinterpret_cast<int*>(b), b + sz.gsp_bytes,
-                              reinterpret_cast<int*>(b + sz.gsp_bytes + sz.steps_bytes), stream);
+    int rc = plan_count_async(rowptr, colidx, K, nnzb, brow_begin, brow_end, reinterpret_cast<int*>(b), stream);
     if (rc == SMAT_OK)
-        rc = pack_values_async(rowptr, vals, v.blk, b + sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes, brow_begin, brow_end, nnzb,
-                               stream);
+        rc = plan_fill_async(rowptr, colidx, K, nnzb, brow_begin, brow_end, v.gsp, b + sz.gsp_bytes,
+                             reinterpret_cast<int*>(b + sz.gsp_bytes + sz.steps_bytes),
+                             b + sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes, stream);
+    if (rc == SMAT_OK)
+        rc = pack_values_async(rowptr, vals, v.gsp, v.steps, v.blk, b + sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes, brow_begin,
+                               brow_end, nnzb, stream);
     if (rc == SMAT_OK) rc = launch_spmm(v, B, C, N, stream);
     const cudaError_t e = cudaFreeAsync(buf, stream);
     if (rc == SMAT_OK && e != cudaSuccess) return fail(SMAT_ERR_CUDA, "cudaFreeAsync failed: %s", cudaGetErrorString(e));

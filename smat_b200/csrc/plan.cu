@@ -77,7 +77,8 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* total, int* sh) 
 template <bool FILL>
 __global__ void __launch_bounds__(kPlanThreads)
 plan_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx, int brow_begin, int brow_end, int Kb,
-            int n_groups, int* __restrict__ gsp, uint4* __restrict__ steps, int* __restrict__ blk) {
+            int n_groups, int* __restrict__ gsp, uint4* __restrict__ steps, int* __restrict__ blk,
+            uint8_t* __restrict__ packed) {
     extern __shared__ uint32_t sm[];
     uint32_t* masks = sm;                                 // [kWindow] row mask per block-column
     int* blk_pre = reinterpret_cast<int*>(sm + kWindow);  // [kWindow] exclusive block number (FILL only)
@@ -89,6 +90,7 @@ plan_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx, int 
         const int beg = have ? __ldg(rowptr + row) : 0;
         const int end = have ? __ldg(rowptr + row + 1) : 0;
         const int gfirst = __ldg(rowptr + brow_begin + g * RG);  // first block of the group
+        const int rfirst = __ldg(rowptr + brow_begin);           // first block of the whole range
         int cur = beg;
         int steps_done = 0, blocks_done = 0;
         const int gs = FILL ? __ldg(gsp + g) : 0;
@@ -128,8 +130,32 @@ plan_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx, int 
                             part |= low;
                             m64 ^= low;
                         }
-                        steps[gs + s] = make_uint4((uint32_t)(w0 + i0 + 4 * qd) << 4, (uint32_t)(gfirst + b), (uint32_t)part,
-                                                   (uint32_t)(part >> 32));
+                        // position of the step's record in the packed stream, in 256-byte units
+                        const uint32_t pos = (uint32_t)(gs + s) * (kPlanOpBytes / 256) + 2u * (uint32_t)(gfirst - rfirst + b);
+                        steps[gs + s] = make_uint4((uint32_t)(w0 + i0 + 4 * qd) << 4, pos, (uint32_t)part, (uint32_t)(part >> 32));
+                        // MMA list of the step: runs of vertically adjacent blocks, per owner of 16/kPlanOwners rows
+                        uint16_t* ops = reinterpret_cast<uint16_t*>(packed + (size_t)pos * 256);
+                        int count[kPlanOwners] = {};
+                        int last_r = -2, last_sub = -1, last_owner = -1, last_len = 0;
+                        unsigned long long rest = part;
+                        for (int q = 0; rest; q++) {
+                            const int bit = __ffsll((long long)rest) - 1;
+                            rest &= rest - 1;
+                            const int r = bit & 15, sub = bit >> 4, owner = r / (RG / kPlanOwners);
+                            if (owner == last_owner && sub == last_sub && r == last_r + 1 && last_len < 4) {  // the length field holds 1..4
+                                last_len++;  // extend the run: entry stays where it is, length field grows
+                                ops[owner * 32 + count[owner]] += (uint16_t)(1u << 9);
+                            } else {
+                                count[owner]++;
+                                ops[owner * 32 + count[owner]] = (uint16_t)(q | (r << 5) | (sub << 11));
+                                last_len = 1;
+                            }
+                            last_r = r;
+                            last_sub = sub;
+                            last_owner = owner;
+                        }
+#pragma unroll
+                        for (int o = 0; o < kPlanOwners; o++) ops[o * 32] = (uint16_t)count[o];
                         s++;
                         b += __popcll(part);
                     }
@@ -185,24 +211,32 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(int* data, int n) {
     }
 }
 
-// packed[i] <- vals[blk[i]] for i in [first, last): one warp per block, lane l moves the 16-byte chunk
-// l (row l/2, half l%2) to chunk l ^ ((l >> 3) & 1), i.e. the 32-byte swizzle.
+// One warp per step: copies the step's value blocks behind its MMA list in the packed stream; lane l moves
+// the 16-byte chunk l of a block (row l/2, half l%2) to chunk l ^ ((l >> 3) & 1), i.e. the 32-byte swizzle.
 __global__ void __launch_bounds__(256) pack_kernel(const uint4* __restrict__ vals, const int* __restrict__ blk,
-                                                  uint4* __restrict__ packed, const int* __restrict__ rowptr, int brow_begin,
-                                                  int brow_end) {
-    const int first = __ldg(rowptr + brow_begin), last = __ldg(rowptr + brow_end);
+                                                  const int* __restrict__ gsp, const uint4* __restrict__ steps,
+                                                  uint8_t* __restrict__ packed, const int* __restrict__ rowptr, int brow_begin,
+                                                  int n_groups) {
+    const int rfirst = __ldg(rowptr + brow_begin);
+    const int total = __ldg(gsp + n_groups);
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
-    for (int i = first + ((blockIdx.x * blockDim.x + threadIdx.x) >> 5); i < last; i += warps) {
-        const int src = __ldg(blk + i);
-        packed[(size_t)i * 32 + (lane ^ ((lane >> 3) & 1))] = __ldg(vals + (size_t)src * 32 + lane);
+    for (int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < total; i += warps) {
+        const uint4 d = __ldg(steps + i);
+        const int cnt = __popc(d.z) + __popc(d.w);
+        const int first = rfirst + (int)((d.y - (uint32_t)i * (kPlanOpBytes / 256)) >> 1);  // position of the step's first block in blk
+        uint4* dst = reinterpret_cast<uint4*>(packed + (size_t)d.y * 256 + kPlanOpBytes);
+        for (int q = 0; q < cnt; q++) {
+            const int src = __ldg(blk + first + q);
+            dst[q * 32 + (lane ^ ((lane >> 3) & 1))] = __ldg(vals + (size_t)src * 32 + lane);
+        }
     }
 }
 
 }  // namespace
 
-int pack_values_async(const int* rowptr, const void* vals, const int* blk, void* packed, size_t brow_begin,
-                      size_t brow_end, size_t nnzb, cudaStream_t stream, const DeviceCtx* ctx_in) {
+int pack_values_async(const int* rowptr, const void* vals, const int* gsp, const void* steps, const int* blk, void* packed,
+                      size_t brow_begin, size_t brow_end, size_t nnzb, cudaStream_t stream, const DeviceCtx* ctx_in) {
     if (nnzb == 0 || brow_end == brow_begin) return SMAT_OK;
     const DeviceCtx* ctx = ctx_in;
     if (!ctx) {
@@ -210,51 +244,72 @@ int pack_values_async(const int* rowptr, const void* vals, const int* blk, void*
         if (int rc = get_device_ctx(&c)) return rc;
         ctx = c;
     }
-    pack_kernel<<<ctx->sm_count * 8, 256, 0, stream>>>(reinterpret_cast<const uint4*>(vals), blk,
-                                                       reinterpret_cast<uint4*>(packed), rowptr, (int)brow_begin,
-                                                       (int)brow_end);
+    const size_t n_groups = (brow_end - brow_begin + RG - 1) / RG;
+    pack_kernel<<<ctx->sm_count * 8, 256, 0, stream>>>(reinterpret_cast<const uint4*>(vals), blk, gsp,
+                                                       reinterpret_cast<const uint4*>(steps), reinterpret_cast<uint8_t*>(packed),
+                                                       rowptr, (int)brow_begin, (int)n_groups);
     count_launch();
     SMAT_CUDA_TRY(cudaGetLastError());
     return SMAT_OK;
 }
 
-PlanSizes plan_sizes(size_t nnzb, size_t brow_begin, size_t brow_end) {
+PlanSizes plan_sizes(size_t nnzb, size_t brow_begin, size_t brow_end, size_t max_steps) {
     PlanSizes s;
     s.n_groups = (brow_end - brow_begin + RG - 1) / RG;
     s.gsp_bytes = ((s.n_groups + 1) * sizeof(int) + 255) / 256 * 256;
-    // a group has at most as many steps as blocks, so nnzb bounds the total
-    s.steps_bytes = ((nnzb ? nnzb : 1) * sizeof(uint4) + 255) / 256 * 256;
+    // a step holds at least one block, so nnzb bounds the number of steps
+    const size_t steps = max_steps ? max_steps : (nnzb ? nnzb : 1);
+    s.steps_bytes = (steps * sizeof(uint4) + 255) / 256 * 256;
     s.blk_bytes = ((nnzb ? nnzb : 1) * sizeof(int) + 255) / 256 * 256;
-    s.packed_bytes = (nnzb ? nnzb : 1) * 512;
+    s.packed_bytes = (nnzb ? nnzb : 1) * 512 + steps * kPlanOpBytes;
     return s;
 }
 
-int build_plan_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
-                     int* gsp, void* steps, int* blk, cudaStream_t stream, const DeviceCtx* ctx_in) {
-    const DeviceCtx* ctx = ctx_in;
-    if (!ctx) {
+static int plan_launch_setup(const DeviceCtx* ctx_in, const DeviceCtx** ctx) {
+    *ctx = ctx_in;
+    if (!*ctx) {
         DeviceCtx* c = nullptr;
         if (int rc = get_device_ctx(&c)) return rc;
-        ctx = c;
+        *ctx = c;
     }
+    return SMAT_OK;
+}
+
+int plan_count_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
+                     int* gsp, cudaStream_t stream, const DeviceCtx* ctx_in) {
+    const DeviceCtx* ctx = nullptr;
+    if (int rc = plan_launch_setup(ctx_in, &ctx)) return rc;
     const size_t n_groups = (brow_end - brow_begin + RG - 1) / RG;
     if (n_groups == 0) return SMAT_OK;
     if (nnzb == 0) {
         SMAT_CUDA_TRY(cudaMemsetAsync(gsp, 0, (n_groups + 1) * sizeof(int), stream));
         return SMAT_OK;
     }
-    const int Kb = (int)(K / 16);
     const int grid = (int)(n_groups < (size_t)ctx->sm_count ? n_groups : (size_t)ctx->sm_count);
-    const size_t smem_count = (size_t)kWindow * 4, smem_fill = (size_t)kWindow * 8;
+    const size_t smem_count = (size_t)kWindow * 4;
     SMAT_CUDA_TRY(cudaFuncSetAttribute(plan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_count));
-    SMAT_CUDA_TRY(cudaFuncSetAttribute(plan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fill));
-    plan_kernel<false><<<grid, kPlanThreads, smem_count, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, Kb,
-                                                                  (int)n_groups, gsp, nullptr, nullptr);
+    plan_kernel<false><<<grid, kPlanThreads, smem_count, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end,
+                                                                  (int)(K / 16), (int)n_groups, gsp, nullptr, nullptr, nullptr);
     count_launch();
     plan_scan_kernel<<<1, 1024, 0, stream>>>(gsp, (int)n_groups + 1);
     count_launch();
-    plan_kernel<true><<<grid, kPlanThreads, smem_fill, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, Kb,
-                                                                 (int)n_groups, gsp, reinterpret_cast<uint4*>(steps), blk);
+    SMAT_CUDA_TRY(cudaGetLastError());
+    return SMAT_OK;
+}
+
+int plan_fill_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
+                    const int* gsp, void* steps, int* blk, void* packed, cudaStream_t stream, const DeviceCtx* ctx_in) {
+    const DeviceCtx* ctx = nullptr;
+    if (int rc = plan_launch_setup(ctx_in, &ctx)) return rc;
+    const size_t n_groups = (brow_end - brow_begin + RG - 1) / RG;
+    if (n_groups == 0 || nnzb == 0) return SMAT_OK;
+    const int grid = (int)(n_groups < (size_t)ctx->sm_count ? n_groups : (size_t)ctx->sm_count);
+    const size_t smem_fill = (size_t)kWindow * 8;
+    SMAT_CUDA_TRY(cudaFuncSetAttribute(plan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fill));
+    plan_kernel<true><<<grid, kPlanThreads, smem_fill, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, (int)(K / 16),
+                                                                 (int)n_groups, const_cast<int*>(gsp),
+                                                                 reinterpret_cast<uint4*>(steps), blk,
+                                                                 reinterpret_cast<uint8_t*>(packed));
     count_launch();
     SMAT_CUDA_TRY(cudaGetLastError());
     return SMAT_OK;
@@ -267,6 +322,7 @@ using namespace smat;
 struct smat_plan {
     PlanView v;
     void* buffer = nullptr;
+    void* gsp_buffer = nullptr;
     int device = -1;
 };
 
@@ -283,31 +339,51 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
     if (nnzb * 16 >= ((size_t)1 << 31) || K >= ((size_t)1 << 31)) return fail(SMAT_ERR_RANGE, "size beyond 2^31");
     smat_plan* p = new (std::nothrow) smat_plan();
     if (!p) return fail(SMAT_ERR_NOMEM, "out of host memory");
-    const PlanSizes sz = plan_sizes(nnzb, brow_begin, brow_end);
+    // phase 1 into a small buffer of its own; the step total then sizes the rest exactly
+    PlanSizes sz = plan_sizes(nnzb, brow_begin, brow_end);
     cudaError_t e = cudaGetDevice(&p->device);
-    if (e == cudaSuccess) e = cudaMalloc(&p->buffer, sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes + sz.packed_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&p->gsp_buffer, sz.gsp_bytes);
     if (e != cudaSuccess) {
         delete p;
         return fail(SMAT_ERR_CUDA, "plan allocation failed: %s", cudaGetErrorString(e));
     }
+    int* gsp = static_cast<int*>(p->gsp_buffer);
+    int rc = plan_count_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, gsp, (cudaStream_t)stream);
+    int total_steps = 0;
+    if (rc == SMAT_OK && sz.n_groups) {
+        e = cudaMemcpyAsync(&total_steps, gsp + sz.n_groups, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+        if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan build failed: %s", cudaGetErrorString(e));
+    }
+    if (rc == SMAT_OK) {
+        sz = plan_sizes(nnzb, brow_begin, brow_end, (size_t)(total_steps > 0 ? total_steps : 1));
+        e = cudaMalloc(&p->buffer, sz.steps_bytes + sz.blk_bytes + sz.packed_bytes);
+        if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan allocation failed: %s", cudaGetErrorString(e));
+    }
+    if (rc) {
+        cudaFree(p->gsp_buffer);
+        delete p;
+        return rc;
+    }
     char* b = static_cast<char*>(p->buffer);
     p->v.rowptr = bcsrRowPtrA;
-    p->v.gsp = reinterpret_cast<int*>(b);
-    p->v.steps = b + sz.gsp_bytes;
-    p->v.blk = reinterpret_cast<int*>(b + sz.gsp_bytes + sz.steps_bytes);
-    p->v.packed = b + sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes;
+    p->v.gsp = gsp;
+    p->v.steps = b;
+    p->v.blk = reinterpret_cast<int*>(b + sz.steps_bytes);
+    p->v.packed = b + sz.steps_bytes + sz.blk_bytes;
     p->v.K = K;
     p->v.nnzb = nnzb;
     p->v.brow_begin = brow_begin;
     p->v.brow_end = brow_end;
     p->v.n_groups = sz.n_groups;
-    int rc = build_plan_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, const_cast<int*>(p->v.gsp),
-                              const_cast<void*>(p->v.steps), const_cast<int*>(p->v.blk), (cudaStream_t)stream);
+    rc = plan_fill_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, gsp, const_cast<void*>(p->v.steps),
+                         const_cast<int*>(p->v.blk), const_cast<void*>(p->v.packed), (cudaStream_t)stream);
     if (rc == SMAT_OK)
-        rc = pack_values_async(bcsrRowPtrA, bcsrValuesA, p->v.blk, const_cast<void*>(p->v.packed), brow_begin, brow_end,
-                               nnzb, (cudaStream_t)stream);
+        rc = pack_values_async(bcsrRowPtrA, bcsrValuesA, gsp, p->v.steps, p->v.blk, const_cast<void*>(p->v.packed), brow_begin,
+                               brow_end, nnzb, (cudaStream_t)stream);
     if (rc) {
         cudaFree(p->buffer);
+        cudaFree(p->gsp_buffer);
         delete p;
         return rc;
     }
@@ -319,8 +395,9 @@ int smat_plan_set_values(smat_plan* plan, const void* bcsrValuesA, void* stream)
     clear_error();
     if (!plan || (plan->v.nnzb && !bcsrValuesA)) return fail(SMAT_ERR_BAD_ARG, "NULL argument");
     if ((uintptr_t)bcsrValuesA & 15) return fail(SMAT_ERR_BAD_ARG, "bcsrValuesA must be 16-byte aligned");
-    return pack_values_async(plan->v.rowptr, bcsrValuesA, plan->v.blk, const_cast<void*>(plan->v.packed),
-                             plan->v.brow_begin, plan->v.brow_end, plan->v.nnzb, (cudaStream_t)stream);
+    return pack_values_async(plan->v.rowptr, bcsrValuesA, plan->v.gsp, plan->v.steps, plan->v.blk,
+                             const_cast<void*>(plan->v.packed), plan->v.brow_begin, plan->v.brow_end, plan->v.nnzb,
+                             (cudaStream_t)stream);
 }
 
 int smat_plan_spmm(const smat_plan* plan, const void* B, void* C, size_t N, void* stream) {
@@ -338,6 +415,8 @@ int smat_plan_destroy(smat_plan* plan) {
     clear_error();
     if (!plan) return SMAT_OK;
     cudaError_t e = cudaFree(plan->buffer);
+    const cudaError_t e2 = cudaFree(plan->gsp_buffer);
+    if (e == cudaSuccess) e = e2;
     delete plan;
     if (e != cudaSuccess) return fail(SMAT_ERR_CUDA, "cudaFree failed: %s", cudaGetErrorString(e));
     return SMAT_OK;

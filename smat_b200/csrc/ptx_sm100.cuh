@@ -186,6 +186,13 @@ __device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint32_t (&v)[8
                  "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
                  : "memory");
 }
+// Writes zero to 16 consecutive 32-bit columns of the calling thread's lane.
+__device__ __forceinline__ void tmem_zero_x16(uint32_t taddr) {
+    asm volatile(
+        "{\n\t.reg .b32 z;\n\tmov.b32 z, 0;\n\t"
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {z, z, z, z, z, z, z, z, z, z, z, z, z, z, z, z};\n\t}" ::"r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 

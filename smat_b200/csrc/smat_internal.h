@@ -44,19 +44,35 @@ int encode_tensor_map_2d_f16(CUtensorMap* map, const void* base, uint64_t inner,
 constexpr int kPlanRowsPerGroup = 16;
 // A step of the plan covers four consecutive block-columns and carries at most this many blocks.
 constexpr int kPlanBlocksPerStep = 24;
+// MMA-issuing threads of the kernel; each owns kPlanRowsPerGroup / kPlanOwners consecutive accumulators.
+#ifndef SMAT_OWNERS
+#define SMAT_OWNERS 8
+#endif
+constexpr int kPlanOwners = SMAT_OWNERS;
+// Bytes of the per-step MMA list that precedes the step's blocks in the packed stream (64 per owner,
+// a multiple of 256).
+constexpr int kPlanOpBytes = (kPlanOwners * 64 + 255) / 256 * 256;
 
 // The precomputed walk order of a block-row range (plan.cu).  All pointers are device memory.
 //   gsp[n_groups + 1]  first step of every group of kPlanRowsPerGroup block-rows
-//   steps              uint4 {element column of the quad (multiple of 64), first entry in blk,
-//                      mask bits 0..31, mask bits 32..63} per step; a step is a quad of four
+//   steps              uint4 {element column of the quad (multiple of 64), position of the step in the
+//                      packed stream in 256-byte units, mask bits 0..31, mask bits 32..63} per step; a step is a quad of four
 //                      consecutive block-columns of a group (or a slice of one holding at most
 //                      kPlanBlocksPerStep blocks), ascending inside a group; mask bit
 //                      16 * sub-column + row marks a block
 //   blk[nnzb]          block indices in (group, block-column, row) order; indexed with the ABSOLUTE
 //                      block position, i.e. the entries of group g occupy
 //                      [rowptr[first row of g], rowptr[first row of g + 1])
-//   packed[nnzb*512 B] the value blocks in that same order, each stored in the 32-byte-swizzled form
-//                      the MMA shared-memory descriptor reads (16-byte chunk index XOR bit 2 of the row)
+//   packed             the stream the kernel copies from, one record per step: a 256-byte MMA list followed
+//                      by the step's value blocks (512 bytes each) in (column, row) order, each block in
+//                      the 32-byte-swizzled form the MMA shared-memory descriptor reads (16-byte chunk
+//                      index XOR bit 2 of the row).  Step number i of the range, preceded by b blocks,
+//                      starts at byte kPlanOpBytes * i + 512 * b.
+//                      MMA list: kPlanOwners regions of 64 bytes; region o = {uint16 count, then count
+//                      uint16 entries}, entry = first block slot q (bits 0..4) | first row (5..8) |
+//                      run length - 1 (9..10) | sub-column (11..12): one MMA multiplies the run of
+//                      vertically adjacent blocks q .. q+len-1 (rows r0 .. r0+len-1 of one block-column);
+//                      runs never cross the rows of two owners.
 struct PlanView {
     const int* rowptr = nullptr;  // bcsrRowPtr of the whole matrix
     const int* gsp = nullptr;
@@ -67,14 +83,18 @@ struct PlanView {
 };
 
 // Work-list sizes for a block-row range and the asynchronous build on `stream` (plan.cu).
-struct PlanSizes { size_t n_groups, gsp_bytes, steps_bytes, blk_bytes, packed_bytes; };
-PlanSizes plan_sizes(size_t nnzb, size_t brow_begin, size_t brow_end);
+struct PlanSizes { size_t n_groups, gsp_bytes, steps_bytes, blk_bytes, packed_bytes; };  // for max_steps steps
+// max_steps = 0 means "not known yet": the bound nnzb (a step holds at least one block) is used.
+PlanSizes plan_sizes(size_t nnzb, size_t brow_begin, size_t brow_end, size_t max_steps = 0);
 // `ctx` (here and below): per-device state to use; nullptr = the lazily created one of get_device_ctx.
-int build_plan_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
-                     int* gsp, void* steps, int* blk, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
-// packed[i] = swizzled copy of value block blk[i] for the blocks of block-rows [brow_begin, brow_end).
-int pack_values_async(const int* rowptr, const void* vals, const int* blk, void* packed, size_t brow_begin,
-                      size_t brow_end, size_t nnzb, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
+// Phase 1 fills gsp (step counts, scanned); phase 2 fills steps, blk and the MMA lists inside packed.
+int plan_count_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
+                     int* gsp, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
+int plan_fill_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
+                    const int* gsp, void* steps, int* blk, void* packed, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
+// Copies the value blocks of block-rows [brow_begin, brow_end) into their places in the packed stream.
+int pack_values_async(const int* rowptr, const void* vals, const int* gsp, const void* steps, const int* blk, void* packed,
+                      size_t brow_begin, size_t brow_end, size_t nnzb, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
 
 // Launch of the SpMM kernel (spmm_sm100.cu).
 int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStream_t stream,

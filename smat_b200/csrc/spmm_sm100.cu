@@ -59,10 +59,8 @@ constexpr int NL = 4;                  // loader warps
 #ifndef SMAT_L2_PREFETCH
 #define SMAT_L2_PREFETCH 1
 #endif
-#ifndef SMAT_NM
-#define SMAT_NM 16
-#endif
-constexpr int NM = SMAT_NM;            // MMA-issuing warps
+constexpr int NM = kPlanOwners;        // MMA-issuing warps; warp m owns accumulators [m * RG / NM, (m + 1) * RG / NM)
+constexpr uint32_t OPS_BYTES = kPlanOpBytes;  // per-step MMA list in front of the step's blocks
 constexpr int NC = 4;                  // panel-copier warps (used by the tensor-memory-operand variant)
 constexpr int kThreads = (NL + NC + NM + 4) * 32;
 constexpr uint32_t TMEM_PANELS = 256;  // first tensor-memory column of the panel ring (TS variant): S x 32 columns
@@ -74,7 +72,7 @@ template <int NH>
 struct Cfg {
     static constexpr uint32_t S = NH == 1 ? 7 : 4;              // steps in flight (pipeline stages)
     static constexpr uint32_t PANEL_BYTES = NH * 128 * 64 * 2;  // NH x (128 n x 64 k fp16)
-    static constexpr uint32_t STAGE_BYTES = PANEL_BYTES + CAP * ABLK_BYTES;
+    static constexpr uint32_t STAGE_BYTES = (PANEL_BYTES + OPS_BYTES + CAP * ABLK_BYTES + 1023) / 1024 * 1024;
     static constexpr uint32_t OFF_STAGE = 0;
     static constexpr uint32_t OFF_META = OFF_STAGE + S * STAGE_BYTES;
     static constexpr uint32_t OFF_BAR = OFF_META + S * 8;
@@ -85,14 +83,17 @@ struct Cfg {
     static_assert(STAGE_BYTES % 1024 == 0 && CAP <= 32, "stage alignment");
 };
 
-constexpr uint32_t IDESC = idesc_f16_f32(128, 16);
-
 static_assert(RG == 16, "row masks and accumulator ownership below assume 16 block-rows per group");
 static_assert(RG * 2 * 16 <= 512 && TMEM_PANELS + Cfg<1>::S * 32 <= 512, "tensor-memory budget");
 
 __device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
     uint32_t v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_shared_u16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr) : "memory");
     return v;
 }
 __device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
@@ -198,6 +199,15 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = ld_shared_u32(tmem_slot);
+    if (warp < 4) {
+        // all accumulators start at zero (later the epilogue re-zeroes what it reads)
+#pragma unroll 4
+        for (uint32_t c = 0; c < 512; c += 16) tmem_zero_x16(tmem_base + ((uint32_t)(warp * 32) << 16) + c);
+        tmem_st_wait();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
 
     if (warp < NL) {
         // ------------------------------ loader warp j: every NL-th step ------------------------------
@@ -248,7 +258,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
 #if SMAT_L2_PREFETCH
                 if (r.live) {
                     tma_prefetch_l2_2d(&mapB, (int)r.d.x, r.tile * NT);
-                    bulk_prefetch_l2(packed + (size_t)r.d.y * ABLK_BYTES, (uint32_t)(__popc(r.d.z) + __popc(r.d.w)) * ABLK_BYTES);
+                    bulk_prefetch_l2(packed + (size_t)r.d.y * 256, OPS_BYTES + (uint32_t)(__popc(r.d.z) + __popc(r.d.w)) * ABLK_BYTES);
                 }
 #endif
             };
@@ -266,12 +276,12 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                     const uint32_t slot = r.st % S;
                     wait_bar(empty(slot), ((r.st / S) & 1) ^ 1, abort_addr, status, 1);
                     const uint32_t stage = base + OFF_STAGE + slot * STAGE_BYTES;
-                    const uint32_t a_bytes = (uint32_t)(__popc(r.d.z) + __popc(r.d.w)) * ABLK_BYTES;
+                    const uint32_t a_bytes = OPS_BYTES + (uint32_t)(__popc(r.d.z) + __popc(r.d.w)) * ABLK_BYTES;
                     st_shared_u32(base + OFF_META + slot * 8, r.d.z);
                     st_shared_u32(base + OFF_META + slot * 8 + 4, r.d.w);
                     mbar_arrive_expect_tx(full(slot), panel_bytes + a_bytes);
                     tma_load_2d(stage, &mapB, (int)r.d.x, r.tile * NT, full(slot));
-                    bulk_load(stage + PANEL_BYTES, packed + (size_t)r.d.y * ABLK_BYTES, a_bytes, full(slot));
+                    bulk_load(stage + PANEL_BYTES, packed + (size_t)r.d.y * 256, a_bytes, full(slot));
                     gen(r);  // this register set now follows the warp's step U positions ahead
                 }
             }
@@ -327,85 +337,50 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
         }
         __syncwarp();
     } else if (warp < NL + NC + NM) {
-        // ------------------------------ MMA warp m: accumulators r = m mod NM ------------------------------
+        // ------------------------------ MMA warp m: walks its part of every step's MMA list ------------------------------
         if (lane == 0) {
-            const int m = warp - NL - NC;
-            const uint32_t rowmask32 =
-                (NM == 16 ? 0x00010001u : NM == 8 ? 0x01010101u : NM == 4 ? 0x11111111u : NM == 2 ? 0x55555555u : ~0u) << m;
+            const uint32_t m = (uint32_t)(warp - NL - NC);
             const uint32_t P_HI = (uint32_t)(smem_desc_k_sw128(0) >> 32), B_HI = (uint32_t)(smem_desc_k_sw32(0) >> 32);
+            constexpr uint32_t IDESC_N0 = idesc_f16_f32(128, 0);  // the N field is added per run: N = 16 * length
             uint32_t st = 0, it = 0;
-#ifdef SMAT_PROFILE2
-            long long pw = 0, ps = 0, pm = 0, pc = 0, pn = 0, pmm = 0;
-#endif
             for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
                 const int g = item / n_tiles;
                 const int ns = __ldg(gsp + g + 1) - __ldg(gsp + g);
                 const uint32_t buf = it % NBUF;
+                // the accumulators were zeroed by the epilogue after it read them (or at kernel start), so
+                // every MMA accumulates and runs may span rows with and without earlier blocks
                 wait_bar(acc_empty(buf), ((it / NBUF) & 1) ^ 1, abort_addr, status, 3);
                 tc_fence_after();
-                uint32_t started = 0;
                 const uint32_t acc0 = tmem_base + buf * RG * 16 * NH;
                 for (int k = 0; k < ns; k++, st++) {
                     const uint32_t slot = st % S;
-#ifdef SMAT_PROFILE2
-                    const long long q0 = clock64();
-#endif
                     wait_bar(TS ? tfull(slot) : full(slot), (st / S) & 1, abort_addr, status, 4);
-#ifdef SMAT_PROFILE2
-                    const long long q1 = clock64();
-#endif
                     tc_fence_after();
-                    const uint32_t mlo = ld_shared_u32(base + OFF_META + slot * 8);
-                    const uint32_t mhi = ld_shared_u32(base + OFF_META + slot * 8 + 4);
                     const uint32_t stage = base + OFF_STAGE + slot * STAGE_BYTES;
-                    const uint32_t p_lo = (uint32_t)smem_desc_k_sw128(stage);             // panel, sub-column 0
-                    const uint32_t tpanel = tmem_base + TMEM_PANELS + slot * 32;          // its copy in tensor memory
-                    const uint32_t b_lo = (uint32_t)smem_desc_k_sw32(stage + PANEL_BYTES);  // first A block of the step
-                    // mask bit 16 * sub-column + row; q = rank of the bit = slot of the block in the stage
-                    uint32_t qbase = 0;
-#ifdef SMAT_PROFILE2
-                    const long long q2 = clock64();
-                    pmm += __popc(mlo & rowmask32) + __popc(mhi & rowmask32);
-#endif
+                    const uint32_t ops = stage + PANEL_BYTES + m * 64;                      // this warp's region of the MMA list
+                    const uint32_t p_lo = (uint32_t)smem_desc_k_sw128(stage);               // panel, sub-column 0
+                    const uint32_t tpanel = tmem_base + TMEM_PANELS + slot * 32;            // its copy in tensor memory
+                    const uint32_t b_lo = (uint32_t)smem_desc_k_sw32(stage + PANEL_BYTES + OPS_BYTES);  // block slot 0
+                    const uint32_t cnt = ld_shared_u16(ops);
+                    uint32_t e = ld_shared_u16(ops + 2);
+                    for (uint32_t i = 0; i < cnt; i++) {
+                        const uint32_t cur = e;
+                        e = ld_shared_u16(ops + 4 + 2 * i);  // next entry (the region has room for one past the last)
+                        const uint32_t q = cur & 31u, r0 = (cur >> 5) & 15u, len = ((cur >> 9) & 3u) + 1u, sub = (cur >> 11) & 3u;
+                        const uint32_t idesc = IDESC_N0 + ((2u * len) << 17);
+                        if (TS) {
+                            mma_f16_ts_lohi(acc0 + r0 * 16, tpanel + sub * 8u, b_lo + q * (ABLK_BYTES >> 4), B_HI, idesc, 1u);
+                        } else {
 #pragma unroll
-                    for (int half = 0; half < 2; half++) {
-                        const uint32_t word = half ? mhi : mlo;
-                        uint32_t mine = word & rowmask32;
-                        while (mine) {
-                            const int b = __ffs(mine) - 1;
-                            mine &= mine - 1;
-                            const uint32_t r = (uint32_t)b & 15u;
-                            const uint32_t q = qbase + __popc(word & ((1u << b) - 1u));
-                            if (TS) {
-                                mma_f16_ts_lohi(acc0 + r * 16, tpanel + (uint32_t)(half * 2 + (b >> 4)) * 8u,
-                                                b_lo + q * (ABLK_BYTES >> 4), B_HI, IDESC, (started >> r) & 1u);
-                            } else {
-#pragma unroll
-                                for (int h = 0; h < NH; h++)  // one MMA per 128-column half, each into its own accumulator
-                                    mma_f16_ss_lohi(acc0 + (r * NH + h) * 16,
-                                                    p_lo + (uint32_t)(half * 2 + (b >> 4)) * 2u + h * (128 * 128 >> 4), P_HI,
-                                                    b_lo + q * (ABLK_BYTES >> 4), B_HI, IDESC, (started >> r) & 1u);
-                            }
-                            started |= 1u << r;
+                            for (int h = 0; h < NH; h++)  // one MMA per 128-column half, each into its own accumulators
+                                mma_f16_ss_lohi(acc0 + (h * RG + r0) * 16, p_lo + sub * 2u + h * (128 * 128 >> 4), P_HI,
+                                                b_lo + q * (ABLK_BYTES >> 4), B_HI, idesc, 1u);
                         }
-                        qbase += __popc(word);
                     }
-#ifdef SMAT_PROFILE2
-                    const long long q3 = clock64();
-#endif
                     tc_commit(empty(slot));
-#ifdef SMAT_PROFILE2
-                    const long long q4 = clock64();
-                    pw += q1 - q0; ps += q2 - q1; pm += q3 - q2; pc += q4 - q3; pn++;
-#endif
                 }
                 tc_commit(acc_full(buf));
             }
-#ifdef SMAT_PROFILE2
-            if (blockIdx.x == 0 && m == 0) {
-                g_prof2[0] = pw; g_prof2[1] = ps; g_prof2[2] = pm; g_prof2[3] = pc; g_prof2[4] = pn; g_prof2[5] = pmm;
-            }
-#endif
         }
         __syncwarp();
     } else {
@@ -430,14 +405,18 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                     const int n = t * NT + h * 128 + quarter * 32 + lane;
                     uint32_t v[16];
                     if ((nonempty >> r) & 1u) {
-                        tmem_ld_x16(tmem_base + ((uint32_t)(quarter * 32) << 16) + ((buf * RG + (uint32_t)r) * NH + h) * 16, v);
+                        const uint32_t taddr =
+                            tmem_base + ((uint32_t)(quarter * 32) << 16) + ((buf * NH + h) * RG + (uint32_t)r) * 16;
+                        tmem_ld_x16(taddr, v);
                         tmem_ld_wait();
+                        tmem_zero_x16(taddr);  // leave the accumulator zeroed for the next item that uses this buffer
                     } else {
 #pragma unroll
                         for (int i = 0; i < 16; i++) v[i] = 0u;
                     }
                     if (r == nrows - 1 && h == NH - 1) {
-                        // every accumulator of this buffer has been read: hand it back to the MMA warps
+                        // every accumulator of this buffer has been read and zeroed: hand it back to the MMA warps
+                        tmem_st_wait();
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(acc_empty(buf));

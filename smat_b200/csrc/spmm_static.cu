@@ -9,7 +9,7 @@
 // plan in a fixed array that is part of the library image, so the call itself allocates nothing
 // and frees nothing.
 //
-// Cost and limits: the array occupies kStaticScratchBytes (about 17 MB) on every GPU that loads
+// Cost and limits: the array occupies kStaticScratchBytes (about 25 MB) on every GPU that loads
 // the library, until the process exits, and therefore bounds the problem: at most
 // SMAT_STATIC_MAX_BLOCKS nonzero blocks and SMAT_STATIC_MAX_ROWS rows.  Larger inputs are refused
 // with SMAT_ERR_RANGE; use the plan API for them.
@@ -36,7 +36,7 @@ constexpr size_t kMaxGroups = kMaxRows / 16 / kPlanRowsPerGroup;
 constexpr size_t kGspBytes = ((kMaxGroups + 1) * sizeof(int) + 255) / 256 * 256;
 constexpr size_t kStepsBytes = kMaxBlocks * 16;   // a group never has more steps than blocks
 constexpr size_t kBlkBytes = kMaxBlocks * sizeof(int);
-constexpr size_t kPackedBytes = kMaxBlocks * 512;
+constexpr size_t kPackedBytes = kMaxBlocks * 512 + kMaxBlocks * kPlanOpBytes;  // blocks + one MMA list per step
 constexpr size_t kStatusBytes = 256;
 constexpr size_t kStaticScratchBytes = kGspBytes + kStepsBytes + kBlkBytes + kPackedBytes + kStatusBytes;
 
@@ -115,7 +115,8 @@ extern "C" int smat_spmm_bcsr_f16_static(const void* vals, const int* rowptr, co
     v.packed = packed;
     // the status word shares the array with earlier calls: start from zero
     SMAT_CUDA_TRY(cudaMemsetAsync(d->ctx.d_status, 0, sizeof(int), stream));
-    if (int rc = build_plan_async(rowptr, colidx, K, nnzb, 0, Mb, gsp, steps, blk, stream, &d->ctx)) return rc;
-    if (int rc = pack_values_async(rowptr, vals, blk, packed, 0, Mb, nnzb, stream, &d->ctx)) return rc;
+    if (int rc = plan_count_async(rowptr, colidx, K, nnzb, 0, Mb, gsp, stream, &d->ctx)) return rc;
+    if (int rc = plan_fill_async(rowptr, colidx, K, nnzb, 0, Mb, gsp, steps, blk, packed, stream, &d->ctx)) return rc;
+    if (int rc = pack_values_async(rowptr, vals, gsp, steps, blk, packed, 0, Mb, nnzb, stream, &d->ctx)) return rc;
     return launch_spmm(v, B, C, N, stream, &d->ctx);
 }

@@ -15,6 +15,8 @@ Outputs:
   reorder_<name>.npz    CSR pattern + reference grouping (.g file of Matrix_Blocking) + permutation
                         (from its *_reordered.el) for -a 5 -F 1 runs
   multiply_<name>.npz   BCSR arrays + B + fp32 C of the reference's VBR::multiply
+  formats/*             outputs of the reference's Python glue (src/reorder.py: mtx2el, el2mtx, row pass,
+                        transpose, column pass) on a small pattern matrix
 """
 import json
 import os
@@ -142,8 +144,51 @@ def multiply_fixtures():
         print("multiply", name, p.M, p.K, N, "nnzb", nb)
 
 
+def formats_fixtures():
+    """Runs the reference's own Python glue (src/reorder.py, imported from the reference tree) and its
+    Matrix_Blocking program on a small pattern matrix: text converters, row pass, column pass."""
+    import shutil
+    import types
+    ref_src = "/root/reference/src"
+    sys.modules.setdefault("utils", types.ModuleType("utils"))  # plotting helpers, not needed (matplotlib absent)
+    sys.path.insert(0, ref_src)
+    import reorder as ref_reorder  # the reference module
+    out = os.path.join(HERE, "formats")
+    os.makedirs(out, exist_ok=True)
+    rng = np.random.default_rng(9)
+    n = 96
+    keys = np.unique(np.concatenate([rng.integers(0, n * n, 500), [(n - 1) * n + n - 1]]))
+    rng.shuffle(keys)
+    with open(os.path.join(out, "in.mtx"), "w") as f:
+        f.write(f"%%MatrixMarket matrix coordinate pattern general\n% fixture\n{n} {n} {len(keys)}\n")
+        f.write("\n".join(f"{k // n + 1} {k % n + 1}" for k in keys.tolist()))
+    with tempfile.TemporaryDirectory() as d:
+        shutil.copy(os.path.join(out, "in.mtx"), os.path.join(d, "m.mtx"))
+        os.makedirs(os.path.join(d, "programs", "general"))
+        shutil.copy(os.path.join(REFDIR, "Matrix_Blocking"), os.path.join(d, "programs", "general", "Matrix_Blocking"))
+        os.makedirs(os.path.join(d, "results"))
+        cwd = os.getcwd()
+        os.chdir(d)  # Matrix_Blocking writes its default outfile under ./results
+        try:
+            ref_reorder.mtx2el(os.path.join(d, "m.mtx"), os.path.join(d, "m.el"))
+            shutil.copy(os.path.join(d, "m.el"), os.path.join(out, "ref.el"))
+            ref_reorder.el2mtx(os.path.join(d, "m.el"), os.path.join(d, "back.mtx"))
+            shutil.copy(os.path.join(d, "back.mtx"), os.path.join(out, "ref_back.mtx"))
+            ref_reorder.reorder_using_paolo(os.path.join(d, "m.mtx"), d, 16, 16)
+            shutil.copy(os.path.join(d, "m_reordered.el"), os.path.join(out, "ref_reordered.el"))
+            shutil.copy(os.path.join(d, "m_reordered.mtx"), os.path.join(out, "ref_reordered.mtx"))
+            ref_reorder.reorder_cols_using_paolo(os.path.join(d, "m_reordered.el"), d, 16, 16)
+            shutil.copy(os.path.join(d, "m_reordered_transposed.el"), os.path.join(out, "ref_reordered_transposed.el"))
+            shutil.copy(os.path.join(d, "m_reordered_transposed_reordered.el"),
+                        os.path.join(out, "ref_reordered_transposed_reordered.el"))
+        finally:
+            os.chdir(cwd)
+    print("formats fixtures:", sorted(os.listdir(out)))
+
+
 if __name__ == "__main__":
     assert oracle.have_ref(), "build oracle/_ref first: make -C oracle ref REF=/root/reference"
     similarities()
     reorder_fixtures()
     multiply_fixtures()
+    formats_fixtures()

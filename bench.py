@@ -266,7 +266,7 @@ def main():
     b0, b1 = int(bounds[rank]), int(bounds[rank + 1])
     my_blocks = int(brp_h[b1] - brp_h[b0])
     t0 = time.time()
-    plan = S.Plan(A, b0, b1)
+    plan = S.Plan(A, b0, b1, n_hint=p.N)
     torch.cuda.synchronize()
     plan_s = time.time() - t0
     log(f"M={p.M} K={p.K} N={p.N} nnzb={A.nnzb} (device BCSR build {build_s:.2f}s, plan {plan_s:.2f}s); "

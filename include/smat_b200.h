@@ -84,8 +84,10 @@ int smat_spmm_bcsr_f16_static(const void* bcsrValuesA, const int* bcsrRowPtrA, c
  * owned).  After the values of A changed (same structure) call smat_plan_set_values.
  * No counterpart in the reference (its kernel re-reads bcsrColIdx per tile, mmaCBT.cu:38-43). */
 typedef struct smat_plan smat_plan;
+/* N_hint: the number of columns of B the plan will mostly be used with (0 = unknown).  It only steers
+ * how many block-rows form a work item (16, 8 or 4), so that small matrices or shards still fill the SMs. */
 int smat_plan_create(smat_plan** plan, const void* bcsrValuesA, const int* bcsrRowPtrA, const int* bcsrColIdxA, size_t M,
-                     size_t K, size_t nonzeroBlocks, size_t brow_begin, size_t brow_end, void* stream);
+                     size_t K, size_t nonzeroBlocks, size_t brow_begin, size_t brow_end, size_t N_hint, void* stream);
 int smat_plan_set_values(smat_plan* plan, const void* bcsrValuesA, void* stream);
 /* Rows [16*brow_begin, 16*brow_end) of C = A x B; C points at the first row of that range. */
 int smat_plan_spmm(const smat_plan* plan, const void* B, void* C, size_t N, void* stream);

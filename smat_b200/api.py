@@ -33,7 +33,7 @@ def lib():
     L.smat_spmm_bcsr_f16.argtypes = [vp, ip, ip, vp, vp, sz, sz, sz, sz, ip, ip, vp]
     L.smat_spmm_bcsr_f16_rows.argtypes = [vp, ip, ip, vp, vp, sz, sz, sz, sz, sz, sz, vp]
     L.smat_spmm_bcsr_f16_static.argtypes = [vp, ip, ip, vp, vp, sz, sz, sz, sz, vp]
-    L.smat_plan_create.argtypes = [C.POINTER(vp), vp, ip, ip, sz, sz, sz, sz, sz, vp]
+    L.smat_plan_create.argtypes = [C.POINTER(vp), vp, ip, ip, sz, sz, sz, sz, sz, sz, vp]
     L.smat_plan_set_values.argtypes = [vp, vp, vp]
     L.smat_plan_spmm.argtypes = [vp, vp, vp, sz, vp]
     L.smat_plan_destroy.argtypes = [vp]
@@ -282,13 +282,13 @@ def spmm_rows(A, B, Cshard, brow_begin, brow_end, check=False):
 class Plan:
     """Reusable multiplication plan for block-rows [brow_begin, brow_end) of A (smat_plan_*)."""
 
-    def __init__(self, A, brow_begin=0, brow_end=None):
+    def __init__(self, A, brow_begin=0, brow_end=None, n_hint=0):
         self.A = A
         self.brow_begin = brow_begin
         self.brow_end = A.M // 16 if brow_end is None else brow_end
         h = C.c_void_p()
         _check(lib().smat_plan_create(C.byref(h), A.getBcsrValues(), A.getBcsrRowPtr(), A.getBcsrColIdx(), A.M, A.K,
-                                      A.nnzb, self.brow_begin, self.brow_end, _stream()))
+                                      A.nnzb, self.brow_begin, self.brow_end, int(n_hint), _stream()))
         self._h = h
 
     def set_values(self):
@@ -332,7 +332,7 @@ class Tester:
         self.C = Matrix(A.M, N, "Matrix C")
         self.profiling_time_ms = 0.0
         self.throughput_tflops = 0.0
-        self.plan = Plan(A)
+        self.plan = Plan(A, n_hint=N)
         self._torch = torch
 
     def evaluateSparse2(self, name="smat_b200"):

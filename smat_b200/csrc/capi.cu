@@ -127,8 +127,12 @@ static int spmm_transient_plan(const void* vals, const int* rowptr, const int* c
     v.nnzb = nnzb;
     v.brow_begin = brow_begin;
     v.brow_end = brow_end;
-    const PlanSizes sz = plan_sizes(nnzb, brow_begin, brow_end);
+    DeviceCtx* ctx = nullptr;
+    if (int rc0 = get_device_ctx(&ctx)) return rc0;
+    const size_t rg = choose_rows_per_group(brow_end - brow_begin, N, ctx->sm_count);
+    const PlanSizes sz = plan_sizes(nnzb, brow_begin, brow_end, rg);
     v.n_groups = sz.n_groups;
+    v.rg = rg;
     if (nnzb == 0) return launch_spmm(v, B, C, N, stream);
     void* buf = nullptr;
     SMAT_CUDA_TRY(cudaMallocAsync(&buf, sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes + sz.packed_bytes, stream));
@@ -137,14 +141,14 @@ static int spmm_transient_plan(const void* vals, const int* rowptr, const int* c
     v.steps = b + sz.gsp_bytes;
     v.blk = reinterpret_cast<int*>(b + sz.gsp_bytes + sz.steps_bytes);
     v.packed = b + sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes;
-    int rc = plan_count_async(rowptr, colidx, K, nnzb, brow_begin, brow_end, reinterpret_cast<int*>(b), stream);
+    int rc = plan_count_async(rowptr, colidx, K, nnzb, brow_begin, brow_end, rg, reinterpret_cast<int*>(b), stream);
     if (rc == SMAT_OK)
-        rc = plan_fill_async(rowptr, colidx, K, nnzb, brow_begin, brow_end, v.gsp, b + sz.gsp_bytes,
+        rc = plan_fill_async(rowptr, colidx, K, nnzb, brow_begin, brow_end, rg, v.gsp, b + sz.gsp_bytes,
                              reinterpret_cast<int*>(b + sz.gsp_bytes + sz.steps_bytes),
                              b + sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes, stream);
     if (rc == SMAT_OK)
         rc = pack_values_async(rowptr, vals, v.gsp, v.steps, v.blk, b + sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes, brow_begin,
-                               brow_end, nnzb, stream);
+                               brow_end, rg, nnzb, stream);
     if (rc == SMAT_OK) rc = launch_spmm(v, B, C, N, stream);
     const cudaError_t e = cudaFreeAsync(buf, stream);
     if (rc == SMAT_OK && e != cudaSuccess) return fail(SMAT_ERR_CUDA, "cudaFreeAsync failed: %s", cudaGetErrorString(e));

@@ -18,6 +18,8 @@
 
 #include <new>
 
+#include <cstdlib>
+
 #include "smat_internal.h"
 
 namespace smat {
@@ -76,7 +78,7 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* total, int* sh) 
 
 template <bool FILL>
 __global__ void __launch_bounds__(kPlanThreads)
-plan_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx, int brow_begin, int brow_end, int Kb,
+plan_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx, int brow_begin, int brow_end, int rg, int Kb,
             int n_groups, int* __restrict__ gsp, uint4* __restrict__ steps, int* __restrict__ blk,
             uint8_t* __restrict__ packed) {
     extern __shared__ uint32_t sm[];
@@ -85,15 +87,16 @@ plan_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx, int 
     __shared__ int scan_sh[64];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
-        const int row = brow_begin + g * RG + warp;
-        const bool have = row < brow_end;
+        const int row = brow_begin + g * rg + warp;  // warps >= rg hold no row
+        const bool have = warp < rg && row < brow_end;
         const int beg = have ? __ldg(rowptr + row) : 0;
         const int end = have ? __ldg(rowptr + row + 1) : 0;
-        const int gfirst = __ldg(rowptr + brow_begin + g * RG);  // first block of the group
+        const int gfirst = __ldg(rowptr + brow_begin + g * rg);  // first block of the group
         const int rfirst = __ldg(rowptr + brow_begin);           // first block of the whole range
         int cur = beg;
         int steps_done = 0, blocks_done = 0;
         const int gs = FILL ? __ldg(gsp + g) : 0;
+        const int rpo = max(1, rg / kPlanOwners);  // rows per owning MMA warp
         for (int w0 = 0; w0 < Kb; w0 += kWindow) {
             const int cur_before = cur;
             mark_window(colidx, cur, end, w0, masks, warp, lane);
@@ -141,7 +144,7 @@ plan_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx, int 
                         for (int q = 0; rest; q++) {
                             const int bit = __ffsll((long long)rest) - 1;
                             rest &= rest - 1;
-                            const int r = bit & 15, sub = bit >> 4, owner = r / (RG / kPlanOwners);
+                            const int r = bit & 15, sub = bit >> 4, owner = r / rpo;
                             if (owner == last_owner && sub == last_sub && r == last_r + 1 && last_len < 4) {  // the length field holds 1..4
                                 last_len++;  // extend the run: entry stays where it is, length field grows
                                 ops[owner * 32 + count[owner]] += (uint16_t)(1u << 9);
@@ -236,7 +239,8 @@ __global__ void __launch_bounds__(256) pack_kernel(const uint4* __restrict__ val
 }  // namespace
 
 int pack_values_async(const int* rowptr, const void* vals, const int* gsp, const void* steps, const int* blk, void* packed,
-                      size_t brow_begin, size_t brow_end, size_t nnzb, cudaStream_t stream, const DeviceCtx* ctx_in) {
+                      size_t brow_begin, size_t brow_end, size_t rg, size_t nnzb, cudaStream_t stream,
+                      const DeviceCtx* ctx_in) {
     if (nnzb == 0 || brow_end == brow_begin) return SMAT_OK;
     const DeviceCtx* ctx = ctx_in;
     if (!ctx) {
@@ -244,7 +248,7 @@ int pack_values_async(const int* rowptr, const void* vals, const int* gsp, const
         if (int rc = get_device_ctx(&c)) return rc;
         ctx = c;
     }
-    const size_t n_groups = (brow_end - brow_begin + RG - 1) / RG;
+    const size_t n_groups = (brow_end - brow_begin + rg - 1) / rg;
     pack_kernel<<<ctx->sm_count * 8, 256, 0, stream>>>(reinterpret_cast<const uint4*>(vals), blk, gsp,
                                                        reinterpret_cast<const uint4*>(steps), reinterpret_cast<uint8_t*>(packed),
                                                        rowptr, (int)brow_begin, (int)n_groups);
@@ -253,9 +257,23 @@ int pack_values_async(const int* rowptr, const void* vals, const int* gsp, const
     return SMAT_OK;
 }
 
-PlanSizes plan_sizes(size_t nnzb, size_t brow_begin, size_t brow_end, size_t max_steps) {
+size_t choose_rows_per_group(size_t block_rows, size_t N, int sm_count) {
+    static const int forced = [] {  // tuning knob: SMAT_ROWS_PER_GROUP=16|8|4 overrides the choice
+        const char* e = std::getenv("SMAT_ROWS_PER_GROUP");
+        const int v = e ? std::atoi(e) : 0;
+        return (v == 16 || v == 8 || v == 4) ? v : 0;
+    }();
+    if (forced) return (size_t)forced;
+    const size_t tiles = N ? (N + 127) / 128 : 1;
+    for (size_t rg : {(size_t)16, (size_t)8}) {
+        if ((block_rows + rg - 1) / rg * tiles >= (size_t)sm_count) return rg;
+    }
+    return 4;
+}
+
+PlanSizes plan_sizes(size_t nnzb, size_t brow_begin, size_t brow_end, size_t rg, size_t max_steps) {
     PlanSizes s;
-    s.n_groups = (brow_end - brow_begin + RG - 1) / RG;
+    s.n_groups = (brow_end - brow_begin + rg - 1) / rg;
     s.gsp_bytes = ((s.n_groups + 1) * sizeof(int) + 255) / 256 * 256;
     // a step holds at least one block, so nnzb bounds the number of steps
     const size_t steps = max_steps ? max_steps : (nnzb ? nnzb : 1);
@@ -276,10 +294,10 @@ static int plan_launch_setup(const DeviceCtx* ctx_in, const DeviceCtx** ctx) {
 }
 
 int plan_count_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
-                     int* gsp, cudaStream_t stream, const DeviceCtx* ctx_in) {
+                     size_t rg, int* gsp, cudaStream_t stream, const DeviceCtx* ctx_in) {
     const DeviceCtx* ctx = nullptr;
     if (int rc = plan_launch_setup(ctx_in, &ctx)) return rc;
-    const size_t n_groups = (brow_end - brow_begin + RG - 1) / RG;
+    const size_t n_groups = (brow_end - brow_begin + rg - 1) / rg;
     if (n_groups == 0) return SMAT_OK;
     if (nnzb == 0) {
         SMAT_CUDA_TRY(cudaMemsetAsync(gsp, 0, (n_groups + 1) * sizeof(int), stream));
@@ -288,7 +306,7 @@ int plan_count_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb
     const int grid = (int)(n_groups < (size_t)ctx->sm_count ? n_groups : (size_t)ctx->sm_count);
     const size_t smem_count = (size_t)kWindow * 4;
     SMAT_CUDA_TRY(cudaFuncSetAttribute(plan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_count));
-    plan_kernel<false><<<grid, kPlanThreads, smem_count, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end,
+    plan_kernel<false><<<grid, kPlanThreads, smem_count, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, (int)rg,
                                                                   (int)(K / 16), (int)n_groups, gsp, nullptr, nullptr, nullptr);
     count_launch();
     plan_scan_kernel<<<1, 1024, 0, stream>>>(gsp, (int)n_groups + 1);
@@ -298,16 +316,16 @@ int plan_count_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb
 }
 
 int plan_fill_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
-                    const int* gsp, void* steps, int* blk, void* packed, cudaStream_t stream, const DeviceCtx* ctx_in) {
+                    size_t rg, const int* gsp, void* steps, int* blk, void* packed, cudaStream_t stream, const DeviceCtx* ctx_in) {
     const DeviceCtx* ctx = nullptr;
     if (int rc = plan_launch_setup(ctx_in, &ctx)) return rc;
-    const size_t n_groups = (brow_end - brow_begin + RG - 1) / RG;
+    const size_t n_groups = (brow_end - brow_begin + rg - 1) / rg;
     if (n_groups == 0 || nnzb == 0) return SMAT_OK;
     const int grid = (int)(n_groups < (size_t)ctx->sm_count ? n_groups : (size_t)ctx->sm_count);
     const size_t smem_fill = (size_t)kWindow * 8;
     SMAT_CUDA_TRY(cudaFuncSetAttribute(plan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fill));
-    plan_kernel<true><<<grid, kPlanThreads, smem_fill, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, (int)(K / 16),
-                                                                 (int)n_groups, const_cast<int*>(gsp),
+    plan_kernel<true><<<grid, kPlanThreads, smem_fill, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, (int)rg,
+                                                                 (int)(K / 16), (int)n_groups, const_cast<int*>(gsp),
                                                                  reinterpret_cast<uint4*>(steps), blk,
                                                                  reinterpret_cast<uint8_t*>(packed));
     count_launch();
@@ -329,7 +347,7 @@ struct smat_plan {
 extern "C" {
 
 int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRowPtrA, const int* bcsrColIdxA, size_t M,
-                     size_t K, size_t nnzb, size_t brow_begin, size_t brow_end, void* stream) {
+                     size_t K, size_t nnzb, size_t brow_begin, size_t brow_end, size_t N_hint, void* stream) {
     clear_error();
     if (!out || !bcsrRowPtrA || (nnzb && (!bcsrColIdxA || !bcsrValuesA))) return fail(SMAT_ERR_BAD_ARG, "NULL argument");
     if (M % 16 || K % 16) return fail(SMAT_ERR_BAD_ARG, "M (%zu) and K (%zu) must be multiples of 16", M, K);
@@ -339,8 +357,14 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
     if (nnzb * 16 >= ((size_t)1 << 31) || K >= ((size_t)1 << 31)) return fail(SMAT_ERR_RANGE, "size beyond 2^31");
     smat_plan* p = new (std::nothrow) smat_plan();
     if (!p) return fail(SMAT_ERR_NOMEM, "out of host memory");
+    DeviceCtx* ctx = nullptr;
+    if (int rc0 = get_device_ctx(&ctx)) {
+        delete p;
+        return rc0;
+    }
+    const size_t rg = choose_rows_per_group(brow_end - brow_begin, N_hint, ctx->sm_count);
     // phase 1 into a small buffer of its own; the step total then sizes the rest exactly
-    PlanSizes sz = plan_sizes(nnzb, brow_begin, brow_end);
+    PlanSizes sz = plan_sizes(nnzb, brow_begin, brow_end, rg);
     cudaError_t e = cudaGetDevice(&p->device);
     if (e == cudaSuccess) e = cudaMalloc(&p->gsp_buffer, sz.gsp_bytes);
     if (e != cudaSuccess) {
@@ -348,7 +372,7 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
         return fail(SMAT_ERR_CUDA, "plan allocation failed: %s", cudaGetErrorString(e));
     }
     int* gsp = static_cast<int*>(p->gsp_buffer);
-    int rc = plan_count_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, gsp, (cudaStream_t)stream);
+    int rc = plan_count_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, rg, gsp, (cudaStream_t)stream);
     int total_steps = 0;
     if (rc == SMAT_OK && sz.n_groups) {
         e = cudaMemcpyAsync(&total_steps, gsp + sz.n_groups, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
@@ -356,7 +380,7 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
         if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan build failed: %s", cudaGetErrorString(e));
     }
     if (rc == SMAT_OK) {
-        sz = plan_sizes(nnzb, brow_begin, brow_end, (size_t)(total_steps > 0 ? total_steps : 1));
+        sz = plan_sizes(nnzb, brow_begin, brow_end, rg, (size_t)(total_steps > 0 ? total_steps : 1));
         e = cudaMalloc(&p->buffer, sz.steps_bytes + sz.blk_bytes + sz.packed_bytes);
         if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan allocation failed: %s", cudaGetErrorString(e));
     }
@@ -376,11 +400,12 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
     p->v.brow_begin = brow_begin;
     p->v.brow_end = brow_end;
     p->v.n_groups = sz.n_groups;
-    rc = plan_fill_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, gsp, const_cast<void*>(p->v.steps),
+    p->v.rg = rg;
+    rc = plan_fill_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, rg, gsp, const_cast<void*>(p->v.steps),
                          const_cast<int*>(p->v.blk), const_cast<void*>(p->v.packed), (cudaStream_t)stream);
     if (rc == SMAT_OK)
         rc = pack_values_async(bcsrRowPtrA, bcsrValuesA, gsp, p->v.steps, p->v.blk, const_cast<void*>(p->v.packed), brow_begin,
-                               brow_end, nnzb, (cudaStream_t)stream);
+                               brow_end, rg, nnzb, (cudaStream_t)stream);
     if (rc) {
         cudaFree(p->buffer);
         cudaFree(p->gsp_buffer);
@@ -396,8 +421,8 @@ int smat_plan_set_values(smat_plan* plan, const void* bcsrValuesA, void* stream)
     if (!plan || (plan->v.nnzb && !bcsrValuesA)) return fail(SMAT_ERR_BAD_ARG, "NULL argument");
     if ((uintptr_t)bcsrValuesA & 15) return fail(SMAT_ERR_BAD_ARG, "bcsrValuesA must be 16-byte aligned");
     return pack_values_async(plan->v.rowptr, bcsrValuesA, plan->v.gsp, plan->v.steps, plan->v.blk,
-                             const_cast<void*>(plan->v.packed), plan->v.brow_begin, plan->v.brow_end, plan->v.nnzb,
-                             (cudaStream_t)stream);
+                             const_cast<void*>(plan->v.packed), plan->v.brow_begin, plan->v.brow_end, plan->v.rg,
+                             plan->v.nnzb, (cudaStream_t)stream);
 }
 
 int smat_plan_spmm(const smat_plan* plan, const void* B, void* C, size_t N, void* stream) {

@@ -40,8 +40,11 @@ void count_launch();
 int encode_tensor_map_2d_f16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_pitch_bytes,
                              uint32_t box_inner, uint32_t box_outer, int swizzle_bytes, int l2_promo_bytes);
 
-// Block-rows per work item of the SpMM kernel; the multiplication plan is built for this grouping.
+// Most block-rows per work item of the SpMM kernel (one accumulator each).  A plan is built for groups of
+// `rg` <= kPlanRowsPerGroup block-rows: small matrices / shards use smaller groups to fill the SMs.
 constexpr int kPlanRowsPerGroup = 16;
+// Group height that yields at least `sm_count` work items when C is N columns wide, from {16, 8, 4}.
+size_t choose_rows_per_group(size_t block_rows, size_t N, int sm_count);
 // A step of the plan covers four consecutive block-columns and carries at most this many blocks.
 constexpr int kPlanBlocksPerStep = 24;
 // MMA-issuing threads of the kernel; each owns kPlanRowsPerGroup / kPlanOwners consecutive accumulators.
@@ -79,22 +82,23 @@ struct PlanView {
     const void* steps = nullptr;
     const int* blk = nullptr;
     const void* packed = nullptr;
-    size_t K = 0, nnzb = 0, brow_begin = 0, brow_end = 0, n_groups = 0;
+    size_t K = 0, nnzb = 0, brow_begin = 0, brow_end = 0, n_groups = 0, rg = kPlanRowsPerGroup;
 };
 
 // Work-list sizes for a block-row range and the asynchronous build on `stream` (plan.cu).
 struct PlanSizes { size_t n_groups, gsp_bytes, steps_bytes, blk_bytes, packed_bytes; };  // for max_steps steps
 // max_steps = 0 means "not known yet": the bound nnzb (a step holds at least one block) is used.
-PlanSizes plan_sizes(size_t nnzb, size_t brow_begin, size_t brow_end, size_t max_steps = 0);
+PlanSizes plan_sizes(size_t nnzb, size_t brow_begin, size_t brow_end, size_t rg, size_t max_steps = 0);
 // `ctx` (here and below): per-device state to use; nullptr = the lazily created one of get_device_ctx.
 // Phase 1 fills gsp (step counts, scanned); phase 2 fills steps, blk and the MMA lists inside packed.
 int plan_count_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
-                     int* gsp, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
+                     size_t rg, int* gsp, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
 int plan_fill_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
-                    const int* gsp, void* steps, int* blk, void* packed, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
+                    size_t rg, const int* gsp, void* steps, int* blk, void* packed, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
 // Copies the value blocks of block-rows [brow_begin, brow_end) into their places in the packed stream.
 int pack_values_async(const int* rowptr, const void* vals, const int* gsp, const void* steps, const int* blk, void* packed,
-                      size_t brow_begin, size_t brow_end, size_t nnzb, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
+                      size_t brow_begin, size_t brow_end, size_t rg, size_t nnzb, cudaStream_t stream,
+                      const DeviceCtx* ctx = nullptr);
 
 // Launch of the SpMM kernel (spmm_sm100.cu).
 int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStream_t stream,

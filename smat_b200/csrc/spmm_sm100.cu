@@ -158,7 +158,7 @@ template <bool TS, int NH>
 __global__ void __launch_bounds__(kThreads, 1)
 spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __restrict__ packed,
                     const uint4* __restrict__ steps, const int* __restrict__ gsp,
-                    const int* __restrict__ rowptr, __half* __restrict__ C, int brow_begin, int brow_end, int N,
+                    const int* __restrict__ rowptr, __half* __restrict__ C, int brow_begin, int brow_end, int rg, int N,
                     int n_tiles, int n_items, uint32_t panel_bytes, int* status) {
     static_assert(!(TS && NH == 2), "the panel ring and 32 accumulators do not fit tensor memory together");
     using G = Cfg<NH>;
@@ -390,8 +390,8 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
         uint32_t it = 0;
         for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
             const int g = item / n_tiles, t = item - g * n_tiles;
-            const int r0 = brow_begin + g * RG;
-            const int nrows = min(RG, brow_end - r0);
+            const int r0 = brow_begin + g * rg;
+            const int nrows = min(rg, brow_end - r0);
             const int lo = (lane < nrows) ? __ldg(rowptr + r0 + lane) : 0;
             const int hi = (lane < nrows) ? __ldg(rowptr + r0 + lane + 1) : 0;
             const uint32_t nonempty = __ballot_sync(0xffffffffu, hi > lo);
@@ -494,9 +494,11 @@ int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStre
     }
     // Item width: 256 columns when C is at least that wide AND the items are long (every A block then
     // feeds two MMAs, but there is a single accumulator buffer, so the epilogue is not overlapped);
-    // matrices with few blocks per 16-row group keep 128-column items with two buffers.
+    // matrices with few blocks per group, or too few groups to give every SM a 256-column item, keep
+    // 128-column items with two buffers.
     int variant = g_spmm_variant;
-    if (variant == 0) variant = (N >= 256 && plan.nnzb / plan.n_groups >= 256) ? 3 : 1;
+    if (variant == 0)
+        variant = (N >= 256 && plan.nnzb / plan.n_groups >= 256 && plan.n_groups * ((N + 255) / 256) >= (size_t)ctx->sm_count) ? 3 : 1;
     const size_t NTI = variant == 3 ? 256 : 128;
     const uint32_t panel_rows = (uint32_t)(N < NTI ? N : NTI);
     CUtensorMap mapB;
@@ -509,7 +511,7 @@ int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStre
         SMAT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
         kernel<<<grid, kThreads, smem_bytes, stream>>>(
             mapB, reinterpret_cast<const uint8_t*>(plan.packed), reinterpret_cast<const uint4*>(plan.steps), plan.gsp,
-            plan.rowptr, reinterpret_cast<__half*>(C), (int)plan.brow_begin, (int)plan.brow_end, (int)N, n_tiles,
+            plan.rowptr, reinterpret_cast<__half*>(C), (int)plan.brow_begin, (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles,
             (int)n_items, panel_rows * 128u, ctx->d_status);
         count_launch();
         SMAT_CUDA_TRY(cudaGetLastError());

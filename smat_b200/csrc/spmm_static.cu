@@ -32,7 +32,7 @@ namespace {
 
 constexpr size_t kMaxBlocks = 32768;          // SMAT_STATIC_MAX_BLOCKS
 constexpr size_t kMaxRows = 1048576;          // SMAT_STATIC_MAX_ROWS
-constexpr size_t kMaxGroups = kMaxRows / 16 / kPlanRowsPerGroup;
+constexpr size_t kMaxGroups = kMaxRows / 16 / 4;  // the smallest group height is 4 block-rows
 constexpr size_t kGspBytes = ((kMaxGroups + 1) * sizeof(int) + 255) / 256 * 256;
 constexpr size_t kStepsBytes = kMaxBlocks * 16;   // a group never has more steps than blocks
 constexpr size_t kBlkBytes = kMaxBlocks * sizeof(int);
@@ -104,7 +104,9 @@ extern "C" int smat_spmm_bcsr_f16_static(const void* vals, const int* rowptr, co
     v.nnzb = nnzb;
     v.brow_begin = 0;
     v.brow_end = Mb;
-    v.n_groups = (Mb + kPlanRowsPerGroup - 1) / kPlanRowsPerGroup;
+    const size_t rg = choose_rows_per_group(Mb, N, d->ctx.sm_count);
+    v.rg = rg;
+    v.n_groups = (Mb + rg - 1) / rg;
     int* gsp = reinterpret_cast<int*>(d->base);
     void* steps = d->base + kGspBytes;
     int* blk = reinterpret_cast<int*>(d->base + kGspBytes + kStepsBytes);
@@ -115,8 +117,8 @@ extern "C" int smat_spmm_bcsr_f16_static(const void* vals, const int* rowptr, co
     v.packed = packed;
     // the status word shares the array with earlier calls: start from zero
     SMAT_CUDA_TRY(cudaMemsetAsync(d->ctx.d_status, 0, sizeof(int), stream));
-    if (int rc = plan_count_async(rowptr, colidx, K, nnzb, 0, Mb, gsp, stream, &d->ctx)) return rc;
-    if (int rc = plan_fill_async(rowptr, colidx, K, nnzb, 0, Mb, gsp, steps, blk, packed, stream, &d->ctx)) return rc;
-    if (int rc = pack_values_async(rowptr, vals, gsp, steps, blk, packed, 0, Mb, nnzb, stream, &d->ctx)) return rc;
+    if (int rc = plan_count_async(rowptr, colidx, K, nnzb, 0, Mb, rg, gsp, stream, &d->ctx)) return rc;
+    if (int rc = plan_fill_async(rowptr, colidx, K, nnzb, 0, Mb, rg, gsp, steps, blk, packed, stream, &d->ctx)) return rc;
+    if (int rc = pack_values_async(rowptr, vals, gsp, steps, blk, packed, 0, Mb, rg, nnzb, stream, &d->ctx)) return rc;
     return launch_spmm(v, B, C, N, stream, &d->ctx);
 }

@@ -55,7 +55,13 @@ namespace {
 
 constexpr int RG = kPlanRowsPerGroup;  // block-rows per work item
 constexpr int CAP = kPlanBlocksPerStep;  // most blocks a step can carry
-constexpr int NL = 4;                  // loader warps
+#ifndef SMAT_UNIFORM_ISSUE
+#define SMAT_UNIFORM_ISSUE 1
+#endif
+#ifndef SMAT_NL
+#define SMAT_NL 4
+#endif
+constexpr int NL = SMAT_NL;            // loader warps
 #ifndef SMAT_L2_PREFETCH
 #define SMAT_L2_PREFETCH 1
 #endif
@@ -161,6 +167,9 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                     const int* __restrict__ rowptr, __half* __restrict__ C, int brow_begin, int brow_end, int rg, int N,
                     int n_tiles, int n_items, uint32_t panel_bytes, int* status) {
     static_assert(!(TS && NH == 2), "the panel ring and 32 accumulators do not fit tensor memory together");
+    // A loader waits on a stage's `empty` barrier by parity, which only tells phases apart while the waiter is
+    // less than two uses ahead of the consumers; with steps consumed in order that holds iff NL <= S.
+    static_assert(NL <= (int)Cfg<NH>::S, "more loader warps than stages would alias barrier phases");
     using G = Cfg<NH>;
     constexpr uint32_t S = G::S, PANEL_BYTES = G::PANEL_BYTES, STAGE_BYTES = G::STAGE_BYTES, OFF_STAGE = G::OFF_STAGE,
                        OFF_META = G::OFF_META, OFF_BAR = G::OFF_BAR, OFF_MISC = G::OFF_MISC;
@@ -266,25 +275,54 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
             for (int a = 0; a < U; a++) gen(rec[a]);
 #pragma unroll
             for (int a = 0; a < U / 2; a++) prefetch(rec[a]);
+#ifdef SMAT_PROFILE2
+            long long lw = 0, li = 0, lg = 0, ln = 0;
+#endif
             bool more = true;
             while (more) {
 #pragma unroll
                 for (int a = 0; a < U; a++) {
                     StepRec& r = rec[a];
                     if (!r.live) { more = false; break; }
+#ifdef SMAT_PROFILE2
+                    const long long l0 = clock64();
+#endif
                     prefetch(rec[(a + U / 2) % U]);
                     const uint32_t slot = r.st % S;
+#ifdef SMAT_PROFILE2
+                    const long long l1 = clock64();
+#endif
                     wait_bar(empty(slot), ((r.st / S) & 1) ^ 1, abort_addr, status, 1);
+#ifdef SMAT_PROFILE2
+                    const long long l2 = clock64();
+#endif
                     const uint32_t stage = base + OFF_STAGE + slot * STAGE_BYTES;
                     const uint32_t a_bytes = OPS_BYTES + (uint32_t)(__popc(r.d.z) + __popc(r.d.w)) * ABLK_BYTES;
                     st_shared_u32(base + OFF_META + slot * 8, r.d.z);
                     st_shared_u32(base + OFF_META + slot * 8 + 4, r.d.w);
-                    mbar_arrive_expect_tx(full(slot), panel_bytes + a_bytes);
-                    tma_load_2d(stage, &mapB, (int)r.d.x, r.tile * NT, full(slot));
+#ifdef SMAT_EXP_SKIP_PANEL  // timing experiment only (results are wrong): fetch the panel on every 4th step
+                    if (r.st & 12u) {
+                        mbar_arrive_expect_tx(full(slot), a_bytes);
+                    } else
+#endif
+                    {
+                        mbar_arrive_expect_tx(full(slot), panel_bytes + a_bytes);
+                        tma_load_2d(stage, &mapB, (int)r.d.x, r.tile * NT, full(slot));
+                    }
                     bulk_load(stage + PANEL_BYTES, packed + (size_t)r.d.y * 256, a_bytes, full(slot));
+#ifdef SMAT_PROFILE2
+                    const long long l3 = clock64();
+#endif
                     gen(r);  // this register set now follows the warp's step U positions ahead
+#ifdef SMAT_PROFILE2
+                    const long long l4 = clock64();
+                    lg += (l1 - l0) + (l4 - l3); lw += l2 - l1; li += l3 - l2; ln++;
+#endif
                 }
             }
+#ifdef SMAT_PROFILE2
+            if (blockIdx.x == 0 && j == 0) { g_prof2[10] = lw; g_prof2[11] = li; g_prof2[12] = lg; g_prof2[13] = ln; }
+#endif
         }
         __syncwarp();
     } else if (warp < NL + NC) {
@@ -337,12 +375,105 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
         }
         __syncwarp();
     } else if (warp < NL + NC + NM) {
-        // ------------------------------ MMA warp m: walks its part of every step's MMA list ------------------------------
+        // ------------------------------ MMA warp m ------------------------------
+#if SMAT_UNIFORM_ISSUE
+        // The whole warp walks the step's (sub-column, row) mask in lock-step and one elected lane issues.
+        // Every operand is derived from warp-uniform values (ballots of the mask words, the warp index
+        // broadcast from lane 0), so the descriptors can be formed without per-MMA transfers from
+        // per-thread registers -- measured: ~200 cycles per MMA for a single-lane loop over list entries.
+        {
+            const uint32_t m = (uint32_t)__shfl_sync(0xffffffffu, warp - NL - NC, 0);
+            const uint32_t P_HI = (uint32_t)(smem_desc_k_sw128(0) >> 32), B_HI = (uint32_t)(smem_desc_k_sw32(0) >> 32);
+            constexpr uint32_t IDESC_N0 = idesc_f16_f32(128, 0);  // the N field is added per run: N = 16 * length
+            const uint32_t rpo = (uint32_t)max(1, rg / NM);        // rows per owning warp, as the plan assigns them
+            const uint32_t rows_m = ((1u << rpo) - 1u) << (m * rpo);
+            const uint32_t own32 = (rows_m & 0xffffu) | (rows_m << 16);  // this warp's rows in both sub-columns of a mask word
+            const bool leader = elect_one();  // the lane that issues; fixed, so that its commits cover its MMAs
+            uint32_t st = 0, it = 0;
+#ifdef SMAT_PROFILE2
+            long long pw = 0, ps = 0, pm = 0, pc = 0, pn = 0, pk = 0;
+#endif
+            for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
+                const int g = item / n_tiles;
+                const int ns = __ldg(gsp + g + 1) - __ldg(gsp + g);
+                const uint32_t buf = it % NBUF;
+                wait_bar(acc_empty(buf), ((it / NBUF) & 1) ^ 1, abort_addr, status, 3);
+                tc_fence_after();
+                const uint32_t acc0 = tmem_base + buf * RG * 16 * NH;
+                for (int k = 0; k < ns; k++, st++) {
+                    const uint32_t slot = st % S;
+#ifdef SMAT_PROFILE2
+                    const long long m0 = clock64();
+#endif
+                    wait_bar(TS ? tfull(slot) : full(slot), (st / S) & 1, abort_addr, status, 4);
+                    tc_fence_after();
+#ifdef SMAT_PROFILE2
+                    const long long m1 = clock64();
+#endif
+                    const uint32_t stage = base + OFF_STAGE + slot * STAGE_BYTES;
+                    const uint32_t p_lo = (uint32_t)smem_desc_k_sw128(stage);               // panel, sub-column 0
+                    const uint32_t tpanel = tmem_base + TMEM_PANELS + slot * 32;            // its copy in tensor memory
+                    const uint32_t b_lo = (uint32_t)smem_desc_k_sw32(stage + PANEL_BYTES + OPS_BYTES);  // block slot 0
+                    const uint32_t wlo = ld_shared_u32(base + OFF_META + slot * 8);
+                    const uint32_t whi = ld_shared_u32(base + OFF_META + slot * 8 + 4);
+                    // ballots turn the (identical) per-lane words into values the compiler knows to be warp-uniform
+                    const uint32_t mw0 = __ballot_sync(0xffffffffu, (wlo >> lane) & 1u);
+                    const uint32_t mw1 = __ballot_sync(0xffffffffu, (whi >> lane) & 1u);
+                    uint32_t qbase = 0;
+#ifdef SMAT_PROFILE2
+                    const long long m2 = clock64() + (long long)(mw1 & 0u);
+                    pk += __popc(mw0 & own32) + __popc(mw1 & own32);
+#endif
+#pragma unroll
+                    for (int half = 0; half < 2; half++) {
+                        const uint32_t mw = half ? mw1 : mw0;
+                        uint32_t own = mw & own32;
+                        while (own) {
+                            const uint32_t b = (uint32_t)__ffs((int)own) - 1u;
+                            const uint32_t len = min((uint32_t)__ffs((int)~(own >> b)) - 1u, 4u);  // run of adjacent rows
+                            const uint32_t q = qbase + (uint32_t)__popc(mw & ((1u << b) - 1u));   // blocks are stored in mask-bit order
+                            const uint32_t r0 = b & 15u, sub = (uint32_t)half * 2u + (b >> 4);
+                            const uint32_t idesc = IDESC_N0 + ((2u * len) << 17);
+                            own &= ~(((1u << len) - 1u) << b);
+                            if (leader) {
+                                if (TS) {
+                                    mma_f16_ts_lohi(acc0 + r0 * 16, tpanel + sub * 8u, b_lo + q * (ABLK_BYTES >> 4), B_HI, idesc, 1u);
+                                } else {
+#pragma unroll
+                                    for (int h = 0; h < NH; h++)
+                                        mma_f16_ss_lohi(acc0 + (h * RG + r0) * 16, p_lo + sub * 2u + h * (128 * 128 >> 4), P_HI,
+                                                        b_lo + q * (ABLK_BYTES >> 4), B_HI, idesc, 1u);
+                                }
+                            }
+                        }
+                        qbase += (uint32_t)__popc(mw);
+                    }
+#ifdef SMAT_PROFILE2
+                    const long long m3 = clock64();
+#endif
+                    if (leader) tc_commit(empty(slot));
+#ifdef SMAT_PROFILE2
+                    const long long m4 = clock64();
+                    pw += m1 - m0; ps += m2 - m1; pm += m3 - m2; pc += m4 - m3; pn++;
+#endif
+                }
+                if (leader) tc_commit(acc_full(buf));
+            }
+#ifdef SMAT_PROFILE2
+            if (blockIdx.x == 0 && m == 0 && leader) { g_prof2[0] = pw; g_prof2[1] = ps; g_prof2[2] = pm; g_prof2[3] = pc; g_prof2[4] = pn; g_prof2[5] = pk; }
+#endif
+        }
+        __syncwarp();
+#else
+        // one lane walks its part of every step's MMA list
         if (lane == 0) {
             const uint32_t m = (uint32_t)(warp - NL - NC);
             const uint32_t P_HI = (uint32_t)(smem_desc_k_sw128(0) >> 32), B_HI = (uint32_t)(smem_desc_k_sw32(0) >> 32);
             constexpr uint32_t IDESC_N0 = idesc_f16_f32(128, 0);  // the N field is added per run: N = 16 * length
             uint32_t st = 0, it = 0;
+#ifdef SMAT_PROFILE2
+            long long pw = 0, ps = 0, pm = 0, pc = 0, pn = 0, pk = 0;
+#endif
             for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
                 const int g = item / n_tiles;
                 const int ns = __ldg(gsp + g + 1) - __ldg(gsp + g);
@@ -354,8 +485,14 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                 const uint32_t acc0 = tmem_base + buf * RG * 16 * NH;
                 for (int k = 0; k < ns; k++, st++) {
                     const uint32_t slot = st % S;
+#ifdef SMAT_PROFILE2
+                    const long long m0 = clock64();
+#endif
                     wait_bar(TS ? tfull(slot) : full(slot), (st / S) & 1, abort_addr, status, 4);
                     tc_fence_after();
+#ifdef SMAT_PROFILE2
+                    const long long m1 = clock64();
+#endif
                     const uint32_t stage = base + OFF_STAGE + slot * STAGE_BYTES;
                     const uint32_t ops = stage + PANEL_BYTES + m * 64;                      // this warp's region of the MMA list
                     const uint32_t p_lo = (uint32_t)smem_desc_k_sw128(stage);               // panel, sub-column 0
@@ -363,6 +500,9 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                     const uint32_t b_lo = (uint32_t)smem_desc_k_sw32(stage + PANEL_BYTES + OPS_BYTES);  // block slot 0
                     const uint32_t cnt = ld_shared_u16(ops);
                     uint32_t e = ld_shared_u16(ops + 2);
+#ifdef SMAT_PROFILE2
+                    const long long m2 = clock64() + (long long)(e & 0u);  // after the list header has arrived
+#endif
                     for (uint32_t i = 0; i < cnt; i++) {
                         const uint32_t cur = e;
                         e = ld_shared_u16(ops + 4 + 2 * i);  // next entry (the region has room for one past the last)
@@ -377,12 +517,23 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                                                 b_lo + q * (ABLK_BYTES >> 4), B_HI, idesc, 1u);
                         }
                     }
+#ifdef SMAT_PROFILE2
+                    const long long m3 = clock64();
+#endif
                     tc_commit(empty(slot));
+#ifdef SMAT_PROFILE2
+                    const long long m4 = clock64();
+                    pw += m1 - m0; ps += m2 - m1; pm += m3 - m2; pc += m4 - m3; pn++; pk += cnt;
+#endif
                 }
                 tc_commit(acc_full(buf));
             }
+#ifdef SMAT_PROFILE2
+            if (blockIdx.x == 0 && m == 0) { g_prof2[0] = pw; g_prof2[1] = ps; g_prof2[2] = pm; g_prof2[3] = pc; g_prof2[4] = pn; g_prof2[5] = pk; }
+#endif
         }
         __syncwarp();
+#endif
     } else {
         // ------------------------------ epilogue: tensor memory -> fp16 -> C ------------------------------
         const int quarter = warp & 3;  // a warp may only read tensor-memory lanes [32*(warp%4), +32)

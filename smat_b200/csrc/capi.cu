@@ -129,14 +129,16 @@ static int spmm_transient_plan(const void* vals, const int* rowptr, const int* c
     v.brow_end = brow_end;
     DeviceCtx* ctx = nullptr;
     if (int rc0 = get_device_ctx(&ctx)) return rc0;
-    const size_t rg = choose_rows_per_group(brow_end - brow_begin, N, ctx->sm_count);
+    const size_t rg = kPlanRowsPerGroup;
     const PlanSizes sz = plan_sizes(nnzb, brow_begin, brow_end, rg);
     v.n_groups = sz.n_groups;
     v.rg = rg;
     if (nnzb == 0) return launch_spmm(v, B, C, N, stream);
     void* buf = nullptr;
-    SMAT_CUDA_TRY(cudaMallocAsync(&buf, sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes + sz.packed_bytes, stream));
+    const size_t plan_bytes = (sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes + sz.packed_bytes + 255) / 256 * 256;
+    SMAT_CUDA_TRY(cudaMallocAsync(&buf, plan_bytes + fix_scratch_bytes(ctx->sm_count), stream));
     char* b = static_cast<char*>(buf);
+    v.fix_scratch = reinterpret_cast<float*>(b + plan_bytes);
     v.gsp = reinterpret_cast<int*>(b);
     v.steps = b + sz.gsp_bytes;
     v.blk = reinterpret_cast<int*>(b + sz.gsp_bytes + sz.steps_bytes);

@@ -341,6 +341,7 @@ struct smat_plan {
     PlanView v;
     void* buffer = nullptr;
     void* gsp_buffer = nullptr;
+    void* fix_buffer = nullptr;  // partial tiles of cut work items
     int device = -1;
 };
 
@@ -362,12 +363,16 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
         delete p;
         return rc0;
     }
-    const size_t rg = choose_rows_per_group(brow_end - brow_begin, N_hint, ctx->sm_count);
+    (void)N_hint;
+    const size_t rg = kPlanRowsPerGroup;  // items may be cut across CTAs, so the tallest group (most panel reuse) is best
     // phase 1 into a small buffer of its own; the step total then sizes the rest exactly
     PlanSizes sz = plan_sizes(nnzb, brow_begin, brow_end, rg);
     cudaError_t e = cudaGetDevice(&p->device);
     if (e == cudaSuccess) e = cudaMalloc(&p->gsp_buffer, sz.gsp_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&p->fix_buffer, fix_scratch_bytes(ctx->sm_count));
     if (e != cudaSuccess) {
+        cudaFree(p->gsp_buffer);
+        cudaFree(p->fix_buffer);
         delete p;
         return fail(SMAT_ERR_CUDA, "plan allocation failed: %s", cudaGetErrorString(e));
     }
@@ -386,6 +391,7 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
     }
     if (rc) {
         cudaFree(p->gsp_buffer);
+        cudaFree(p->fix_buffer);
         delete p;
         return rc;
     }
@@ -401,6 +407,7 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
     p->v.brow_end = brow_end;
     p->v.n_groups = sz.n_groups;
     p->v.rg = rg;
+    p->v.fix_scratch = static_cast<float*>(p->fix_buffer);
     rc = plan_fill_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, rg, gsp, const_cast<void*>(p->v.steps),
                          const_cast<int*>(p->v.blk), const_cast<void*>(p->v.packed), (cudaStream_t)stream);
     if (rc == SMAT_OK)
@@ -409,6 +416,7 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
     if (rc) {
         cudaFree(p->buffer);
         cudaFree(p->gsp_buffer);
+        cudaFree(p->fix_buffer);
         delete p;
         return rc;
     }
@@ -441,7 +449,9 @@ int smat_plan_destroy(smat_plan* plan) {
     if (!plan) return SMAT_OK;
     cudaError_t e = cudaFree(plan->buffer);
     const cudaError_t e2 = cudaFree(plan->gsp_buffer);
+    const cudaError_t e3 = cudaFree(plan->fix_buffer);
     if (e == cudaSuccess) e = e2;
+    if (e == cudaSuccess) e = e3;
     delete plan;
     if (e != cudaSuccess) return fail(SMAT_ERR_CUDA, "cudaFree failed: %s", cudaGetErrorString(e));
     return SMAT_OK;

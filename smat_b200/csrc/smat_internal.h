@@ -45,6 +45,8 @@ int encode_tensor_map_2d_f16(CUtensorMap* map, const void* base, uint64_t inner,
 constexpr int kPlanRowsPerGroup = 16;
 // Group height that yields at least `sm_count` work items when C is N columns wide, from {16, 8, 4}.
 size_t choose_rows_per_group(size_t block_rows, size_t N, int sm_count);
+// Bytes of that scratch: one partial tile of 2 x 16 block-rows x 16 x 128 fp32 per SM.
+inline size_t fix_scratch_bytes(int sm_count) { return (size_t)sm_count * (2 * 16 * 16 * 128) * sizeof(float); }
 // A step of the plan covers four consecutive block-columns and carries at most this many blocks.
 constexpr int kPlanBlocksPerStep = 24;
 // MMA-issuing threads of the kernel; each owns kPlanRowsPerGroup / kPlanOwners consecutive accumulators.
@@ -83,6 +85,9 @@ struct PlanView {
     const int* blk = nullptr;
     const void* packed = nullptr;
     size_t K = 0, nnzb = 0, brow_begin = 0, brow_end = 0, n_groups = 0, rg = kPlanRowsPerGroup;
+    // Scratch for work items that are computed in segments by several CTAs (null: items are never cut):
+    // fix_scratch_bytes(SMs) bytes, used by one launch at a time.
+    float* fix_scratch = nullptr;
 };
 
 // Work-list sizes for a block-row range and the asynchronous build on `stream` (plan.cu).

@@ -97,11 +97,6 @@ __device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
     return v;
 }
-__device__ __forceinline__ uint32_t ld_shared_u16(uint32_t addr) {
-    uint16_t v;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr) : "memory");
-    return v;
-}
 __device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
     asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
@@ -151,12 +146,53 @@ struct StepRec {
     uint4 d;      // {element column of the quad, first packed block, mask bits 0..31, mask bits 32..63}
 };
 
+// A segment: steps [k0, k1) of work item `item` (the first step of the item is steps[gs]).  parts > 1: the item is
+// computed in `parts` segments by as many CTAs; it is the tail-th item of the last round and this is part `part`.
+struct Seg {
+    int item, k0, k1, gs, parts, part, tail;
+};
+
+// What a CTA works on, in order: work items round-robin over the CTAs, as long as there is one for every CTA.  The
+// items left for the last round (fewer than CTAs) are each cut into P = #CTAs / #items-left segments of equal step
+// count, one per CTA, so that the last round keeps every SM busy and takes 1/P of an item's time.  All items are
+// cut at the same fractions and consecutive CTAs take consecutive segments, so the CTAs of a round still walk the
+// block-columns in step (what they fetch is shared through L2).  A cut item is assembled from fp32 partial tiles:
+// each CTA stores its segment's result to its scratch tile and a small second kernel adds them in order.
+struct SegGen {
+    const int* gsp;
+    int n_tiles, n_items, n_ctas, cta, item, n_full, P;
+    bool tail_done;
+    __device__ __forceinline__ bool next(Seg& s) {
+        if (item < n_full) {
+            const int g = item / n_tiles;
+            const int gs = __ldg(gsp + g), ns = __ldg(gsp + g + 1) - gs;
+            s.item = item; s.k0 = 0; s.k1 = ns; s.gs = gs; s.parts = 1; s.part = 0; s.tail = 0;
+            item += n_ctas;
+            return true;
+        }
+        if (tail_done) return false;
+        tail_done = true;
+        if (cta >= (n_items - n_full) * P) return false;
+        const int i = cta / P, j = cta - i * P;
+        const int g = (n_full + i) / n_tiles;
+        const int gs = __ldg(gsp + g), ns = __ldg(gsp + g + 1) - gs;
+        s.item = n_full + i; s.gs = gs; s.parts = P; s.part = j; s.tail = i;
+        s.k0 = (int)((long long)ns * j / P);
+        s.k1 = (int)((long long)ns * (j + 1) / P);
+        return true;
+    }
+};
+
+constexpr int kFixSlotFloats = 2 * RG * 16 * 128;  // one partial tile: up to 2 halves x 16 block-rows x 16 rows x 128 columns
+static_assert((size_t)kFixSlotFloats * sizeof(float) == (2 * 16 * 16 * 128) * sizeof(float), "fix_scratch_bytes() assumes this tile size");
+constexpr int kMinStepsPerCta = 16;                // an item is not cut into segments shorter than this (on average)
+
 // TS = false: both MMA operands from shared memory, two accumulator buffers (the epilogue of an item
 //   overlaps the main loop of the next).
 // TS = true: the panel is first copied shared -> tensor memory (tcgen05.cp, once per sub-column) and the
-//   MMAs read it from there, so the 4 KB panel no longer crosses the shared-memory port once per block
-//   (measured: ~16 instead of ~42 cycles per N=16 MMA per SM); the panel ring takes the tensor-memory
-//   columns of the second accumulator buffer, so there is one buffer and no epilogue overlap.
+//   MMAs read it from there, so the 4 KB panel no longer crosses the shared-memory port once per block;
+//   the panel ring takes the tensor-memory columns of the second accumulator buffer, so there is one
+//   buffer and no epilogue overlap.
 // NH = 1: a work item is 128 columns of C wide.  NH = 2: 256 columns -- every A block then feeds two
 //   independent MMAs (one per 128-column half, own accumulator), which doubles the MMA work per stage
 //   hand-over and halves the A traffic per MMA; the 32 accumulators fill tensor memory (one buffer).
@@ -165,7 +201,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __restrict__ packed,
                     const uint4* __restrict__ steps, const int* __restrict__ gsp,
                     const int* __restrict__ rowptr, __half* __restrict__ C, int brow_begin, int brow_end, int rg, int N,
-                    int n_tiles, int n_items, uint32_t panel_bytes, int* status) {
+                    int n_tiles, int n_items, int tail_parts, uint32_t panel_bytes, float* __restrict__ fix_scratch, int* status) {
     static_assert(!(TS && NH == 2), "the panel ring and 32 accumulators do not fit tensor memory together");
     // A loader waits on a stage's `empty` barrier by parity, which only tells phases apart while the waiter is
     // less than two uses ahead of the consumers; with steps consumed in order that holds iff NL <= S.
@@ -191,6 +227,15 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
 #ifdef SMAT_PROFILE
     const long long prof_t0 = clock64();
 #endif
+
+    // The CTA's share of the work (every role walks the same sequence of segments).
+    const int n_full = n_items / (int)gridDim.x * (int)gridDim.x;  // items of the complete rounds
+    auto make_gen = [&]() {
+        SegGen sg;
+        sg.gsp = gsp; sg.n_tiles = n_tiles; sg.n_items = n_items; sg.n_ctas = (int)gridDim.x; sg.cta = (int)blockIdx.x;
+        sg.item = (int)blockIdx.x; sg.n_full = n_full; sg.P = tail_parts; sg.tail_done = false;
+        return sg;
+    };
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < S; s++) { mbar_init(full(s), 1); mbar_init(empty(s), NM); mbar_init(tfull(s), 1); }
@@ -221,42 +266,26 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
     if (warp < NL) {
         // ------------------------------ loader warp j: every NL-th step ------------------------------
         const int j = warp;
-        // head of the step stream: current item, its first step in `steps`, its step count, the position
-        // of its first step in the CTA's sequence, and the next position this warp owns
-        int h_item = blockIdx.x, h_gs = 0, h_ns = 0, n_gs = 0, n_ns = 0;
-        uint32_t h_st0 = 0, h_next = (uint32_t)j;
-        auto load_item = [&](int item, int& gs, int& ns) {
-            if (item < n_items) {
-                const int g = item / n_tiles;
-                gs = __ldg(gsp + g);
-                ns = __ldg(gsp + g + 1) - gs;
-            } else {
-                gs = 0;
-                ns = 0;
-            }
-        };
-        load_item(h_item, h_gs, h_ns);
-        load_item(h_item + (int)gridDim.x, n_gs, n_ns);
-
         // Software pipeline over the warp's steps, unrolled U times so that every record lives in fixed
         // registers (a record whose descriptor load is still in flight is never copied): the descriptor
         // of position i + U is requested while position i is consumed.  One thread per warp works.
         if (lane == 0) {
+            SegGen sg = make_gen();
+            Seg cs;
+            bool have = sg.next(cs);
+            uint32_t h_st0 = 0, h_next = (uint32_t)j;  // sequence position of the segment's first step; next position of this warp
             constexpr int U = 8;
             StepRec rec[U];
             auto gen = [&](StepRec& r) {  // next step of this warp; requests its descriptor
-                while (h_item < n_items && h_next >= h_st0 + (uint32_t)h_ns) {
-                    h_st0 += (uint32_t)h_ns;
-                    h_item += gridDim.x;
-                    h_gs = n_gs;
-                    h_ns = n_ns;
-                    load_item(h_item + (int)gridDim.x, n_gs, n_ns);
+                while (have && h_next >= h_st0 + (uint32_t)(cs.k1 - cs.k0)) {
+                    h_st0 += (uint32_t)(cs.k1 - cs.k0);
+                    have = sg.next(cs);
                 }
-                r.live = h_item < n_items;
-                if (r.live) {
-                    r.tile = h_item % n_tiles;
+                r.live = have;
+                if (have) {
+                    r.tile = cs.item % n_tiles;
                     r.st = h_next;
-                    r.d = __ldg(steps + h_gs + (int)(h_next - h_st0));
+                    r.d = __ldg(steps + cs.gs + cs.k0 + (int)(h_next - h_st0));
                     h_next += NL;
                 }
             };
@@ -300,15 +329,8 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                     const uint32_t a_bytes = OPS_BYTES + (uint32_t)(__popc(r.d.z) + __popc(r.d.w)) * ABLK_BYTES;
                     st_shared_u32(base + OFF_META + slot * 8, r.d.z);
                     st_shared_u32(base + OFF_META + slot * 8 + 4, r.d.w);
-#ifdef SMAT_EXP_SKIP_PANEL  // timing experiment only (results are wrong): fetch the panel on every 4th step
-                    if (r.st & 12u) {
-                        mbar_arrive_expect_tx(full(slot), a_bytes);
-                    } else
-#endif
-                    {
-                        mbar_arrive_expect_tx(full(slot), panel_bytes + a_bytes);
-                        tma_load_2d(stage, &mapB, (int)r.d.x, r.tile * NT, full(slot));
-                    }
+                    mbar_arrive_expect_tx(full(slot), panel_bytes + a_bytes);
+                    tma_load_2d(stage, &mapB, (int)r.d.x, r.tile * NT, full(slot));
                     bulk_load(stage + PANEL_BYTES, packed + (size_t)r.d.y * 256, a_bytes, full(slot));
 #ifdef SMAT_PROFILE2
                     const long long l3 = clock64();
@@ -330,25 +352,15 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
         if (TS && lane == 0) {
             const uint32_t j = (uint32_t)(warp - NL);
             uint32_t st = 0;
-#ifdef SMAT_PROFILE2
-            long long cw = 0, cc = 0, cm = 0, cn = 0;
-#endif
-            for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-                const int g = item / n_tiles;
-                const int ns = __ldg(gsp + g + 1) - __ldg(gsp + g);
-                for (int k = 0; k < ns; k++, st++) {
+            SegGen sg = make_gen();
+            Seg cs;
+            while (sg.next(cs)) {
+                for (int k = cs.k0; k < cs.k1; k++, st++) {
                     const uint32_t slot = st % S;
                     // Every copier observes every stage in order, although it copies only its own: a
                     // parity wait is only meaningful for a waiter that is less than one phase away, and
                     // a copier that skipped stages could meet a barrier one whole use behind.
-#ifdef SMAT_PROFILE2
-                    const long long c0 = clock64();
-#endif
                     wait_bar(full(slot), (st / S) & 1, abort_addr, status, 2);
-#ifdef SMAT_PROFILE2
-                    const long long c1 = clock64();
-                    cw += c1 - c0;
-#endif
                     if (st % NC != j) continue;
                     tc_fence_after();
                     const uint32_t mlo = ld_shared_u32(base + OFF_META + slot * 8);
@@ -359,33 +371,21 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                     if (mlo >> 16) tc_cp_128x256b(tdst + 8, pdesc + 2);
                     if (mhi & 0xffffu) tc_cp_128x256b(tdst + 16, pdesc + 4);
                     if (mhi >> 16) tc_cp_128x256b(tdst + 24, pdesc + 6);
-#ifdef SMAT_PROFILE2
-                    const long long c2 = clock64();
-#endif
                     tc_commit(tfull(slot));
-#ifdef SMAT_PROFILE2
-                    const long long c3 = clock64();
-                    cc += c2 - c1; cm += c3 - c2; cn++;
-#endif
                 }
             }
-#ifdef SMAT_PROFILE2
-            if (blockIdx.x == 0 && j == 0) { g_prof2[6] = cw; g_prof2[7] = cc; g_prof2[8] = cm; g_prof2[9] = cn; }
-#endif
         }
         __syncwarp();
     } else if (warp < NL + NC + NM) {
         // ------------------------------ MMA warp m ------------------------------
-#if SMAT_UNIFORM_ISSUE
-        // The whole warp walks the step's (sub-column, row) mask in lock-step and one elected lane issues.
-        // Every operand is derived from warp-uniform values (ballots of the mask words, the warp index
-        // broadcast from lane 0), so the descriptors can be formed without per-MMA transfers from
-        // per-thread registers -- measured: ~200 cycles per MMA for a single-lane loop over list entries.
+        // The whole warp walks the step's (sub-column, row) mask in lock-step and one elected lane issues;
+        // the mask words reach the loop as ballots, i.e. as values the compiler knows to be warp-uniform.
+        // (Measured: a single lane walking a precomputed list of MMAs from shared memory was ~20 % slower.)
         {
             const uint32_t m = (uint32_t)__shfl_sync(0xffffffffu, warp - NL - NC, 0);
             const uint32_t P_HI = (uint32_t)(smem_desc_k_sw128(0) >> 32), B_HI = (uint32_t)(smem_desc_k_sw32(0) >> 32);
             constexpr uint32_t IDESC_N0 = idesc_f16_f32(128, 0);  // the N field is added per run: N = 16 * length
-            const uint32_t rpo = (uint32_t)max(1, rg / NM);        // rows per owning warp, as the plan assigns them
+            const uint32_t rpo = (uint32_t)max(1, rg / NM);        // rows per owning warp
             const uint32_t rows_m = ((1u << rpo) - 1u) << (m * rpo);
             const uint32_t own32 = (rows_m & 0xffffu) | (rows_m << 16);  // this warp's rows in both sub-columns of a mask word
             const bool leader = elect_one();  // the lane that issues; fixed, so that its commits cover its MMAs
@@ -393,14 +393,16 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
 #ifdef SMAT_PROFILE2
             long long pw = 0, ps = 0, pm = 0, pc = 0, pn = 0, pk = 0;
 #endif
-            for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
-                const int g = item / n_tiles;
-                const int ns = __ldg(gsp + g + 1) - __ldg(gsp + g);
+            // One segment = steps [k0, k1) of an item.  Kept as a plain counted loop called from two plain loops
+            // (measured: driving it from the segment generator's control flow made the issue loop ~35 % slower).
+            auto run_segment = [&](const int k0, const int k1) {
                 const uint32_t buf = it % NBUF;
+                // the accumulators were zeroed by the epilogue after it read them (or at kernel start), so
+                // every MMA accumulates and runs may span rows with and without earlier blocks
                 wait_bar(acc_empty(buf), ((it / NBUF) & 1) ^ 1, abort_addr, status, 3);
                 tc_fence_after();
                 const uint32_t acc0 = tmem_base + buf * RG * 16 * NH;
-                for (int k = 0; k < ns; k++, st++) {
+                for (int k = k0; k < k1; k++, st++) {
                     const uint32_t slot = st % S;
 #ifdef SMAT_PROFILE2
                     const long long m0 = clock64();
@@ -416,7 +418,6 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                     const uint32_t b_lo = (uint32_t)smem_desc_k_sw32(stage + PANEL_BYTES + OPS_BYTES);  // block slot 0
                     const uint32_t wlo = ld_shared_u32(base + OFF_META + slot * 8);
                     const uint32_t whi = ld_shared_u32(base + OFF_META + slot * 8 + 4);
-                    // ballots turn the (identical) per-lane words into values the compiler knows to be warp-uniform
                     const uint32_t mw0 = __ballot_sync(0xffffffffu, (wlo >> lane) & 1u);
                     const uint32_t mw1 = __ballot_sync(0xffffffffu, (whi >> lane) & 1u);
                     uint32_t qbase = 0;
@@ -440,7 +441,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                                     mma_f16_ts_lohi(acc0 + r0 * 16, tpanel + sub * 8u, b_lo + q * (ABLK_BYTES >> 4), B_HI, idesc, 1u);
                                 } else {
 #pragma unroll
-                                    for (int h = 0; h < NH; h++)
+                                    for (int h = 0; h < NH; h++)  // one MMA per 128-column half, each into its own accumulators
                                         mma_f16_ss_lohi(acc0 + (h * RG + r0) * 16, p_lo + sub * 2u + h * (128 * 128 >> 4), P_HI,
                                                         b_lo + q * (ABLK_BYTES >> 4), B_HI, idesc, 1u);
                                 }
@@ -458,109 +459,55 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
 #endif
                 }
                 if (leader) tc_commit(acc_full(buf));
+                ++it;
+            };
+            for (int item = blockIdx.x; item < n_full; item += gridDim.x) {  // the complete rounds: whole items
+                const int g = item / n_tiles;
+                run_segment(0, __ldg(gsp + g + 1) - __ldg(gsp + g));
+            }
+            if ((int)blockIdx.x < (n_items - n_full) * tail_parts) {  // the last round: one segment of an item
+                const int i = (int)blockIdx.x / tail_parts, j = (int)blockIdx.x - i * tail_parts;
+                const int g = (n_full + i) / n_tiles;
+                const int ns = __ldg(gsp + g + 1) - __ldg(gsp + g);
+                run_segment((int)((long long)ns * j / tail_parts), (int)((long long)ns * (j + 1) / tail_parts));
             }
 #ifdef SMAT_PROFILE2
             if (blockIdx.x == 0 && m == 0 && leader) { g_prof2[0] = pw; g_prof2[1] = ps; g_prof2[2] = pm; g_prof2[3] = pc; g_prof2[4] = pn; g_prof2[5] = pk; }
 #endif
         }
         __syncwarp();
-#else
-        // one lane walks its part of every step's MMA list
-        if (lane == 0) {
-            const uint32_t m = (uint32_t)(warp - NL - NC);
-            const uint32_t P_HI = (uint32_t)(smem_desc_k_sw128(0) >> 32), B_HI = (uint32_t)(smem_desc_k_sw32(0) >> 32);
-            constexpr uint32_t IDESC_N0 = idesc_f16_f32(128, 0);  // the N field is added per run: N = 16 * length
-            uint32_t st = 0, it = 0;
-#ifdef SMAT_PROFILE2
-            long long pw = 0, ps = 0, pm = 0, pc = 0, pn = 0, pk = 0;
-#endif
-            for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
-                const int g = item / n_tiles;
-                const int ns = __ldg(gsp + g + 1) - __ldg(gsp + g);
-                const uint32_t buf = it % NBUF;
-                // the accumulators were zeroed by the epilogue after it read them (or at kernel start), so
-                // every MMA accumulates and runs may span rows with and without earlier blocks
-                wait_bar(acc_empty(buf), ((it / NBUF) & 1) ^ 1, abort_addr, status, 3);
-                tc_fence_after();
-                const uint32_t acc0 = tmem_base + buf * RG * 16 * NH;
-                for (int k = 0; k < ns; k++, st++) {
-                    const uint32_t slot = st % S;
-#ifdef SMAT_PROFILE2
-                    const long long m0 = clock64();
-#endif
-                    wait_bar(TS ? tfull(slot) : full(slot), (st / S) & 1, abort_addr, status, 4);
-                    tc_fence_after();
-#ifdef SMAT_PROFILE2
-                    const long long m1 = clock64();
-#endif
-                    const uint32_t stage = base + OFF_STAGE + slot * STAGE_BYTES;
-                    const uint32_t ops = stage + PANEL_BYTES + m * 64;                      // this warp's region of the MMA list
-                    const uint32_t p_lo = (uint32_t)smem_desc_k_sw128(stage);               // panel, sub-column 0
-                    const uint32_t tpanel = tmem_base + TMEM_PANELS + slot * 32;            // its copy in tensor memory
-                    const uint32_t b_lo = (uint32_t)smem_desc_k_sw32(stage + PANEL_BYTES + OPS_BYTES);  // block slot 0
-                    const uint32_t cnt = ld_shared_u16(ops);
-                    uint32_t e = ld_shared_u16(ops + 2);
-#ifdef SMAT_PROFILE2
-                    const long long m2 = clock64() + (long long)(e & 0u);  // after the list header has arrived
-#endif
-                    for (uint32_t i = 0; i < cnt; i++) {
-                        const uint32_t cur = e;
-                        e = ld_shared_u16(ops + 4 + 2 * i);  // next entry (the region has room for one past the last)
-                        const uint32_t q = cur & 31u, r0 = (cur >> 5) & 15u, len = ((cur >> 9) & 3u) + 1u, sub = (cur >> 11) & 3u;
-                        const uint32_t idesc = IDESC_N0 + ((2u * len) << 17);
-                        if (TS) {
-                            mma_f16_ts_lohi(acc0 + r0 * 16, tpanel + sub * 8u, b_lo + q * (ABLK_BYTES >> 4), B_HI, idesc, 1u);
-                        } else {
-#pragma unroll
-                            for (int h = 0; h < NH; h++)  // one MMA per 128-column half, each into its own accumulators
-                                mma_f16_ss_lohi(acc0 + (h * RG + r0) * 16, p_lo + sub * 2u + h * (128 * 128 >> 4), P_HI,
-                                                b_lo + q * (ABLK_BYTES >> 4), B_HI, idesc, 1u);
-                        }
-                    }
-#ifdef SMAT_PROFILE2
-                    const long long m3 = clock64();
-#endif
-                    tc_commit(empty(slot));
-#ifdef SMAT_PROFILE2
-                    const long long m4 = clock64();
-                    pw += m1 - m0; ps += m2 - m1; pm += m3 - m2; pc += m4 - m3; pn++; pk += cnt;
-#endif
-                }
-                tc_commit(acc_full(buf));
-            }
-#ifdef SMAT_PROFILE2
-            if (blockIdx.x == 0 && m == 0) { g_prof2[0] = pw; g_prof2[1] = ps; g_prof2[2] = pm; g_prof2[3] = pc; g_prof2[4] = pn; g_prof2[5] = pk; }
-#endif
-        }
-        __syncwarp();
-#endif
     } else {
         // ------------------------------ epilogue: tensor memory -> fp16 -> C ------------------------------
         const int quarter = warp & 3;  // a warp may only read tensor-memory lanes [32*(warp%4), +32)
         const bool odd = lane & 1;
+        const int et = quarter * 32 + lane;  // index among the 128 epilogue threads = column within a 128-column half
         uint32_t it = 0;
-        for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
-            const int g = item / n_tiles, t = item - g * n_tiles;
+        SegGen sg = make_gen();
+        Seg cs;
+        for (; sg.next(cs); ++it) {
+            const int g = cs.item / n_tiles, t = cs.item - g * n_tiles;
             const int r0 = brow_begin + g * rg;
             const int nrows = min(rg, brow_end - r0);
             const int lo = (lane < nrows) ? __ldg(rowptr + r0 + lane) : 0;
             const int hi = (lane < nrows) ? __ldg(rowptr + r0 + lane + 1) : 0;
             const uint32_t nonempty = __ballot_sync(0xffffffffu, hi > lo);
             const uint32_t buf = it % NBUF;
+            const bool partial = cs.parts > 1;
+            float* part_dst = fix_scratch + (size_t)blockIdx.x * (size_t)kFixSlotFloats;  // this CTA's scratch tile
             if (lane == 0) wait_bar(acc_full(buf), (it / NBUF) & 1, abort_addr, status, 6);
             __syncwarp();
             tc_fence_after();
             for (int r = 0; r < nrows; r++) {
 #pragma unroll
                 for (int h = 0; h < NH; h++) {
-                    const int n = t * NT + h * 128 + quarter * 32 + lane;
+                    const int n = t * NT + h * 128 + et;
                     uint32_t v[16];
                     if ((nonempty >> r) & 1u) {
                         const uint32_t taddr =
                             tmem_base + ((uint32_t)(quarter * 32) << 16) + ((buf * NH + h) * RG + (uint32_t)r) * 16;
                         tmem_ld_x16(taddr, v);
                         tmem_ld_wait();
-                        tmem_zero_x16(taddr);  // leave the accumulator zeroed for the next item that uses this buffer
+                        tmem_zero_x16(taddr);  // leave the accumulator zeroed for the next segment that uses this buffer
                     } else {
 #pragma unroll
                         for (int i = 0; i < 16; i++) v[i] = 0u;
@@ -571,6 +518,12 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(acc_empty(buf));
+                    }
+                    if (partial) {
+                        float* d = part_dst + ((size_t)(h * RG + r) * 16) * 128 + et;
+#pragma unroll
+                        for (int i = 0; i < 16; i++) d[(size_t)i * 128] = __uint_as_float(v[i]);
+                        continue;
                     }
                     __half* crow = C + ((size_t)(r0 - brow_begin + r) * 16 + (odd ? 8 : 0)) * (size_t)N + (size_t)(n & ~1);
 #pragma unroll
@@ -609,6 +562,37 @@ __global__ void zero_rows_kernel(uint4* dst, size_t n16) {
     for (; i < n16; i += stride) dst[i] = make_uint4(0, 0, 0, 0);
 }
 
+// Adds up the partial tiles of the work items that the main kernel computed in `parts` segments (the items of its
+// last round; segment j of the i-th of them is in scratch tile i * parts + j) and writes their part of C.
+// One block of (128 columns x 4) threads per item.
+template <int NH>
+__global__ void __launch_bounds__(512) sum_cut_items_kernel(const float* __restrict__ scratch, __half* __restrict__ C, int brow_begin,
+                                                           int brow_end, int rg, int N, int n_tiles, int n_full, int parts) {
+    const int item = n_full + (int)blockIdx.x;
+    const int g = item / n_tiles, t = item - g * n_tiles;
+    const int r0 = brow_begin + g * rg;
+    const int nrows = min(rg, brow_end - r0);
+    const float* tile0 = scratch + (size_t)blockIdx.x * parts * (size_t)kFixSlotFloats;
+    for (int r = (int)threadIdx.y; r < nrows; r += (int)blockDim.y) {
+#pragma unroll
+        for (int h = 0; h < NH; h++) {
+            const int n = t * (128 * NH) + h * 128 + (int)threadIdx.x;
+            if (n >= N) continue;
+            float acc[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) acc[i] = 0.0f;
+            for (int j = 0; j < parts; j++) {
+                const float* src = tile0 + (size_t)j * kFixSlotFloats + ((size_t)(h * RG + r) * 16) * 128 + threadIdx.x;
+#pragma unroll
+                for (int i = 0; i < 16; i++) acc[i] += __ldg(src + (size_t)i * 128);
+            }
+            __half* ccol = C + ((size_t)(r0 - brow_begin + r) * 16) * (size_t)N + (size_t)n;
+#pragma unroll
+            for (int i = 0; i < 16; i++) ccol[(size_t)i * (size_t)N] = __float2half_rn(acc[i]);
+        }
+    }
+}
+
 }  // namespace
 
 #ifdef SMAT_PROFILE2
@@ -643,13 +627,29 @@ int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStre
         SMAT_CUDA_TRY(cudaGetLastError());
         return SMAT_OK;
     }
-    // Item width: 256 columns when C is at least that wide AND the items are long (every A block then
-    // feeds two MMAs, but there is a single accumulator buffer, so the epilogue is not overlapped);
-    // matrices with few blocks per group, or too few groups to give every SM a 256-column item, keep
-    // 128-column items with two buffers.
+    // Item width: 256 columns (every A block then feeds two MMAs; one accumulator buffer, so the epilogue is not
+    // overlapped) or 128.  Wide items need C that wide and long items; between the two the estimated time decides:
+    // rounds of items over the SMs -- the last round counting 1/P when its items are cut into P segments -- times
+    // the measured cost of an item (a wide one costs 1.95 narrow ones).
+    const bool split = plan.fix_scratch != nullptr;
+    const size_t sms = (size_t)ctx->sm_count;
+    auto tail_parts = [&](size_t items) -> size_t {  // segments per item of the last round
+        const size_t left = items % sms;
+        if (!split || left == 0) return 1;
+        size_t est_steps = plan.nnzb / plan.n_groups;  // steps per item: at most one per block and one per 64 columns
+        if (plan.K / 64 < est_steps) est_steps = plan.K / 64;
+        size_t P = sms / left;
+        if (P > est_steps / kMinStepsPerCta) P = est_steps / kMinStepsPerCta;
+        return P < 1 ? 1 : P;
+    };
+    auto rounds = [&](size_t items) { return (double)(items / sms) + (items % sms ? 1.0 / (double)tail_parts(items) : 0.0); };
     int variant = g_spmm_variant;
-    if (variant == 0)
-        variant = (N >= 256 && plan.nnzb / plan.n_groups >= 256 && plan.n_groups * ((N + 255) / 256) >= (size_t)ctx->sm_count) ? 3 : 1;
+    if (variant == 0) {
+        variant = 1;
+        if (N >= 256 && plan.nnzb / plan.n_groups >= 256 &&
+            1.95 * rounds(plan.n_groups * ((N + 255) / 256)) < rounds(plan.n_groups * ((N + 127) / 128)))
+            variant = 3;
+    }
     const size_t NTI = variant == 3 ? 256 : 128;
     const uint32_t panel_rows = (uint32_t)(N < NTI ? N : NTI);
     CUtensorMap mapB;
@@ -657,20 +657,35 @@ int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStre
     const int n_tiles = (int)((N + NTI - 1) / NTI);
     const size_t n_items = plan.n_groups * (size_t)n_tiles;
     if (n_items > (size_t)INT_MAX) return fail(SMAT_ERR_RANGE, "too many work items (%zu)", n_items);
-    const int grid = (int)(n_items < (size_t)ctx->sm_count ? n_items : (size_t)ctx->sm_count);
+    // one CTA per SM; fewer only when there are fewer items than SMs and they are not cut
+    const int parts = (int)tail_parts(n_items);
+    const int grid = (int)((parts > 1 || n_items > sms) ? sms : n_items);
+    const int n_full = (int)(n_items / (size_t)grid * (size_t)grid);
     auto launch = [&](auto kernel, uint32_t smem_bytes) -> int {
         SMAT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
         kernel<<<grid, kThreads, smem_bytes, stream>>>(
             mapB, reinterpret_cast<const uint8_t*>(plan.packed), reinterpret_cast<const uint4*>(plan.steps), plan.gsp,
             plan.rowptr, reinterpret_cast<__half*>(C), (int)plan.brow_begin, (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles,
-            (int)n_items, panel_rows * 128u, ctx->d_status);
+            (int)n_items, parts, panel_rows * 128u, plan.fix_scratch, ctx->d_status);
         count_launch();
         SMAT_CUDA_TRY(cudaGetLastError());
         return SMAT_OK;
     };
-    if (variant == 3) return launch(spmm_bcsr_tc_kernel<false, 2>, Cfg<2>::SMEM_BYTES);
-    if (variant == 2) return launch(spmm_bcsr_tc_kernel<true, 1>, Cfg<1>::SMEM_BYTES);
-    return launch(spmm_bcsr_tc_kernel<false, 1>, Cfg<1>::SMEM_BYTES);
+    int rc;
+    if (variant == 3) rc = launch(spmm_bcsr_tc_kernel<false, 2>, Cfg<2>::SMEM_BYTES);
+    else if (variant == 2) rc = launch(spmm_bcsr_tc_kernel<true, 1>, Cfg<1>::SMEM_BYTES);
+    else rc = launch(spmm_bcsr_tc_kernel<false, 1>, Cfg<1>::SMEM_BYTES);
+    if (rc != SMAT_OK || parts == 1) return rc;
+    const int cut_items = (int)n_items - n_full;
+    if (variant == 3)
+        sum_cut_items_kernel<2><<<cut_items, dim3(128, 4), 0, stream>>>(plan.fix_scratch, reinterpret_cast<__half*>(C), (int)plan.brow_begin,
+                                                                       (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles, n_full, parts);
+    else
+        sum_cut_items_kernel<1><<<cut_items, dim3(128, 4), 0, stream>>>(plan.fix_scratch, reinterpret_cast<__half*>(C), (int)plan.brow_begin,
+                                                                       (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles, n_full, parts);
+    count_launch();
+    SMAT_CUDA_TRY(cudaGetLastError());
+    return SMAT_OK;
 }
 
 }  // namespace smat

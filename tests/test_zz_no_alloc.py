@@ -32,20 +32,28 @@ def _both(p, brp, bci, bv, B_nk):
     return want.data.cpu().numpy(), got.data.cpu().numpy()
 
 
+def _same(a, b):
+    """The allocating entry point may compute a work item in parts (fp32 partial tiles added up afterwards),
+    the static one never does: equal up to the one rounding of differently grouped fp32 sums to fp16."""
+    a = a.astype(np.float32)
+    b = b.astype(np.float32)
+    return bool(np.all(np.abs(a - b) <= 2.0 ** -9 * np.maximum(np.abs(a), np.abs(b)) + 1e-3 * float(np.abs(a).max())))
+
+
 def test_static_scratch_entry_matches_allocating_entry_twice():
     rng = np.random.default_rng(5)
     # first call: the band configuration (2284 blocks)
     p = gen.make_config("band")
     brp, bci, bv = oracle.csr_to_bcsr(p.M, p.K, p.rowptr, p.colidx, p.vals)
     want, got = _both(p, brp, bci, bv, p.B_nk)
-    assert np.array_equal(want.view(np.uint16), got.view(np.uint16))
+    assert _same(want, got)
     # second call right after it: another matrix and width, so leftovers of the first call in the
     # shared array would show
     p2 = gen.make_config("uniform", scale=0.03)
     brp2, bci2, bv2 = oracle.csr_to_bcsr(p2.M, p2.K, p2.rowptr, p2.colidx, p2.vals)
     B2 = rng.standard_normal((136, p2.K)).astype(np.float16)
     want2, got2 = _both(p2, brp2, bci2, bv2, B2)
-    assert np.array_equal(want2.view(np.uint16), got2.view(np.uint16))
+    assert _same(want2, got2)
     # and against the oracle, like every other parity test (max relative error 1e-2)
     ref = oracle.bcsr_spmm(bv2, brp2, bci2, B2, p2.M, 136, p2.K)
     mag = oracle.bcsr_spmm(np.abs(bv2), brp2, bci2, np.abs(B2), p2.M, 136, p2.K)

@@ -96,7 +96,6 @@ plan_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx, int 
         int cur = beg;
         int steps_done = 0, blocks_done = 0;
         const int gs = FILL ? __ldg(gsp + g) : 0;
-        const int rpo = max(1, rg / kPlanOwners);  // rows per owning MMA warp
         for (int w0 = 0; w0 < Kb; w0 += kWindow) {
             const int cur_before = cur;
             mark_window(colidx, cur, end, w0, masks, warp, lane);
@@ -133,32 +132,9 @@ plan_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx, int 
                             part |= low;
                             m64 ^= low;
                         }
-                        // position of the step's record in the packed stream, in 256-byte units
-                        const uint32_t pos = (uint32_t)(gs + s) * (kPlanOpBytes / 256) + 2u * (uint32_t)(gfirst - rfirst + b);
+                        // position of the step's first block in the packed stream, in 256-byte units
+                        const uint32_t pos = 2u * (uint32_t)(gfirst - rfirst + b);
                         steps[gs + s] = make_uint4((uint32_t)(w0 + i0 + 4 * qd) << 4, pos, (uint32_t)part, (uint32_t)(part >> 32));
-                        // MMA list of the step: runs of vertically adjacent blocks, per owner of 16/kPlanOwners rows
-                        uint16_t* ops = reinterpret_cast<uint16_t*>(packed + (size_t)pos * 256);
-                        int count[kPlanOwners] = {};
-                        int last_r = -2, last_sub = -1, last_owner = -1, last_len = 0;
-                        unsigned long long rest = part;
-                        for (int q = 0; rest; q++) {
-                            const int bit = __ffsll((long long)rest) - 1;
-                            rest &= rest - 1;
-                            const int r = bit & 15, sub = bit >> 4, owner = r / rpo;
-                            if (owner == last_owner && sub == last_sub && r == last_r + 1 && last_len < 4) {  // the length field holds 1..4
-                                last_len++;  // extend the run: entry stays where it is, length field grows
-                                ops[owner * 32 + count[owner]] += (uint16_t)(1u << 9);
-                            } else {
-                                count[owner]++;
-                                ops[owner * 32 + count[owner]] = (uint16_t)(q | (r << 5) | (sub << 11));
-                                last_len = 1;
-                            }
-                            last_r = r;
-                            last_sub = sub;
-                            last_owner = owner;
-                        }
-#pragma unroll
-                        for (int o = 0; o < kPlanOwners; o++) ops[o * 32] = (uint16_t)count[o];
                         s++;
                         b += __popcll(part);
                     }
@@ -214,7 +190,7 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(int* data, int n) {
     }
 }
 
-// One warp per step: copies the step's value blocks behind its MMA list in the packed stream; lane l moves
+// One warp per step: copies the step's value blocks to their place in the packed stream; lane l moves
 // the 16-byte chunk l of a block (row l/2, half l%2) to chunk l ^ ((l >> 3) & 1), i.e. the 32-byte swizzle.
 __global__ void __launch_bounds__(256) pack_kernel(const uint4* __restrict__ vals, const int* __restrict__ blk,
                                                   const int* __restrict__ gsp, const uint4* __restrict__ steps,
@@ -227,8 +203,8 @@ __global__ void __launch_bounds__(256) pack_kernel(const uint4* __restrict__ val
     for (int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < total; i += warps) {
         const uint4 d = __ldg(steps + i);
         const int cnt = __popc(d.z) + __popc(d.w);
-        const int first = rfirst + (int)((d.y - (uint32_t)i * (kPlanOpBytes / 256)) >> 1);  // position of the step's first block in blk
-        uint4* dst = reinterpret_cast<uint4*>(packed + (size_t)d.y * 256 + kPlanOpBytes);
+        const int first = rfirst + (int)(d.y >> 1);  // position of the step's first block in blk
+        uint4* dst = reinterpret_cast<uint4*>(packed + (size_t)d.y * 256);
         for (int q = 0; q < cnt; q++) {
             const int src = __ldg(blk + first + q);
             dst[q * 32 + (lane ^ ((lane >> 3) & 1))] = __ldg(vals + (size_t)src * 32 + lane);
@@ -279,7 +255,7 @@ PlanSizes plan_sizes(size_t nnzb, size_t brow_begin, size_t brow_end, size_t rg,
     const size_t steps = max_steps ? max_steps : (nnzb ? nnzb : 1);
     s.steps_bytes = (steps * sizeof(uint4) + 255) / 256 * 256;
     s.blk_bytes = ((nnzb ? nnzb : 1) * sizeof(int) + 255) / 256 * 256;
-    s.packed_bytes = (nnzb ? nnzb : 1) * 512 + steps * kPlanOpBytes;
+    s.packed_bytes = (nnzb ? nnzb : 1) * 512;
     return s;
 }
 
@@ -408,6 +384,7 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
     p->v.n_groups = sz.n_groups;
     p->v.rg = rg;
     p->v.fix_scratch = static_cast<float*>(p->fix_buffer);
+    p->v.total_steps = (size_t)(total_steps > 0 ? total_steps : 0);
     rc = plan_fill_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, rg, gsp, const_cast<void*>(p->v.steps),
                          const_cast<int*>(p->v.blk), const_cast<void*>(p->v.packed), (cudaStream_t)stream);
     if (rc == SMAT_OK)

@@ -49,18 +49,15 @@ size_t choose_rows_per_group(size_t block_rows, size_t N, int sm_count);
 inline size_t fix_scratch_bytes(int sm_count) { return (size_t)sm_count * (2 * 16 * 16 * 128) * sizeof(float); }
 // A step of the plan covers four consecutive block-columns and carries at most this many blocks.
 constexpr int kPlanBlocksPerStep = 24;
-// MMA-issuing threads of the kernel; each owns kPlanRowsPerGroup / kPlanOwners consecutive accumulators.
+// MMA-issuing warps of the kernel; each owns kPlanRowsPerGroup / kPlanOwners consecutive accumulators.
 #ifndef SMAT_OWNERS
 #define SMAT_OWNERS 8
 #endif
 constexpr int kPlanOwners = SMAT_OWNERS;
-// Bytes of the per-step MMA list that precedes the step's blocks in the packed stream (64 per owner,
-// a multiple of 256).
-constexpr int kPlanOpBytes = (kPlanOwners * 64 + 255) / 256 * 256;
 
 // The precomputed walk order of a block-row range (plan.cu).  All pointers are device memory.
 //   gsp[n_groups + 1]  first step of every group of kPlanRowsPerGroup block-rows
-//   steps              uint4 {element column of the quad (multiple of 64), position of the step in the
+//   steps              uint4 {element column of the quad (multiple of 64), position of the step's first block in the
 //                      packed stream in 256-byte units, mask bits 0..31, mask bits 32..63} per step; a step is a quad of four
 //                      consecutive block-columns of a group (or a slice of one holding at most
 //                      kPlanBlocksPerStep blocks), ascending inside a group; mask bit
@@ -68,16 +65,10 @@ constexpr int kPlanOpBytes = (kPlanOwners * 64 + 255) / 256 * 256;
 //   blk[nnzb]          block indices in (group, block-column, row) order; indexed with the ABSOLUTE
 //                      block position, i.e. the entries of group g occupy
 //                      [rowptr[first row of g], rowptr[first row of g + 1])
-//   packed             the stream the kernel copies from, one record per step: a 256-byte MMA list followed
-//                      by the step's value blocks (512 bytes each) in (column, row) order, each block in
-//                      the 32-byte-swizzled form the MMA shared-memory descriptor reads (16-byte chunk
-//                      index XOR bit 2 of the row).  Step number i of the range, preceded by b blocks,
-//                      starts at byte kPlanOpBytes * i + 512 * b.
-//                      MMA list: kPlanOwners regions of 64 bytes; region o = {uint16 count, then count
-//                      uint16 entries}, entry = first block slot q (bits 0..4) | first row (5..8) |
-//                      run length - 1 (9..10) | sub-column (11..12): one MMA multiplies the run of
-//                      vertically adjacent blocks q .. q+len-1 (rows r0 .. r0+len-1 of one block-column);
-//                      runs never cross the rows of two owners.
+//   packed             the stream the kernel copies from: the value blocks (512 bytes each) in (group, quad,
+//                      sub-column, row) order, i.e. step after step and inside a step in mask-bit order, each
+//                      block in the 32-byte-swizzled form the MMA shared-memory descriptor reads (16-byte
+//                      chunk index XOR bit 2 of the row).  A step preceded by b blocks starts at byte 512 * b.
 struct PlanView {
     const int* rowptr = nullptr;  // bcsrRowPtr of the whole matrix
     const int* gsp = nullptr;
@@ -85,6 +76,7 @@ struct PlanView {
     const int* blk = nullptr;
     const void* packed = nullptr;
     size_t K = 0, nnzb = 0, brow_begin = 0, brow_end = 0, n_groups = 0, rg = kPlanRowsPerGroup;
+    size_t total_steps = 0;  // number of steps of the range when the host knows it, else 0
     // Scratch for work items that are computed in segments by several CTAs (null: items are never cut):
     // fix_scratch_bytes(SMs) bytes, used by one launch at a time.
     float* fix_scratch = nullptr;
@@ -95,7 +87,7 @@ struct PlanSizes { size_t n_groups, gsp_bytes, steps_bytes, blk_bytes, packed_by
 // max_steps = 0 means "not known yet": the bound nnzb (a step holds at least one block) is used.
 PlanSizes plan_sizes(size_t nnzb, size_t brow_begin, size_t brow_end, size_t rg, size_t max_steps = 0);
 // `ctx` (here and below): per-device state to use; nullptr = the lazily created one of get_device_ctx.
-// Phase 1 fills gsp (step counts, scanned); phase 2 fills steps, blk and the MMA lists inside packed.
+// Phase 1 fills gsp (step counts, scanned); phase 2 fills steps and blk.
 int plan_count_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
                      size_t rg, int* gsp, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
 int plan_fill_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,

@@ -66,7 +66,6 @@ constexpr int NL = SMAT_NL;            // loader warps
 #define SMAT_L2_PREFETCH 1
 #endif
 constexpr int NM = kPlanOwners;        // MMA-issuing warps; warp m owns accumulators [m * RG / NM, (m + 1) * RG / NM)
-constexpr uint32_t OPS_BYTES = kPlanOpBytes;  // per-step MMA list in front of the step's blocks
 constexpr int NC = 4;                  // panel-copier warps (used by the tensor-memory-operand variant)
 constexpr int kThreads = (NL + NC + NM + 4) * 32;
 constexpr uint32_t TMEM_PANELS = 256;  // first tensor-memory column of the panel ring (TS variant): S x 32 columns
@@ -76,9 +75,9 @@ constexpr long long WAIT_LIMIT = 4000000000LL;  // clock cycles (about two secon
 // Shared-memory plan of a kernel whose work item is NH x 128 columns of C wide.
 template <int NH>
 struct Cfg {
-    static constexpr uint32_t S = NH == 1 ? 7 : 4;              // steps in flight (pipeline stages)
+    static constexpr uint32_t S = NH == 1 ? 7 : 5;              // steps in flight (pipeline stages)
     static constexpr uint32_t PANEL_BYTES = NH * 128 * 64 * 2;  // NH x (128 n x 64 k fp16)
-    static constexpr uint32_t STAGE_BYTES = (PANEL_BYTES + OPS_BYTES + CAP * ABLK_BYTES + 1023) / 1024 * 1024;
+    static constexpr uint32_t STAGE_BYTES = (PANEL_BYTES + CAP * ABLK_BYTES + 1023) / 1024 * 1024;
     static constexpr uint32_t OFF_STAGE = 0;
     static constexpr uint32_t OFF_META = OFF_STAGE + S * STAGE_BYTES;
     static constexpr uint32_t OFF_BAR = OFF_META + S * 8;
@@ -296,7 +295,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
 #if SMAT_L2_PREFETCH
                 if (r.live) {
                     tma_prefetch_l2_2d(&mapB, (int)r.d.x, r.tile * NT);
-                    bulk_prefetch_l2(packed + (size_t)r.d.y * 256, OPS_BYTES + (uint32_t)(__popc(r.d.z) + __popc(r.d.w)) * ABLK_BYTES);
+                    bulk_prefetch_l2(packed + (size_t)r.d.y * 256, (uint32_t)(__popc(r.d.z) + __popc(r.d.w)) * ABLK_BYTES);
                 }
 #endif
             };
@@ -326,7 +325,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                     const long long l2 = clock64();
 #endif
                     const uint32_t stage = base + OFF_STAGE + slot * STAGE_BYTES;
-                    const uint32_t a_bytes = OPS_BYTES + (uint32_t)(__popc(r.d.z) + __popc(r.d.w)) * ABLK_BYTES;
+                    const uint32_t a_bytes = (uint32_t)(__popc(r.d.z) + __popc(r.d.w)) * ABLK_BYTES;
                     st_shared_u32(base + OFF_META + slot * 8, r.d.z);
                     st_shared_u32(base + OFF_META + slot * 8 + 4, r.d.w);
                     mbar_arrive_expect_tx(full(slot), panel_bytes + a_bytes);
@@ -415,7 +414,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                     const uint32_t stage = base + OFF_STAGE + slot * STAGE_BYTES;
                     const uint32_t p_lo = (uint32_t)smem_desc_k_sw128(stage);               // panel, sub-column 0
                     const uint32_t tpanel = tmem_base + TMEM_PANELS + slot * 32;            // its copy in tensor memory
-                    const uint32_t b_lo = (uint32_t)smem_desc_k_sw32(stage + PANEL_BYTES + OPS_BYTES);  // block slot 0
+                    const uint32_t b_lo = (uint32_t)smem_desc_k_sw32(stage + PANEL_BYTES);  // block slot 0
                     const uint32_t wlo = ld_shared_u32(base + OFF_META + slot * 8);
                     const uint32_t whi = ld_shared_u32(base + OFF_META + slot * 8 + 4);
                     const uint32_t mw0 = __ballot_sync(0xffffffffu, (wlo >> lane) & 1u);
@@ -628,16 +627,19 @@ int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStre
         return SMAT_OK;
     }
     // Item width: 256 columns (every A block then feeds two MMAs; one accumulator buffer, so the epilogue is not
-    // overlapped) or 128.  Wide items need C that wide and long items; between the two the estimated time decides:
+    // overlapped) or 128.  Wide items need C that wide and long items (many blocks, many steps: short items are
+    // dominated by the epilogue, which only narrow items overlap); between the two the estimated time decides:
     // rounds of items over the SMs -- the last round counting 1/P when its items are cut into P segments -- times
     // the measured cost of an item (a wide one costs 1.95 narrow ones).
     const bool split = plan.fix_scratch != nullptr;
     const size_t sms = (size_t)ctx->sm_count;
+    // steps per item: the average when the plan knows its step count, else a bound (one per block, one per 64 columns)
+    size_t est_steps = plan.nnzb / plan.n_groups;
+    if (plan.K / 64 < est_steps) est_steps = plan.K / 64;
+    if (plan.total_steps) est_steps = plan.total_steps / plan.n_groups;
     auto tail_parts = [&](size_t items) -> size_t {  // segments per item of the last round
         const size_t left = items % sms;
         if (!split || left == 0) return 1;
-        size_t est_steps = plan.nnzb / plan.n_groups;  // steps per item: at most one per block and one per 64 columns
-        if (plan.K / 64 < est_steps) est_steps = plan.K / 64;
         size_t P = sms / left;
         if (P > est_steps / kMinStepsPerCta) P = est_steps / kMinStepsPerCta;
         return P < 1 ? 1 : P;
@@ -646,7 +648,7 @@ int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStre
     int variant = g_spmm_variant;
     if (variant == 0) {
         variant = 1;
-        if (N >= 256 && plan.nnzb / plan.n_groups >= 256 &&
+        if (N >= 256 && plan.nnzb / plan.n_groups >= 256 && est_steps >= 64 &&
             1.95 * rounds(plan.n_groups * ((N + 255) / 256)) < rounds(plan.n_groups * ((N + 127) / 128)))
             variant = 3;
     }

@@ -36,7 +36,7 @@ constexpr size_t kMaxGroups = kMaxRows / 16 / 4;  // the smallest group height i
 constexpr size_t kGspBytes = ((kMaxGroups + 1) * sizeof(int) + 255) / 256 * 256;
 constexpr size_t kStepsBytes = kMaxBlocks * 16;   // a group never has more steps than blocks
 constexpr size_t kBlkBytes = kMaxBlocks * sizeof(int);
-constexpr size_t kPackedBytes = kMaxBlocks * 512 + kMaxBlocks * kPlanOpBytes;  // blocks + one MMA list per step
+constexpr size_t kPackedBytes = kMaxBlocks * 512;  // the blocks in walk order
 constexpr size_t kStatusBytes = 256;
 constexpr size_t kStaticScratchBytes = kGspBytes + kStepsBytes + kBlkBytes + kPackedBytes + kStatusBytes;
 

@@ -129,7 +129,7 @@ static int spmm_transient_plan(const void* vals, const int* rowptr, const int* c
     v.brow_end = brow_end;
     DeviceCtx* ctx = nullptr;
     if (int rc0 = get_device_ctx(&ctx)) return rc0;
-    const size_t rg = kPlanRowsPerGroup;
+    const size_t rg = choose_rows_per_group(brow_end - brow_begin, N, ctx->sm_count, true, nnzb, K);
     const PlanSizes sz = plan_sizes(nnzb, brow_begin, brow_end, rg);
     v.n_groups = sz.n_groups;
     v.rg = rg;

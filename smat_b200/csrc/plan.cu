@@ -233,18 +233,34 @@ int pack_values_async(const int* rowptr, const void* vals, const int* gsp, const
     return SMAT_OK;
 }
 
-size_t choose_rows_per_group(size_t block_rows, size_t N, int sm_count) {
-    static const int forced = [] {  // tuning knob: SMAT_ROWS_PER_GROUP=16|8|4 overrides the choice
+size_t choose_rows_per_group(size_t block_rows, size_t N, int sm_count, bool can_cut, size_t nnzb, size_t K) {
+    static const int forced = [] {  // tuning knob: SMAT_ROWS_PER_GROUP=4..16 overrides the choice
         const char* e = std::getenv("SMAT_ROWS_PER_GROUP");
         const int v = e ? std::atoi(e) : 0;
-        return (v == 16 || v == 8 || v == 4) ? v : 0;
+        return (v >= 4 && v <= kPlanRowsPerGroup) ? v : 0;
     }();
     if (forced) return (size_t)forced;
-    const size_t tiles = N ? (N + 127) / 128 : 1;
-    for (size_t rg : {(size_t)16, (size_t)8}) {
-        if ((block_rows + rg - 1) / rg * tiles >= (size_t)sm_count) return rg;
+    if (N == 0 || block_rows == 0) return kPlanRowsPerGroup;
+    const size_t sms = (size_t)sm_count;
+    size_t best = kPlanRowsPerGroup;
+    double best_cost = 0.0;
+    for (size_t rg = kPlanRowsPerGroup; rg >= 8; rg--) {
+        const size_t groups = (block_rows + rg - 1) / rg;
+        size_t est_steps = nnzb / groups;  // steps per item: at most one per block and one per 64 columns
+        if (K / 64 < est_steps) est_steps = K / 64;
+        // the per-item overhead (pipeline fill, epilogue, steps that do not shrink with the height) is worth about
+        // four block-rows of work
+        double cost = rounds_for(groups * ((N + 127) / 128), sms, can_cut, est_steps, false) * (double)(rg + 4);
+        if (N >= 256 && nnzb / groups >= 256 && est_steps >= 64) {
+            const double wide = kWideItemCost * rounds_for(groups * ((N + 255) / 256), sms, can_cut, est_steps, true) * (double)(rg + 4);
+            if (wide < cost) cost = wide;
+        }
+        if (rg == kPlanRowsPerGroup || cost < best_cost * 0.97) {  // a smaller group must pay for its lower panel reuse
+            best = rg;
+            best_cost = cost;
+        }
     }
-    return 4;
+    return best;
 }
 
 PlanSizes plan_sizes(size_t nnzb, size_t brow_begin, size_t brow_end, size_t rg, size_t max_steps) {
@@ -339,8 +355,7 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
         delete p;
         return rc0;
     }
-    (void)N_hint;
-    const size_t rg = kPlanRowsPerGroup;  // items may be cut across CTAs, so the tallest group (most panel reuse) is best
+    const size_t rg = choose_rows_per_group(brow_end - brow_begin, N_hint, ctx->sm_count, true, nnzb, K);
     // phase 1 into a small buffer of its own; the step total then sizes the rest exactly
     PlanSizes sz = plan_sizes(nnzb, brow_begin, brow_end, rg);
     cudaError_t e = cudaGetDevice(&p->device);

@@ -43,8 +43,33 @@ int encode_tensor_map_2d_f16(CUtensorMap* map, const void* base, uint64_t inner,
 // Most block-rows per work item of the SpMM kernel (one accumulator each).  A plan is built for groups of
 // `rg` <= kPlanRowsPerGroup block-rows: small matrices / shards use smaller groups to fill the SMs.
 constexpr int kPlanRowsPerGroup = 16;
-// Group height that yields at least `sm_count` work items when C is N columns wide, from {16, 8, 4}.
-size_t choose_rows_per_group(size_t block_rows, size_t N, int sm_count);
+// Scheduling model shared by the plan builder (group height) and the launcher (item width).
+// An item is not cut into segments shorter than this many steps (on average).
+constexpr int kMinStepsPerCta = 16;
+// ... nor into more than this many: measured, finer cuts cost more in partial tiles than they save.
+constexpr size_t kMaxTailParts = 4;
+// Segments per item of the last round: `items` work items of about `est_steps` steps over `sms` CTAs.
+inline size_t tail_parts_for(size_t items, size_t sms, bool can_cut, size_t est_steps) {
+    const size_t left = items % sms;
+    if (!can_cut || left == 0) return 1;
+    size_t P = sms / left;
+    if (P > est_steps / kMinStepsPerCta) P = est_steps / kMinStepsPerCta;
+    if (P > kMaxTailParts) P = kMaxTailParts;
+    return P < 1 ? 1 : P;
+}
+// Rounds of items over the SMs.  When the items of the last round are cut into P segments it counts 1/P plus the
+// measured cost of the cut (pipeline refill, partial tiles, their summation): about a third of an item for
+// 128-column items, a twelfth for 256-column items.
+inline double rounds_for(size_t items, size_t sms, bool can_cut, size_t est_steps, bool wide) {
+    if (items % sms == 0) return (double)(items / sms);
+    const size_t P = tail_parts_for(items, sms, can_cut, est_steps);
+    return (double)(items / sms) + 1.0 / (double)P + (P > 1 ? (wide ? 0.08 : 0.35) : 0.0);
+}
+// Measured cost of a 256-column item relative to a 128-column item of the same group.
+constexpr double kWideItemCost = 1.95;
+// Group height for a range of `block_rows` block-rows when C is N columns wide (0 = unknown): the height in
+// [8, 16] with the smallest estimated time, rounds x (height + per-item overhead), for the better item width.
+size_t choose_rows_per_group(size_t block_rows, size_t N, int sm_count, bool can_cut, size_t nnzb, size_t K);
 // Bytes of that scratch: one partial tile of 2 x 16 block-rows x 16 x 128 fp32 per SM.
 inline size_t fix_scratch_bytes(int sm_count) { return (size_t)sm_count * (2 * 16 * 16 * 128) * sizeof(float); }
 // A step of the plan covers four consecutive block-columns and carries at most this many blocks.

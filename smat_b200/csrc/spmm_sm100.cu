@@ -176,15 +176,14 @@ struct SegGen {
         const int g = (n_full + i) / n_tiles;
         const int gs = __ldg(gsp + g), ns = __ldg(gsp + g + 1) - gs;
         s.item = n_full + i; s.gs = gs; s.parts = P; s.part = j; s.tail = i;
-        s.k0 = (int)((long long)ns * j / P);
-        s.k1 = (int)((long long)ns * (j + 1) / P);
+        s.k0 = (int)((unsigned)ns * (unsigned)j / (unsigned)P);  // P <= kMaxTailParts: the products fit 32 bits
+        s.k1 = (int)((unsigned)ns * (unsigned)(j + 1) / (unsigned)P);
         return true;
     }
 };
 
 constexpr int kFixSlotFloats = 2 * RG * 16 * 128;  // one partial tile: up to 2 halves x 16 block-rows x 16 rows x 128 columns
 static_assert((size_t)kFixSlotFloats * sizeof(float) == (2 * 16 * 16 * 128) * sizeof(float), "fix_scratch_bytes() assumes this tile size");
-constexpr int kMinStepsPerCta = 16;                // an item is not cut into segments shorter than this (on average)
 
 // TS = false: both MMA operands from shared memory, two accumulator buffers (the epilogue of an item
 //   overlaps the main loop of the next).
@@ -384,7 +383,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
             const uint32_t m = (uint32_t)__shfl_sync(0xffffffffu, warp - NL - NC, 0);
             const uint32_t P_HI = (uint32_t)(smem_desc_k_sw128(0) >> 32), B_HI = (uint32_t)(smem_desc_k_sw32(0) >> 32);
             constexpr uint32_t IDESC_N0 = idesc_f16_f32(128, 0);  // the N field is added per run: N = 16 * length
-            const uint32_t rpo = (uint32_t)max(1, rg / NM);        // rows per owning warp
+            const uint32_t rpo = (uint32_t)((rg + NM - 1) / NM);  // rows per owning warp (the last warps may own none)
             const uint32_t rows_m = ((1u << rpo) - 1u) << (m * rpo);
             const uint32_t own32 = (rows_m & 0xffffu) | (rows_m << 16);  // this warp's rows in both sub-columns of a mask word
             const bool leader = elect_one();  // the lane that issues; fixed, so that its commits cover its MMAs
@@ -467,8 +466,10 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
             if ((int)blockIdx.x < (n_items - n_full) * tail_parts) {  // the last round: one segment of an item
                 const int i = (int)blockIdx.x / tail_parts, j = (int)blockIdx.x - i * tail_parts;
                 const int g = (n_full + i) / n_tiles;
-                const int ns = __ldg(gsp + g + 1) - __ldg(gsp + g);
-                run_segment((int)((long long)ns * j / tail_parts), (int)((long long)ns * (j + 1) / tail_parts));
+                const unsigned ns = (unsigned)(__ldg(gsp + g + 1) - __ldg(gsp + g));  // times j <= 4: fits 32 bits
+                const int k0 = __shfl_sync(0xffffffffu, (int)(ns * (unsigned)j / (unsigned)tail_parts), 0);
+                const int k1 = __shfl_sync(0xffffffffu, (int)(ns * (unsigned)(j + 1) / (unsigned)tail_parts), 0);
+                run_segment(k0, k1);
             }
 #ifdef SMAT_PROFILE2
             if (blockIdx.x == 0 && m == 0 && leader) { g_prof2[0] = pw; g_prof2[1] = ps; g_prof2[2] = pm; g_prof2[3] = pc; g_prof2[4] = pn; g_prof2[5] = pk; }
@@ -637,19 +638,13 @@ int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStre
     size_t est_steps = plan.nnzb / plan.n_groups;
     if (plan.K / 64 < est_steps) est_steps = plan.K / 64;
     if (plan.total_steps) est_steps = plan.total_steps / plan.n_groups;
-    auto tail_parts = [&](size_t items) -> size_t {  // segments per item of the last round
-        const size_t left = items % sms;
-        if (!split || left == 0) return 1;
-        size_t P = sms / left;
-        if (P > est_steps / kMinStepsPerCta) P = est_steps / kMinStepsPerCta;
-        return P < 1 ? 1 : P;
-    };
-    auto rounds = [&](size_t items) { return (double)(items / sms) + (items % sms ? 1.0 / (double)tail_parts(items) : 0.0); };
+    auto tail_parts = [&](size_t items) { return tail_parts_for(items, sms, split, est_steps); };
+    auto rounds = [&](size_t items, bool wide) { return rounds_for(items, sms, split, est_steps, wide); };
     int variant = g_spmm_variant;
     if (variant == 0) {
         variant = 1;
         if (N >= 256 && plan.nnzb / plan.n_groups >= 256 && est_steps >= 64 &&
-            1.95 * rounds(plan.n_groups * ((N + 255) / 256)) < rounds(plan.n_groups * ((N + 127) / 128)))
+            kWideItemCost * rounds(plan.n_groups * ((N + 255) / 256), true) < rounds(plan.n_groups * ((N + 127) / 128), false))
             variant = 3;
     }
     const size_t NTI = variant == 3 ? 256 : 128;

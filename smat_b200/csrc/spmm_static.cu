@@ -104,7 +104,7 @@ extern "C" int smat_spmm_bcsr_f16_static(const void* vals, const int* rowptr, co
     v.nnzb = nnzb;
     v.brow_begin = 0;
     v.brow_end = Mb;
-    const size_t rg = choose_rows_per_group(Mb, N, d->ctx.sm_count);
+    const size_t rg = choose_rows_per_group(Mb, N, d->ctx.sm_count, false, nnzb, K);
     v.rg = rg;
     v.n_groups = (Mb + rg - 1) / rg;
     int* gsp = reinterpret_cast<int*>(d->base);

@@ -1,5 +1,5 @@
 // Block-sparse SpMM  C = A_bcsr x B  for NVIDIA B200 (sm_100a): tcgen05.mma with fp32 accumulators
-// in tensor memory, B panels fetched by TMA, A blocks by cp.async, persistent warp-specialised CTAs.
+// in tensor memory, B panels fetched by TMA, A blocks by bulk copies, persistent warp-specialised CTAs.
 //
 // Replaces the reference's one-warp-per-tile mma.sync kernel and its launcher
 // (mmaCBTKernelSparse / mmaCBTKernel, src/cuda_hgemm/src/mma/mmaCBT.cu:13-88) behind the same
@@ -18,25 +18,30 @@
 //     bytes/clock/SM from HBM because few of them can be in flight);
 //   * D = 128 lanes (columns of C) x 16 fp32 columns (rows of the block-row) in tensor memory.
 //
-// Work decomposition.  A work item is (group of RG = 16 consecutive block-rows) x (128 columns of
-// C).  The 16 accumulators of an item live in tensor memory at once (two buffers of 256 columns,
-// so the epilogue of one item overlaps the main loop of the next).  An item walks the group's
-// block-columns in ascending order in units of FOUR block-columns (64 k): measured on B200, a
-// gather of 32-byte rows (one block-column of B) is limited to one 32-byte L2 sector per clock
-// per SM whatever the engine (TMA or cp.async), so the panel is fetched 128 bytes wide -- the same
-// number of requests moves four block-columns -- and feeds every block of the group in those four
-// columns.  The walk order is precomputed (plan.cu): one 16-byte step descriptor {element column
-// of the quad, first block, 64-bit (sub-column, row) mask} per non-empty quad (quads with more than
-// CAP blocks are split) and a block-index list in (group, column, row) order.
+// Work decomposition.  A work item is (group of rg <= 16 consecutive block-rows) x (128 or 256 columns
+// of C).  The accumulators of an item live in tensor memory at once (narrow items: two buffers of 256
+// columns, so the epilogue of one item overlaps the main loop of the next; wide items: one buffer of
+// 512).  An item walks the group's block-columns in ascending order in units of FOUR block-columns
+// (64 k): measured on B200, a gather of 32-byte rows (one block-column of B) is limited to one 32-byte
+// L2 sector per clock per SM whatever the engine (TMA or cp.async), so the panel is fetched 128 bytes
+// wide -- the same number of requests moves four block-columns -- and feeds every block of the group
+// in those four columns.  The walk order is precomputed (plan.cu): one 16-byte step descriptor
+// {element column of the quad, first block, 64-bit (sub-column, row) mask} per non-empty quad (quads
+// with more than CAP blocks are split) and the blocks themselves copied into (group, column, row) order.
+// Vertically adjacent blocks of one block-column (adjacent accumulators, adjacent in the stage) are
+// multiplied by ONE MMA with N = 16 x run length.
 //
-// Measured on B200: one thread can issue a tcgen05.mma only every ~50 cycles and a TMA / bulk copy
-// only every ~160-250 cycles, whatever their size, while different warps issue concurrently.  So
-// issue is spread over warps: 4 loader warps (each takes every 4th step: one TMA for the 16 KB
-// panel, one bulk copy for the step's A blocks), 16 MMA warps (one issuing thread each, owning one
-// accumulator, so that every accumulator is updated by a single thread, in order; the per-MMA
-// address arithmetic of a lone thread is a serial dependency chain of ~200 cycles, which is why
-// one accumulator per thread pays), and 4 epilogue warps (tcgen05.ld -> fp16 -> paired coalesced
-// stores).
+// Measured on B200: one thread can issue a tcgen05.mma only every ~50 cycles (150-200 when the
+// descriptors change from one MMA to the next) and a TMA / bulk copy only every ~160-250 cycles,
+// whatever their size, while different warps issue concurrently.  So issue is spread over warps:
+// 4 loader warps (each takes every 4th step: one TMA for the panel, one bulk copy for the step's A
+// blocks), 8 MMA warps (each owns two accumulator rows, so that every accumulator is updated by a
+// single thread, in order), 4 epilogue warps (tcgen05.ld -> zero the accumulator -> fp16 -> paired
+// coalesced stores) and, for the tensor-memory-operand variant, 4 panel-copier warps.
+//
+// Scheduling.  Items go round-robin over the persistent CTAs while there is one for every CTA; the
+// items left for the last round are cut into equal segments so that it keeps every SM busy (SegGen
+// below), and a small second kernel adds the fp32 partial tiles of the cut items.
 //
 // Every wait is bounded: when a wait runs out the kernel records a status code, stops waiting
 // anywhere in the CTA, and runs to completion (results are then invalid and the host reports

@@ -71,6 +71,7 @@ int smat_spmm_bcsr_f16_rows(const void* bcsrValuesA, const int* bcsrRowPtrA, con
 int smat_spmm_bcsr_f16_static(const void* bcsrValuesA, const int* bcsrRowPtrA, const int* bcsrColIdxA, const void* B,
                               void* C, size_t M, size_t N, size_t K, size_t nonzeroBlocks, void* stream);
 
+
 /* Multiplication plan: what the kernel needs beyond the BCSR arrays, computed on the device and
  * reusable for any number of multiplications:
  *   - the walk order (per group of 16 block-rows, its block-columns four at a time in ascending
@@ -91,6 +92,17 @@ int smat_plan_create(smat_plan** plan, const void* bcsrValuesA, const int* bcsrR
 int smat_plan_set_values(smat_plan* plan, const void* bcsrValuesA, void* stream);
 /* Rows [16*brow_begin, 16*brow_end) of C = A x B; C points at the first row of that range. */
 int smat_plan_spmm(const smat_plan* plan, const void* B, void* C, size_t N, void* stream);
+
+/* The same product with B and C in HOST memory (pinned memory for copies that overlap), pipelined on two
+ * internal streams: B comes in by column chunks of one work-item width, each multiplied as soon as it has
+ * arrived; the last chunk is multiplied range of block-rows by range, and the rows of C it completes are copied
+ * out under the multiplication of the next range.  B_host is [N][K] (k contiguous), C_host row-major
+ * [(brow_end - brow_begin) * 16][N].  Everything is ordered after earlier work on `stream`, and `stream` ends
+ * after the last copy.  The staging buffers (all of B and C) and the streams belong to the plan and are created
+ * by the first call, which therefore must not happen inside a stream capture.
+ * No reference counterpart: the reference harness uploads B once and downloads C once
+ * (src/cuda_hgemm/src/common/matrix.h:88-101). */
+int smat_plan_spmm_host(smat_plan* plan, const void* B_host, void* C_host, size_t N, void* stream);
 int smat_plan_destroy(smat_plan* plan);
 
 /* Kernel variant used by every multiplication of this process: 0 = chosen per matrix (default),

@@ -36,6 +36,7 @@ def lib():
     L.smat_plan_create.argtypes = [C.POINTER(vp), vp, ip, ip, sz, sz, sz, sz, sz, sz, vp]
     L.smat_plan_set_values.argtypes = [vp, vp, vp]
     L.smat_plan_spmm.argtypes = [vp, vp, vp, sz, vp]
+    L.smat_plan_spmm_host.argtypes = [vp, vp, vp, sz, vp]
     L.smat_plan_destroy.argtypes = [vp]
     L.smat_spmm_set_variant.argtypes = [C.c_int]
     L.smat_device_status.argtypes = [vp]
@@ -304,6 +305,14 @@ class Plan:
         _check(lib().smat_plan_spmm(self._h, Bt.data_ptr(), Ct.data_ptr(), N, _stream()))
         if check:
             _check(lib().smat_device_status(_stream()))
+
+    def spmm_host(self, B_host, C_host):
+        """B_host [N][K], C_host [rows][N]: CPU tensors (pinned for overlap); copies pipelined with the multiply."""
+        N = B_host.shape[0]
+        assert B_host.shape[1] == self.A.K and tuple(C_host.shape) == ((self.brow_end - self.brow_begin) * 16, N)
+        assert B_host.is_contiguous() and C_host.is_contiguous() and not B_host.is_cuda and not C_host.is_cuda
+        assert B_host.element_size() == 2 and C_host.element_size() == 2
+        _check(lib().smat_plan_spmm_host(self._h, B_host.data_ptr(), C_host.data_ptr(), N, _stream()))
 
     def close(self):
         if self._h is not None:

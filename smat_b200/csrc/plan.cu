@@ -19,6 +19,7 @@
 #include <new>
 
 #include <cstdlib>
+#include <vector>
 
 #include "smat_internal.h"
 
@@ -335,6 +336,13 @@ struct smat_plan {
     void* gsp_buffer = nullptr;
     void* fix_buffer = nullptr;  // partial tiles of cut work items
     int device = -1;
+    // smat_plan_spmm_host: device staging (B and C whole), the copy streams, per-chunk and per-range events
+    void* host_B = nullptr;
+    void* host_C = nullptr;
+    size_t host_B_bytes = 0, host_C_bytes = 0;
+    cudaStream_t s_in = nullptr, s_out = nullptr;
+    cudaEvent_t ev_start = nullptr;
+    std::vector<cudaEvent_t> ev_in, ev_done, ev_out;
 };
 
 extern "C" {
@@ -436,9 +444,113 @@ int smat_plan_spmm(const smat_plan* plan, const void* B, void* C, size_t N, void
     return launch_spmm(plan->v, B, C, N, (cudaStream_t)stream);
 }
 
+int smat_plan_spmm_host(smat_plan* plan, const void* B_host, void* C_host, size_t N, void* stream) {
+    clear_error();
+    if (!plan) return fail(SMAT_ERR_BAD_ARG, "plan is NULL");
+    if (N % 8) return fail(SMAT_ERR_BAD_ARG, "N (%zu) must be a multiple of 8", N);
+    if (N >= ((size_t)1 << 31)) return fail(SMAT_ERR_RANGE, "N beyond 2^31");
+    const size_t rows = (plan->v.brow_end - plan->v.brow_begin) * 16, K = plan->v.K;
+    if (rows == 0 || N == 0) return SMAT_OK;
+    if (!B_host || !C_host) return fail(SMAT_ERR_BAD_ARG, "B_host or C_host is NULL");
+    cudaStream_t s = (cudaStream_t)stream;
+    // B comes in by column chunks as wide as the kernel's widest work item (rows of the [N][K] array: contiguous);
+    // every chunk but the last is multiplied for all block-rows as soon as it has arrived; the last chunk is
+    // multiplied group range by group range, and the rows of C that it completes go out at once (rows of the
+    // row-major C: contiguous), under the multiplication of the next range.
+    const size_t W = N >= 512 ? 256 : (N > 128 ? 128 : N);
+    const size_t n_chunks = (N + W - 1) / W;
+    const size_t n_groups = plan->v.n_groups;
+    // ranges of the last chunk: each should still fill the SMs for about one round of work items (shorter launches
+    // lose more to partly filled rounds than the overlap of the copy-out wins back); at most 4
+    DeviceCtx* ctx = nullptr;
+    if (int rc0 = get_device_ctx(&ctx)) return rc0;
+    size_t n_ranges = (n_groups * ((W + 127) / 128) + (size_t)ctx->sm_count / 2) / (size_t)ctx->sm_count;
+    if (const char* e = std::getenv("SMAT_HOST_RANGES")) n_ranges = (size_t)std::atoi(e);  // tuning knob
+    if (n_ranges > 4) n_ranges = 4;
+    if (n_ranges > n_groups) n_ranges = n_groups;
+    if (n_ranges < 1) n_ranges = 1;
+    // staging memory and streams: created on first use and kept with the plan (grown when a later call is wider)
+    if (!plan->s_in) {
+        SMAT_CUDA_TRY(cudaStreamCreateWithFlags(&plan->s_in, cudaStreamNonBlocking));
+        SMAT_CUDA_TRY(cudaStreamCreateWithFlags(&plan->s_out, cudaStreamNonBlocking));
+        SMAT_CUDA_TRY(cudaEventCreateWithFlags(&plan->ev_start, cudaEventDisableTiming));
+    }
+    if (plan->host_B_bytes < N * K * 2 || plan->host_C_bytes < rows * N * 2) {
+        SMAT_CUDA_TRY(cudaStreamSynchronize(plan->s_in));
+        SMAT_CUDA_TRY(cudaStreamSynchronize(plan->s_out));
+        SMAT_CUDA_TRY(cudaStreamSynchronize(s));
+        SMAT_CUDA_TRY(cudaFree(plan->host_B));
+        SMAT_CUDA_TRY(cudaFree(plan->host_C));
+        plan->host_B = plan->host_C = nullptr;
+        plan->host_B_bytes = plan->host_C_bytes = 0;
+        SMAT_CUDA_TRY(cudaMalloc(&plan->host_B, N * K * 2));
+        plan->host_B_bytes = N * K * 2;
+        SMAT_CUDA_TRY(cudaMalloc(&plan->host_C, rows * N * 2));
+        plan->host_C_bytes = rows * N * 2;
+    }
+    while (plan->ev_in.size() < n_chunks) {
+        cudaEvent_t e = nullptr;
+        SMAT_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        plan->ev_in.push_back(e);
+    }
+    while (plan->ev_done.size() < n_ranges) {
+        cudaEvent_t a = nullptr, b = nullptr;
+        SMAT_CUDA_TRY(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
+        plan->ev_done.push_back(a);
+        SMAT_CUDA_TRY(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
+        plan->ev_out.push_back(b);
+    }
+    // the copies start after whatever the caller had put on its stream (e.g. the previous call's use of the buffers)
+    SMAT_CUDA_TRY(cudaEventRecord(plan->ev_start, s));
+    SMAT_CUDA_TRY(cudaStreamWaitEvent(plan->s_in, plan->ev_start, 0));
+    SMAT_CUDA_TRY(cudaStreamWaitEvent(plan->s_out, plan->ev_start, 0));
+    const char* Bh = static_cast<const char*>(B_host);
+    char* Ch = static_cast<char*>(C_host);
+    char* Bd = static_cast<char*>(plan->host_B);
+    char* Cd = static_cast<char*>(plan->host_C);
+    for (size_t j = 0; j < n_chunks; j++) {
+        const size_t n0 = j * W, w = (N - n0 < W) ? N - n0 : W;
+        SMAT_CUDA_TRY(cudaMemcpyAsync(Bd + n0 * K * 2, Bh + n0 * K * 2, w * K * 2, cudaMemcpyHostToDevice, plan->s_in));
+        SMAT_CUDA_TRY(cudaEventRecord(plan->ev_in[j], plan->s_in));
+    }
+    for (size_t j = 0; j < n_chunks; j++) {
+        const size_t n0 = j * W, w = (N - n0 < W) ? N - n0 : W;
+        SMAT_CUDA_TRY(cudaStreamWaitEvent(s, plan->ev_in[j], 0));
+        if (j + 1 < n_chunks) {
+            if (int rc = launch_spmm(plan->v, Bd + n0 * K * 2, Cd + n0 * 2, w, s, nullptr, N)) return rc;
+            continue;
+        }
+        for (size_t r = 0; r < n_ranges; r++) {
+            const size_t g0 = n_groups * r / n_ranges, g1 = n_groups * (r + 1) / n_ranges;
+            const size_t row0 = g0 * plan->v.rg * 16;
+            const size_t row1 = (g1 * plan->v.rg * 16 < rows) ? g1 * plan->v.rg * 16 : rows;
+            if (int rc = launch_spmm(plan->v, Bd + n0 * K * 2, Cd + (row0 * N + n0) * 2, w, s, nullptr, N, g0, g1)) return rc;
+            SMAT_CUDA_TRY(cudaEventRecord(plan->ev_done[r], s));
+            SMAT_CUDA_TRY(cudaStreamWaitEvent(plan->s_out, plan->ev_done[r], 0));
+            SMAT_CUDA_TRY(cudaMemcpyAsync(Ch + row0 * N * 2, Cd + row0 * N * 2, (row1 - row0) * N * 2, cudaMemcpyDeviceToHost,
+                                          plan->s_out));
+            SMAT_CUDA_TRY(cudaEventRecord(plan->ev_out[r], plan->s_out));
+        }
+    }
+    // the caller's stream ends after the last copy out, so that ordering on it covers the whole call
+    SMAT_CUDA_TRY(cudaStreamWaitEvent(s, plan->ev_out[n_ranges - 1], 0));
+    return SMAT_OK;
+}
+
 int smat_plan_destroy(smat_plan* plan) {
     clear_error();
     if (!plan) return SMAT_OK;
+    if (plan->s_in) {
+        cudaStreamSynchronize(plan->s_in);
+        cudaStreamSynchronize(plan->s_out);
+        cudaStreamDestroy(plan->s_in);
+        cudaStreamDestroy(plan->s_out);
+        cudaEventDestroy(plan->ev_start);
+        for (auto& v : {plan->ev_in, plan->ev_done, plan->ev_out})
+            for (cudaEvent_t ev : v) cudaEventDestroy(ev);
+        cudaFree(plan->host_B);
+        cudaFree(plan->host_C);
+    }
     cudaError_t e = cudaFree(plan->buffer);
     const cudaError_t e2 = cudaFree(plan->gsp_buffer);
     const cudaError_t e3 = cudaFree(plan->fix_buffer);

@@ -122,9 +122,11 @@ int pack_values_async(const int* rowptr, const void* vals, const int* gsp, const
                       size_t brow_begin, size_t brow_end, size_t rg, size_t nnzb, cudaStream_t stream,
                       const DeviceCtx* ctx = nullptr);
 
-// Launch of the SpMM kernel (spmm_sm100.cu).
+// Launch of the SpMM kernel (spmm_sm100.cu).  `ldc`: elements between rows of C (0 = N, i.e. C is exactly N wide).
+// [group_begin, group_end): the groups of the plan to multiply (default: all); C points at the first row of
+// group_begin.
 int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStream_t stream,
-                const DeviceCtx* ctx = nullptr);
+                const DeviceCtx* ctx = nullptr, size_t ldc = 0, size_t group_begin = 0, size_t group_end = (size_t)-1);
 
 // 0 = choose per call, 1 = shared-memory-operand kernel, 2 = tensor-memory-operand kernel, 3 = 256-column items.
 extern int g_spmm_variant;

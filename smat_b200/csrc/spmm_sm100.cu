@@ -204,7 +204,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __restrict__ packed,
                     const uint4* __restrict__ steps, const int* __restrict__ gsp,
                     const int* __restrict__ rowptr, __half* __restrict__ C, int brow_begin, int brow_end, int rg, int N,
-                    int n_tiles, int n_items, int tail_parts, uint32_t panel_bytes, float* __restrict__ fix_scratch, int* status) {
+                    int n_tiles, int n_items, int tail_parts, uint32_t panel_bytes, float* __restrict__ fix_scratch, int* status,
+                    size_t ldc) {
     static_assert(!(TS && NH == 2), "the panel ring and 32 accumulators do not fit tensor memory together");
     // A loader waits on a stage's `empty` barrier by parity, which only tells phases apart while the waiter is
     // less than two uses ahead of the consumers; with steps consumed in order that holds iff NL <= S.
@@ -530,7 +531,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                         for (int i = 0; i < 16; i++) d[(size_t)i * 128] = __uint_as_float(v[i]);
                         continue;
                     }
-                    __half* crow = C + ((size_t)(r0 - brow_begin + r) * 16 + (odd ? 8 : 0)) * (size_t)N + (size_t)(n & ~1);
+                    __half* crow = C + ((size_t)(r0 - brow_begin + r) * 16 + (odd ? 8 : 0)) * ldc + (size_t)(n & ~1);
 #pragma unroll
                     for (int i = 0; i < 8; i++) {
                         // lane pairs exchange halves: even lanes keep rows 0..7, odd lanes rows 8..15,
@@ -539,7 +540,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                         const float send = __uint_as_float(odd ? v[i] : v[i + 8]);
                         const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
                         const __half2 hh = odd ? __floats2half2_rn(recv, keep) : __floats2half2_rn(keep, recv);
-                        if (n < N) *reinterpret_cast<__half2*>(crow + (size_t)i * (size_t)N) = hh;
+                        if (n < N) *reinterpret_cast<__half2*>(crow + (size_t)i * ldc) = hh;
                     }
                 }
             }
@@ -572,7 +573,7 @@ __global__ void zero_rows_kernel(uint4* dst, size_t n16) {
 // One block of (128 columns x 4) threads per item.
 template <int NH>
 __global__ void __launch_bounds__(512) sum_cut_items_kernel(const float* __restrict__ scratch, __half* __restrict__ C, int brow_begin,
-                                                           int brow_end, int rg, int N, int n_tiles, int n_full, int parts) {
+                                                           int brow_end, int rg, int N, int n_tiles, int n_full, int parts, size_t ldc) {
     const int item = n_full + (int)blockIdx.x;
     const int g = item / n_tiles, t = item - g * n_tiles;
     const int r0 = brow_begin + g * rg;
@@ -591,9 +592,9 @@ __global__ void __launch_bounds__(512) sum_cut_items_kernel(const float* __restr
 #pragma unroll
                 for (int i = 0; i < 16; i++) acc[i] += __ldg(src + (size_t)i * 128);
             }
-            __half* ccol = C + ((size_t)(r0 - brow_begin + r) * 16) * (size_t)N + (size_t)n;
+            __half* ccol = C + ((size_t)(r0 - brow_begin + r) * 16) * ldc + (size_t)n;
 #pragma unroll
-            for (int i = 0; i < 16; i++) ccol[(size_t)i * (size_t)N] = __float2half_rn(acc[i]);
+            for (int i = 0; i < 16; i++) ccol[(size_t)i * ldc] = __float2half_rn(acc[i]);
         }
     }
 }
@@ -616,20 +617,40 @@ extern "C" void smat_prof_read(unsigned long long* out, int reset) {
 
 int g_spmm_variant = 0;
 
-int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStream_t stream, const DeviceCtx* ctx_in) {
+int launch_spmm(const PlanView& whole, const void* B, void* C, size_t N, cudaStream_t stream, const DeviceCtx* ctx_in,
+                size_t ldc, size_t group_begin, size_t group_end) {
     const DeviceCtx* ctx = ctx_in;
     if (!ctx) {
         DeviceCtx* c = nullptr;
         if (int rc = get_device_ctx(&c)) return rc;
         ctx = c;
     }
+    if (ldc == 0) ldc = N;
+    // the view of the groups asked for: steps, blocks and row pointers are addressed absolutely, so a sub-range is
+    // the same plan with its first group, first block-row and group count moved
+    PlanView plan = whole;
+    if (group_end > whole.n_groups) group_end = whole.n_groups;
+    if (group_begin > 0 || group_end < whole.n_groups) {
+        if (group_begin >= group_end) return SMAT_OK;
+        plan.gsp = whole.gsp + group_begin;
+        plan.n_groups = group_end - group_begin;
+        plan.brow_begin = whole.brow_begin + group_begin * whole.rg;
+        if (whole.brow_begin + group_end * whole.rg < whole.brow_end) plan.brow_end = whole.brow_begin + group_end * whole.rg;
+        plan.nnzb = whole.nnzb * plan.n_groups / whole.n_groups;  // only steers the choice of the variant
+        if (plan.nnzb == 0 && whole.nnzb) plan.nnzb = 1;
+        plan.total_steps = whole.total_steps * plan.n_groups / whole.n_groups;
+    }
     const size_t nb_rows = plan.brow_end - plan.brow_begin;
     if (nb_rows == 0 || N == 0) return SMAT_OK;
     if (plan.nnzb == 0) {
-        const size_t n16 = nb_rows * 16 * N * 2 / 16;
-        zero_rows_kernel<<<ctx->sm_count * 4, 256, 0, stream>>>(reinterpret_cast<uint4*>(C), n16);
-        count_launch();
-        SMAT_CUDA_TRY(cudaGetLastError());
+        if (ldc == N) {
+            const size_t n16 = nb_rows * 16 * N * 2 / 16;
+            zero_rows_kernel<<<ctx->sm_count * 4, 256, 0, stream>>>(reinterpret_cast<uint4*>(C), n16);
+            count_launch();
+            SMAT_CUDA_TRY(cudaGetLastError());
+        } else {
+            SMAT_CUDA_TRY(cudaMemset2DAsync(C, ldc * 2, 0, N * 2, nb_rows * 16, stream));
+        }
         return SMAT_OK;
     }
     // Item width: 256 columns (every A block then feeds two MMAs; one accumulator buffer, so the epilogue is not
@@ -668,7 +689,7 @@ int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStre
         kernel<<<grid, kThreads, smem_bytes, stream>>>(
             mapB, reinterpret_cast<const uint8_t*>(plan.packed), reinterpret_cast<const uint4*>(plan.steps), plan.gsp,
             plan.rowptr, reinterpret_cast<__half*>(C), (int)plan.brow_begin, (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles,
-            (int)n_items, parts, panel_rows * 128u, plan.fix_scratch, ctx->d_status);
+            (int)n_items, parts, panel_rows * 128u, plan.fix_scratch, ctx->d_status, ldc);
         count_launch();
         SMAT_CUDA_TRY(cudaGetLastError());
         return SMAT_OK;
@@ -681,10 +702,10 @@ int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStre
     const int cut_items = (int)n_items - n_full;
     if (variant == 3)
         sum_cut_items_kernel<2><<<cut_items, dim3(128, 4), 0, stream>>>(plan.fix_scratch, reinterpret_cast<__half*>(C), (int)plan.brow_begin,
-                                                                       (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles, n_full, parts);
+                                                                       (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles, n_full, parts, ldc);
     else
         sum_cut_items_kernel<1><<<cut_items, dim3(128, 4), 0, stream>>>(plan.fix_scratch, reinterpret_cast<__half*>(C), (int)plan.brow_begin,
-                                                                       (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles, n_full, parts);
+                                                                       (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles, n_full, parts, ldc);
     count_launch();
     SMAT_CUDA_TRY(cudaGetLastError());
     return SMAT_OK;

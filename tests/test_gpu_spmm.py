@@ -189,6 +189,30 @@ def test_block_row_range_entry_point():
         assert _close(shard.cpu().numpy(), full.data[b0 * 16:b1 * 16].cpu().numpy())
 
 
+@pytest.mark.parametrize("ranges", ["", "3"])
+@pytest.mark.parametrize("N", [64, 264, 1024])
+def test_host_buffer_entry_point(N, ranges, monkeypatch):
+    """smat_plan_spmm_host: B and C in pinned host memory, copies pipelined in column chunks (1, 3 and 4 chunks
+    here, the 264-column case with a ragged last chunk), called twice to cover the reuse of its staging; the last
+    chunk multiplied and copied out in one range of block-rows (the automatic choice at this size) and in three."""
+    torch = _torch()
+    if ranges:
+        monkeypatch.setenv("SMAT_HOST_RANGES", ranges)
+    p, brp, bci, bv = _problem("uniform", 0.03, N)
+    A = S.SparseMatrix.from_bcsr(p.M, p.K, brp, bci, bv)
+    plan = S.Plan(A, n_hint=N)
+    B_host = torch.from_numpy(p.B_nk.view(np.int16)).pin_memory()
+    C_host = torch.full((p.M, N), -1, dtype=torch.int16).pin_memory()
+    Cref, Cabs = _oracle_c(bv, brp, bci, p.B_nk, p.M, N, p.K)
+    for _ in range(2):
+        C_host.fill_(-1)
+        plan.spmm_host(B_host, C_host)
+        torch.cuda.synchronize()
+        S.api._check(S.lib().smat_device_status(None))
+        assert _rel_err(C_host.numpy().view(np.float16), Cref, Cabs) <= TOL
+    plan.close()
+
+
 def test_deterministic():
     p, brp, bci, bv = _problem("llm", 0.0625, 256)
     a = _run(brp, bci, bv, p.B_nk, p.M, 256, p.K)

@@ -20,6 +20,9 @@
 
 #include <cstdlib>
 #include <vector>
+#include <utility>
+#include <queue>
+#include <algorithm>
 
 #include "smat_internal.h"
 
@@ -159,13 +162,15 @@ plan_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx, int 
 // In-place inclusive scan of data[0..n) by one CTA.
 __global__ void __launch_bounds__(1024) plan_scan_kernel(int* data, int n) {
     __shared__ int warp_tot[32];
-    __shared__ int carry_s;
+    __shared__ int carry_s, max_s;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (threadIdx.x == 0) carry_s = 0;
+    if (threadIdx.x == 0) { carry_s = 0; max_s = 0; }
     __syncthreads();
+    int vmax = 0;  // the largest entry before the scan = the most steps of any group, stored behind the scanned array
     for (int base = 0; base < n; base += 1024) {
         const int i = base + threadIdx.x;
         int v = i < n ? data[i] : 0;
+        vmax = max(vmax, v);
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
             const int t = __shfl_up_sync(0xffffffffu, v, d);
@@ -189,6 +194,9 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(int* data, int n) {
         if (threadIdx.x == 1023) carry_s = v;
         __syncthreads();
     }
+    atomicMax(&max_s, vmax);
+    __syncthreads();
+    if (threadIdx.x == 0) data[n] = max_s;
 }
 
 // One warp per step: copies the step's value blocks to their place in the packed stream; lane l moves
@@ -267,7 +275,7 @@ size_t choose_rows_per_group(size_t block_rows, size_t N, int sm_count, bool can
 PlanSizes plan_sizes(size_t nnzb, size_t brow_begin, size_t brow_end, size_t rg, size_t max_steps) {
     PlanSizes s;
     s.n_groups = (brow_end - brow_begin + rg - 1) / rg;
-    s.gsp_bytes = ((s.n_groups + 1) * sizeof(int) + 255) / 256 * 256;
+    s.gsp_bytes = ((s.n_groups + 2) * sizeof(int) + 255) / 256 * 256;  // + the largest step count of a group
     // a step holds at least one block, so nnzb bounds the number of steps
     const size_t steps = max_steps ? max_steps : (nnzb ? nnzb : 1);
     s.steps_bytes = (steps * sizeof(uint4) + 255) / 256 * 256;
@@ -335,6 +343,7 @@ struct smat_plan {
     void* buffer = nullptr;
     void* gsp_buffer = nullptr;
     void* fix_buffer = nullptr;  // partial tiles of cut work items
+    void* sched_buffer = nullptr;  // listed schedule: offsets per CTA, then the groups
     int device = -1;
     // smat_plan_spmm_host: device staging (B and C whole), the copy streams, per-chunk and per-range events
     void* host_B = nullptr;
@@ -372,16 +381,71 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
     if (e != cudaSuccess) {
         cudaFree(p->gsp_buffer);
         cudaFree(p->fix_buffer);
+        cudaFree(p->sched_buffer);
         delete p;
         return fail(SMAT_ERR_CUDA, "plan allocation failed: %s", cudaGetErrorString(e));
     }
     int* gsp = static_cast<int*>(p->gsp_buffer);
     int rc = plan_count_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, rg, gsp, (cudaStream_t)stream);
-    int total_steps = 0;
+    int total_and_max[2] = {0, 0};
     if (rc == SMAT_OK && sz.n_groups) {
-        e = cudaMemcpyAsync(&total_steps, gsp + sz.n_groups, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+        e = cudaMemcpyAsync(total_and_max, gsp + sz.n_groups, 2 * sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
         if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan build failed: %s", cudaGetErrorString(e));
+    }
+    const int total_steps = total_and_max[0];
+    // Schedule: when the heaviest group holds many times the average number of steps, items dealt out round-robin
+    // leave most SMs waiting for the one with the heaviest item; such plans deal out equal step ranges instead.
+    bool balanced = (size_t)total_and_max[1] * sz.n_groups > 4 * (size_t)total_steps &&
+                    (size_t)total_steps >= 8 * (size_t)ctx->sm_count;
+    if (rc == SMAT_OK && balanced && sz.n_groups >= 4 * (size_t)ctx->sm_count) {
+        // First choice: whole groups dealt out heaviest first to the least loaded CTA (keeps every item in one piece
+        // and the CTAs sweeping the block-columns the way the round-robin schedule does); taken when the heaviest
+        // CTA ends up within a quarter of the average load.
+        const int G = ctx->sm_count;
+        std::vector<int> h_gsp(sz.n_groups + 1);
+        e = cudaMemcpy(h_gsp.data(), gsp, (sz.n_groups + 1) * sizeof(int), cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan build failed: %s", cudaGetErrorString(e));
+        if (rc == SMAT_OK) {
+            std::vector<int> order(sz.n_groups);
+            for (size_t g = 0; g < sz.n_groups; g++) order[g] = (int)g;
+            std::stable_sort(order.begin(), order.end(),
+                             [&](int a, int b) { return h_gsp[a + 1] - h_gsp[a] > h_gsp[b + 1] - h_gsp[b]; });
+            std::priority_queue<std::pair<long long, int>, std::vector<std::pair<long long, int>>, std::greater<>> heap;
+            for (int c = 0; c < G; c++) heap.push({0, c});
+            std::vector<std::vector<int>> lists(G);
+            long long heaviest = 0;
+            for (int g : order) {
+                auto [load, c] = heap.top();
+                heap.pop();
+                load += h_gsp[g + 1] - h_gsp[g];
+                lists[c].push_back(g);
+                if (load > heaviest) heaviest = load;
+                heap.push({load, c});
+            }
+            if (heaviest * 4 * G <= 5LL * total_steps) {
+                std::vector<int> flat(G + 1 + sz.n_groups);
+                int pos = 0;
+                for (int c = 0; c < G; c++) {
+                    flat[c] = pos;
+                    for (int g : lists[c]) flat[G + 1 + pos++] = g;
+                }
+                flat[G] = pos;
+                e = cudaMalloc(&p->sched_buffer, flat.size() * sizeof(int));
+                if (e == cudaSuccess) e = cudaMemcpy(p->sched_buffer, flat.data(), flat.size() * sizeof(int), cudaMemcpyHostToDevice);
+                if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan allocation failed: %s", cudaGetErrorString(e));
+                p->v.sched_off = static_cast<const int*>(p->sched_buffer);
+                p->v.sched_list = static_cast<const int*>(p->sched_buffer) + G + 1;
+                p->v.sched_ctas = G;
+                balanced = false;
+            }
+        }
+    }
+    if (rc == SMAT_OK && balanced) {  // two partial tiles per CTA
+        cudaFree(p->fix_buffer);
+        p->fix_buffer = nullptr;
+        e = cudaMalloc(&p->fix_buffer, 2 * fix_scratch_bytes(ctx->sm_count));
+        if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan allocation failed: %s", cudaGetErrorString(e));
     }
     if (rc == SMAT_OK) {
         sz = plan_sizes(nnzb, brow_begin, brow_end, rg, (size_t)(total_steps > 0 ? total_steps : 1));
@@ -391,6 +455,7 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
     if (rc) {
         cudaFree(p->gsp_buffer);
         cudaFree(p->fix_buffer);
+        cudaFree(p->sched_buffer);
         delete p;
         return rc;
     }
@@ -408,6 +473,7 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
     p->v.rg = rg;
     p->v.fix_scratch = static_cast<float*>(p->fix_buffer);
     p->v.total_steps = (size_t)(total_steps > 0 ? total_steps : 0);
+    p->v.balanced = balanced;
     rc = plan_fill_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, rg, gsp, const_cast<void*>(p->v.steps),
                          const_cast<int*>(p->v.blk), const_cast<void*>(p->v.packed), (cudaStream_t)stream);
     if (rc == SMAT_OK)
@@ -417,6 +483,7 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
         cudaFree(p->buffer);
         cudaFree(p->gsp_buffer);
         cudaFree(p->fix_buffer);
+        cudaFree(p->sched_buffer);
         delete p;
         return rc;
     }
@@ -465,6 +532,7 @@ int smat_plan_spmm_host(smat_plan* plan, const void* B_host, void* C_host, size_
     DeviceCtx* ctx = nullptr;
     if (int rc0 = get_device_ctx(&ctx)) return rc0;
     size_t n_ranges = (n_groups * ((W + 127) / 128) + (size_t)ctx->sm_count / 2) / (size_t)ctx->sm_count;
+    if (plan->v.sched_list || plan->v.balanced) n_ranges = 1;  // such plans balance a launch over all their groups
     if (const char* e = std::getenv("SMAT_HOST_RANGES")) n_ranges = (size_t)std::atoi(e);  // tuning knob
     if (n_ranges > 4) n_ranges = 4;
     if (n_ranges > n_groups) n_ranges = n_groups;
@@ -554,6 +622,7 @@ int smat_plan_destroy(smat_plan* plan) {
     cudaError_t e = cudaFree(plan->buffer);
     const cudaError_t e2 = cudaFree(plan->gsp_buffer);
     const cudaError_t e3 = cudaFree(plan->fix_buffer);
+    cudaFree(plan->sched_buffer);
     if (e == cudaSuccess) e = e2;
     if (e == cudaSuccess) e = e3;
     delete plan;

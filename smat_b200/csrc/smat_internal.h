@@ -102,6 +102,14 @@ struct PlanView {
     const void* packed = nullptr;
     size_t K = 0, nnzb = 0, brow_begin = 0, brow_end = 0, n_groups = 0, rg = kPlanRowsPerGroup;
     size_t total_steps = 0;  // number of steps of the range when the host knows it, else 0
+    // The heaviest group has many times the average number of steps: deal out equal step ranges instead of items
+    // (needs fix_scratch of 2 x fix_scratch_bytes).
+    bool balanced = false;
+    // Or, preferred when it balances well enough: a fixed assignment of whole groups to `sched_ctas` CTAs, heaviest
+    // first to the least loaded (device arrays: CTA c works on groups sched_list[sched_off[c] .. sched_off[c + 1])).
+    const int* sched_off = nullptr;
+    const int* sched_list = nullptr;
+    int sched_ctas = 0;
     // Scratch for work items that are computed in segments by several CTAs (null: items are never cut):
     // fix_scratch_bytes(SMs) bytes, used by one launch at a time.
     float* fix_scratch = nullptr;

@@ -150,27 +150,85 @@ struct StepRec {
     uint4 d;      // {element column of the quad, first packed block, mask bits 0..31, mask bits 32..63}
 };
 
-// A segment: steps [k0, k1) of work item `item` (the first step of the item is steps[gs]).  parts > 1: the item is
-// computed in `parts` segments by as many CTAs; it is the tail-th item of the last round and this is part `part`.
+// A segment: steps [k0, k1) of the ns steps of work item `item` (the first step of the item is steps[gs]).
+// cut: the item is computed in several segments by as many CTAs and this segment goes to scratch tile `slot`.
 struct Seg {
-    int item, k0, k1, gs, parts, part, tail;
+    int item, k0, k1, ns, gs, slot;
+    bool cut;
 };
 
-// What a CTA works on, in order: work items round-robin over the CTAs, as long as there is one for every CTA.  The
-// items left for the last round (fewer than CTAs) are each cut into P = #CTAs / #items-left segments of equal step
-// count, one per CTA, so that the last round keeps every SM busy and takes 1/P of an item's time.  All items are
-// cut at the same fractions and consecutive CTAs take consecutive segments, so the CTAs of a round still walk the
-// block-columns in step (what they fetch is shared through L2).  A cut item is assembled from fp32 partial tiles:
-// each CTA stores its segment's result to its scratch tile and a small second kernel adds them in order.
+// The (item, step) pairs of a launch flattened in item order; position 0 is the first step of the first item.
+struct Flat {
+    const int* gsp;
+    int n_tiles, n_groups;
+    long long total;  // number of positions
+    __device__ __forceinline__ long long first_of_group(int g) const { return (long long)(__ldg(gsp + g) - __ldg(gsp)) * n_tiles; }
+    // first position of CTA c's range when the positions are dealt out in `parts` equal contiguous ranges
+    __device__ __forceinline__ long long range_begin(int parts, int c) const { return total * c / parts; }
+    // the CTA whose range holds position p: the largest c with range_begin(c) <= p
+    __device__ __forceinline__ int range_owner(int parts, long long p) const { return (int)(((p + 1) * parts - 1) / total); }
+    // last group whose first position is <= p (groups without steps share their successor's first position)
+    __device__ __forceinline__ int group_of(long long p) const {
+        int lo = 0, hi = n_groups - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (first_of_group(mid) <= p) lo = mid; else hi = mid - 1;
+        }
+        return lo;
+    }
+};
+
+// What a CTA works on, in order.  Three schedules:
+//  * round-robin (default): work items go round-robin over the CTAs as long as there is one for every CTA.  The
+//    items left for the last round (fewer than CTAs) are each cut into P = #CTAs / #items-left segments of equal
+//    step count, one per CTA, so that the last round keeps every SM busy and takes 1/P of an item's time.  All
+//    items are cut at the same fractions and consecutive CTAs take consecutive segments, so the CTAs of a round
+//    still walk the block-columns in step (what they fetch is shared through L2).
+//  * listed (plans whose heaviest group holds many times the average number of steps): every CTA has a fixed list
+//    of whole groups, dealt out at plan time heaviest first to the least loaded CTA;
+//  * balanced (such plans when whole groups cannot be dealt out evenly, e.g. one group outweighs a CTA's share): the flattened
+//    (item, step) sequence is dealt out in equal contiguous ranges, one per CTA, whatever the number and the
+//    length of the items; an item that a range boundary falls into is computed in segments.
+// A cut item is assembled from fp32 partial tiles: each CTA stores its segment's result to a scratch tile (one
+// per CTA, two in the balanced schedule: the head and the tail of its range) and a small second kernel adds them.
 struct SegGen {
     const int* gsp;
     int n_tiles, n_items, n_ctas, cta, item, n_full, P;
-    bool tail_done;
+    bool tail_done, balanced;
+    Flat flat;
+    long long p, p_begin, p_end;
+    int g;
+    const int* list;      // listed schedule: the groups of this CTA, else null
+    int li, li_end, lt;   // position in the list, its end, next tile of the current group
     __device__ __forceinline__ bool next(Seg& s) {
-        if (item < n_full) {
-            const int g = item / n_tiles;
+        if (list) {
+            if (li >= li_end) return false;
+            const int gg = __ldg(list + li);
+            const int gs = __ldg(gsp + gg), ns = __ldg(gsp + gg + 1) - gs;
+            s.item = gg * n_tiles + lt; s.k0 = 0; s.k1 = ns; s.ns = ns; s.gs = gs; s.cut = false; s.slot = 0;
+            if (++lt == n_tiles) { lt = 0; li++; }
+            return true;
+        }
+        if (balanced) {
+            if (p >= p_end) return false;
+            while (flat.first_of_group(g + 1) <= p) g++;  // groups without steps are passed over
             const int gs = __ldg(gsp + g), ns = __ldg(gsp + g + 1) - gs;
-            s.item = item; s.k0 = 0; s.k1 = ns; s.gs = gs; s.parts = 1; s.part = 0; s.tail = 0;
+            const long long item_p0 = flat.first_of_group(g);
+            const long long off = p - item_p0;
+            const int t = (int)(off / ns), k0 = (int)(off - (long long)t * ns);
+            const long long left = p_end - p;
+            const int k1 = (left < (long long)(ns - k0)) ? k0 + (int)left : ns;
+            s.item = g * n_tiles + t; s.k0 = k0; s.k1 = k1; s.ns = ns; s.gs = gs;
+            s.cut = k0 != 0 || k1 != ns;
+            // the tail of this CTA's range (the item began inside the range) goes to its second tile
+            s.slot = cta * 2 + ((p_begin < item_p0 + (long long)t * ns) ? 1 : 0);
+            p += k1 - k0;
+            return true;
+        }
+        if (item < n_full) {
+            const int gg = item / n_tiles;
+            const int gs = __ldg(gsp + gg), ns = __ldg(gsp + gg + 1) - gs;
+            s.item = item; s.k0 = 0; s.k1 = ns; s.ns = ns; s.gs = gs; s.cut = false; s.slot = 0;
             item += n_ctas;
             return true;
         }
@@ -178,9 +236,9 @@ struct SegGen {
         tail_done = true;
         if (cta >= (n_items - n_full) * P) return false;
         const int i = cta / P, j = cta - i * P;
-        const int g = (n_full + i) / n_tiles;
-        const int gs = __ldg(gsp + g), ns = __ldg(gsp + g + 1) - gs;
-        s.item = n_full + i; s.gs = gs; s.parts = P; s.part = j; s.tail = i;
+        const int gg = (n_full + i) / n_tiles;
+        const int gs = __ldg(gsp + gg), ns = __ldg(gsp + gg + 1) - gs;
+        s.item = n_full + i; s.gs = gs; s.ns = ns; s.cut = P > 1; s.slot = cta;
         s.k0 = (int)((unsigned)ns * (unsigned)j / (unsigned)P);  // P <= kMaxTailParts: the products fit 32 bits
         s.k1 = (int)((unsigned)ns * (unsigned)(j + 1) / (unsigned)P);
         return true;
@@ -204,8 +262,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __restrict__ packed,
                     const uint4* __restrict__ steps, const int* __restrict__ gsp,
                     const int* __restrict__ rowptr, __half* __restrict__ C, int brow_begin, int brow_end, int rg, int N,
-                    int n_tiles, int n_items, int tail_parts, uint32_t panel_bytes, float* __restrict__ fix_scratch, int* status,
-                    size_t ldc) {
+                    int n_tiles, int n_items, int n_groups, int tail_parts, int balanced, uint32_t panel_bytes,
+                    float* __restrict__ fix_scratch, int* status, size_t ldc, const int* __restrict__ sched_off,
+                    const int* __restrict__ sched_list) {
     static_assert(!(TS && NH == 2), "the panel ring and 32 accumulators do not fit tensor memory together");
     // A loader waits on a stage's `empty` barrier by parity, which only tells phases apart while the waiter is
     // less than two uses ahead of the consumers; with steps consumed in order that holds iff NL <= S.
@@ -234,10 +293,22 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
 
     // The CTA's share of the work (every role walks the same sequence of segments).
     const int n_full = n_items / (int)gridDim.x * (int)gridDim.x;  // items of the complete rounds
+    Flat flat;
+    flat.gsp = gsp; flat.n_tiles = n_tiles; flat.n_groups = n_groups;
+    flat.total = balanced ? (long long)(__ldg(gsp + n_groups) - __ldg(gsp)) * n_tiles : 0;
     auto make_gen = [&]() {
         SegGen sg;
         sg.gsp = gsp; sg.n_tiles = n_tiles; sg.n_items = n_items; sg.n_ctas = (int)gridDim.x; sg.cta = (int)blockIdx.x;
         sg.item = (int)blockIdx.x; sg.n_full = n_full; sg.P = tail_parts; sg.tail_done = false;
+        sg.balanced = balanced != 0; sg.flat = flat; sg.g = 0;
+        sg.p = sg.p_begin = sg.p_end = 0;
+        sg.list = sched_list; sg.li = sg.li_end = 0; sg.lt = 0;
+        if (sched_list) { sg.li = __ldg(sched_off + blockIdx.x); sg.li_end = __ldg(sched_off + blockIdx.x + 1); }
+        if (balanced) {
+            sg.p = sg.p_begin = flat.range_begin((int)gridDim.x, (int)blockIdx.x);
+            sg.p_end = flat.range_begin((int)gridDim.x, (int)blockIdx.x + 1);
+            if (sg.p < sg.p_end) sg.g = flat.group_of(sg.p);
+        }
         return sg;
     };
 
@@ -465,11 +536,32 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                 if (leader) tc_commit(acc_full(buf));
                 ++it;
             };
-            for (int item = blockIdx.x; item < n_full; item += gridDim.x) {  // the complete rounds: whole items
+            if (sched_list) {  // this CTA's list of groups, every tile of each
+                const int l1 = __ldg(sched_off + blockIdx.x + 1);
+                for (int l = __ldg(sched_off + blockIdx.x); l < l1; l++) {
+                    const int g = __ldg(sched_list + l);
+                    const int ns = __ldg(gsp + g + 1) - __ldg(gsp + g);
+                    for (int t = 0; t < n_tiles; t++) run_segment(0, ns);
+                }
+            } else if (balanced) {  // this CTA's range of the flattened (item, step) sequence
+                long long pp = flat.range_begin((int)gridDim.x, (int)blockIdx.x);
+                const long long pe = flat.range_begin((int)gridDim.x, (int)blockIdx.x + 1);
+                int g = pp < pe ? flat.group_of(pp) : 0;
+                while (pp < pe) {
+                    while (flat.first_of_group(g + 1) <= pp) g++;
+                    const int ns = __ldg(gsp + g + 1) - __ldg(gsp + g);
+                    const long long off = pp - flat.first_of_group(g);
+                    const int k0 = (int)(off % ns);
+                    const int k1 = (pe - pp < (long long)(ns - k0)) ? k0 + (int)(pe - pp) : ns;
+                    run_segment(k0, k1);
+                    pp += k1 - k0;
+                }
+            }
+            for (int item = blockIdx.x; !balanced && !sched_list && item < n_full; item += gridDim.x) {  // the complete rounds: whole items
                 const int g = item / n_tiles;
                 run_segment(0, __ldg(gsp + g + 1) - __ldg(gsp + g));
             }
-            if ((int)blockIdx.x < (n_items - n_full) * tail_parts) {  // the last round: one segment of an item
+            if (!balanced && !sched_list && (int)blockIdx.x < (n_items - n_full) * tail_parts) {  // the last round: one segment of an item
                 const int i = (int)blockIdx.x / tail_parts, j = (int)blockIdx.x - i * tail_parts;
                 const int g = (n_full + i) / n_tiles;
                 const unsigned ns = (unsigned)(__ldg(gsp + g + 1) - __ldg(gsp + g));  // times j <= 4: fits 32 bits
@@ -487,6 +579,18 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
         const int quarter = warp & 3;  // a warp may only read tensor-memory lanes [32*(warp%4), +32)
         const bool odd = lane & 1;
         const int et = quarter * 32 + lane;  // index among the 128 epilogue threads = column within a 128-column half
+        if (balanced) {
+            // groups without any block have no steps, so no range reaches them: their rows of C are zeroed here
+            for (int g = (int)blockIdx.x; g < n_groups; g += (int)gridDim.x) {
+                if (__ldg(gsp + g + 1) != __ldg(gsp + g)) continue;
+                const int r0 = brow_begin + g * rg;
+                const int nrows = min(rg, brow_end - r0);
+                for (int row = 0; row < nrows * 16; row++) {
+                    uint4* dst = reinterpret_cast<uint4*>(C + ((size_t)(r0 - brow_begin) * 16 + row) * ldc);
+                    for (int i = et; i < N / 8; i += 128) dst[i] = make_uint4(0, 0, 0, 0);
+                }
+            }
+        }
         uint32_t it = 0;
         SegGen sg = make_gen();
         Seg cs;
@@ -498,8 +602,8 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
             const int hi = (lane < nrows) ? __ldg(rowptr + r0 + lane + 1) : 0;
             const uint32_t nonempty = __ballot_sync(0xffffffffu, hi > lo);
             const uint32_t buf = it % NBUF;
-            const bool partial = cs.parts > 1;
-            float* part_dst = fix_scratch + (size_t)blockIdx.x * (size_t)kFixSlotFloats;  // this CTA's scratch tile
+            const bool partial = cs.cut;
+            float* part_dst = fix_scratch + (size_t)cs.slot * (size_t)kFixSlotFloats;  // scratch tile of this segment
             if (lane == 0) wait_bar(acc_full(buf), (it / NBUF) & 1, abort_addr, status, 6);
             __syncwarp();
             tc_fence_after();
@@ -599,6 +703,52 @@ __global__ void __launch_bounds__(512) sum_cut_items_kernel(const float* __restr
     }
 }
 
+// The same for the balanced schedule.  Block c-1 looks at the boundary between the ranges of CTAs c-1 and c: if it
+// falls strictly inside a work item and is the first boundary to do so, the block adds up that item's segments
+// (tile 1 of the CTA in whose range the item begins, tile 0 of every later CTA up to the one holding its end).
+template <int NH>
+__global__ void __launch_bounds__(512) sum_split_items_kernel(const float* __restrict__ scratch, const int* __restrict__ gsp,
+                                                             __half* __restrict__ C, int brow_begin, int brow_end, int rg, int N,
+                                                             int n_tiles, int n_groups, int n_ctas, size_t ldc) {
+    Flat flat;
+    flat.gsp = gsp; flat.n_tiles = n_tiles; flat.n_groups = n_groups;
+    flat.total = (long long)(__ldg(gsp + n_groups) - __ldg(gsp)) * n_tiles;
+    const int c = (int)blockIdx.x + 1;
+    const long long b = flat.range_begin(n_ctas, c);
+    if (b <= 0 || b >= flat.total) return;
+    int g = flat.group_of(b);
+    while (flat.first_of_group(g + 1) <= b) g++;
+    const int ns = __ldg(gsp + g + 1) - __ldg(gsp + g);
+    const long long off = b - flat.first_of_group(g);
+    const int t = (int)(off / ns);
+    const long long item_p0 = flat.first_of_group(g) + (long long)t * ns;
+    if (b == item_p0) return;                                       // the boundary is the start of an item
+    if (c > 1 && flat.range_begin(n_ctas, c - 1) > item_p0) return;  // an earlier boundary cuts the same item
+    const int c_first = c - 1, c_last = flat.range_owner(n_ctas, item_p0 + ns - 1);
+    const int r0 = brow_begin + g * rg;
+    const int nrows = min(rg, brow_end - r0);
+    for (int r = (int)threadIdx.y; r < nrows; r += (int)blockDim.y) {
+#pragma unroll
+        for (int h = 0; h < NH; h++) {
+            const int n = t * (128 * NH) + h * 128 + (int)threadIdx.x;
+            if (n >= N) continue;
+            float acc[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) acc[i] = 0.0f;
+            for (int cc = c_first; cc <= c_last; cc++) {
+                if (flat.range_begin(n_ctas, cc) == flat.range_begin(n_ctas, cc + 1)) continue;  // a CTA without work
+                const int slot = cc * 2 + (flat.range_begin(n_ctas, cc) < item_p0 ? 1 : 0);
+                const float* src = scratch + (size_t)slot * kFixSlotFloats + ((size_t)(h * RG + r) * 16) * 128 + threadIdx.x;
+#pragma unroll
+                for (int i = 0; i < 16; i++) acc[i] += __ldg(src + (size_t)i * 128);
+            }
+            __half* ccol = C + ((size_t)(r0 - brow_begin + r) * 16) * ldc + (size_t)n;
+#pragma unroll
+            for (int i = 0; i < 16; i++) ccol[(size_t)i * ldc] = __float2half_rn(acc[i]);
+        }
+    }
+}
+
 }  // namespace
 
 #ifdef SMAT_PROFILE2
@@ -666,7 +816,11 @@ int launch_spmm(const PlanView& whole, const void* B, void* C, size_t N, cudaStr
     if (plan.total_steps) est_steps = plan.total_steps / plan.n_groups;
     auto tail_parts = [&](size_t items) { return tail_parts_for(items, sms, split, est_steps); };
     auto rounds = [&](size_t items, bool wide) { return rounds_for(items, sms, split, est_steps, wide); };
+    // a plan's list of groups per CTA covers all its groups and was made for one CTA per SM
+    const bool listed = plan.sched_list != nullptr && plan.sched_ctas == ctx->sm_count && plan.n_groups == whole.n_groups;
+    const bool balanced = !listed && split && plan.balanced;
     int variant = g_spmm_variant;
+    if (variant == 0 && (balanced || listed)) variant = (N >= 256 && plan.nnzb / plan.n_groups >= 256 && est_steps >= 64) ? 3 : 1;
     if (variant == 0) {
         variant = 1;
         if (N >= 256 && plan.nnzb / plan.n_groups >= 256 && est_steps >= 64 &&
@@ -681,15 +835,16 @@ int launch_spmm(const PlanView& whole, const void* B, void* C, size_t N, cudaStr
     const size_t n_items = plan.n_groups * (size_t)n_tiles;
     if (n_items > (size_t)INT_MAX) return fail(SMAT_ERR_RANGE, "too many work items (%zu)", n_items);
     // one CTA per SM; fewer only when there are fewer items than SMs and they are not cut
-    const int parts = (int)tail_parts(n_items);
-    const int grid = (int)((parts > 1 || n_items > sms) ? sms : n_items);
+    const int parts = (balanced || listed) ? 1 : (int)tail_parts(n_items);
+    const int grid = (int)((balanced || listed || parts > 1 || n_items > sms) ? sms : n_items);
     const int n_full = (int)(n_items / (size_t)grid * (size_t)grid);
     auto launch = [&](auto kernel, uint32_t smem_bytes) -> int {
         SMAT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
         kernel<<<grid, kThreads, smem_bytes, stream>>>(
             mapB, reinterpret_cast<const uint8_t*>(plan.packed), reinterpret_cast<const uint4*>(plan.steps), plan.gsp,
             plan.rowptr, reinterpret_cast<__half*>(C), (int)plan.brow_begin, (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles,
-            (int)n_items, parts, panel_rows * 128u, plan.fix_scratch, ctx->d_status, ldc);
+            (int)n_items, (int)plan.n_groups, parts, balanced ? 1 : 0, panel_rows * 128u, plan.fix_scratch, ctx->d_status, ldc,
+            listed ? plan.sched_off : nullptr, listed ? plan.sched_list : nullptr);
         count_launch();
         SMAT_CUDA_TRY(cudaGetLastError());
         return SMAT_OK;
@@ -698,7 +853,22 @@ int launch_spmm(const PlanView& whole, const void* B, void* C, size_t N, cudaStr
     if (variant == 3) rc = launch(spmm_bcsr_tc_kernel<false, 2>, Cfg<2>::SMEM_BYTES);
     else if (variant == 2) rc = launch(spmm_bcsr_tc_kernel<true, 1>, Cfg<1>::SMEM_BYTES);
     else rc = launch(spmm_bcsr_tc_kernel<false, 1>, Cfg<1>::SMEM_BYTES);
-    if (rc != SMAT_OK || parts == 1) return rc;
+    if (rc != SMAT_OK) return rc;
+    if (balanced) {
+        if (grid < 2) return SMAT_OK;
+        if (variant == 3)
+            sum_split_items_kernel<2><<<grid - 1, dim3(128, 4), 0, stream>>>(plan.fix_scratch, plan.gsp, reinterpret_cast<__half*>(C),
+                                                                            (int)plan.brow_begin, (int)plan.brow_end, (int)plan.rg, (int)N,
+                                                                            n_tiles, (int)plan.n_groups, grid, ldc);
+        else
+            sum_split_items_kernel<1><<<grid - 1, dim3(128, 4), 0, stream>>>(plan.fix_scratch, plan.gsp, reinterpret_cast<__half*>(C),
+                                                                            (int)plan.brow_begin, (int)plan.brow_end, (int)plan.rg, (int)N,
+                                                                            n_tiles, (int)plan.n_groups, grid, ldc);
+        count_launch();
+        SMAT_CUDA_TRY(cudaGetLastError());
+        return SMAT_OK;
+    }
+    if (parts == 1) return rc;
     const int cut_items = (int)n_items - n_full;
     if (variant == 3)
         sum_cut_items_kernel<2><<<cut_items, dim3(128, 4), 0, stream>>>(plan.fix_scratch, reinterpret_cast<__half*>(C), (int)plan.brow_begin,

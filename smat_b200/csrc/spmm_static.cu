@@ -33,7 +33,7 @@ namespace {
 constexpr size_t kMaxBlocks = 32768;          // SMAT_STATIC_MAX_BLOCKS
 constexpr size_t kMaxRows = 1048576;          // SMAT_STATIC_MAX_ROWS
 constexpr size_t kMaxGroups = kMaxRows / 16 / 4;  // the smallest group height is 4 block-rows
-constexpr size_t kGspBytes = ((kMaxGroups + 1) * sizeof(int) + 255) / 256 * 256;
+constexpr size_t kGspBytes = ((kMaxGroups + 2) * sizeof(int) + 255) / 256 * 256;  // prefix of step counts + the largest count
 constexpr size_t kStepsBytes = kMaxBlocks * 16;   // a group never has more steps than blocks
 constexpr size_t kBlkBytes = kMaxBlocks * sizeof(int);
 constexpr size_t kPackedBytes = kMaxBlocks * 512;  // the blocks in walk order

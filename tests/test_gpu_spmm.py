@@ -172,6 +172,52 @@ def test_items_cut_across_ctas(Mb, Kb, N, fill, variant):
     assert np.array_equal(C.view(np.uint16), again.view(np.uint16))  # same cuts, same order of addition
 
 
+@pytest.mark.parametrize("variant", ["plan", "smem", "tmem", "wide"])
+def test_balanced_schedule_for_skewed_matrices(variant):
+    """One group of block-rows holds a third of all steps (as the power-law configuration does after the reorder):
+    such plans deal out equal ranges of the flattened (item, step) sequence, so range boundaries fall inside work
+    items almost everywhere and C is assembled from partial tiles; two groups are empty (their rows must be zeroed)."""
+    rng = np.random.default_rng(11)
+    Mb, Kb, N = 1024, 2048, 264
+    counts = rng.integers(1, 4, Mb)
+    counts[160:176] = rng.integers(900, 1100, 16)  # the heavy group
+    counts[80:112] = 0                             # two empty groups
+    brp = np.zeros(Mb + 1, np.int32)
+    brp[1:] = np.cumsum(counts)
+    bci = np.concatenate([np.sort(rng.choice(Kb, c, replace=False)) for c in counts]).astype(np.int32) * 16
+    bv = (rng.standard_normal(brp[-1] * 256) * 0.1).astype(np.float16)
+    B = rng.standard_normal((N, Kb * 16)).astype(np.float16)
+    C = _run(brp, bci, bv, B, Mb * 16, N, Kb * 16, variant)
+    Cref, Cabs = _oracle_c(bv, brp, bci, B, Mb * 16, N, Kb * 16)
+    assert np.all(C[80 * 16:112 * 16] == 0)
+    assert _rel_err(C, Cref, Cabs) <= TOL
+    again = _run(brp, bci, bv, B, Mb * 16, N, Kb * 16, variant)
+    assert np.array_equal(C.view(np.uint16), again.view(np.uint16))
+
+
+def test_listed_schedule_for_skewed_matrices():
+    """Many groups, twenty of them eight times heavier than the rest: the plan deals whole groups out to the CTAs
+    heaviest first (a fixed list per CTA) instead of round-robin; some groups are empty."""
+    rng = np.random.default_rng(12)
+    Mb, Kb, N = 16384, 1024, 72
+    counts = rng.integers(1, 4, Mb)
+    for g in rng.choice(Mb // 16, 20, replace=False):
+        counts[g * 16:(g + 1) * 16] = rng.integers(90, 110, 16)
+    counts[4000 * 1:4000 + 64] = 0
+    brp = np.zeros(Mb + 1, np.int32)
+    brp[1:] = np.cumsum(counts)
+    bci = np.concatenate([np.sort(rng.choice(Kb, c, replace=False)) for c in counts]).astype(np.int32) * 16
+    bv = (rng.standard_normal(brp[-1] * 256) * 0.1).astype(np.float16)
+    B = rng.standard_normal((N, Kb * 16)).astype(np.float16)
+    C = _run(brp, bci, bv, B, Mb * 16, N, Kb * 16, "plan")
+    Cref, Cabs = _oracle_c(bv, brp, bci, B, Mb * 16, N, Kb * 16)
+    assert np.all(C[4000 * 16:4064 * 16] == 0)
+    assert _rel_err(C, Cref, Cabs) <= TOL
+    # whole items only: bit-identical to the round-robin launch of the call entry point
+    C2 = _run(brp, bci, bv, B, Mb * 16, N, Kb * 16, "smem")
+    assert np.array_equal(C.view(np.uint16), C2.view(np.uint16))
+
+
 def test_block_row_range_entry_point():
     torch = _torch()
     p, brp, bci, bv = _problem("powerlaw", 0.01, 64)

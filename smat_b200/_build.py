@@ -36,8 +36,6 @@ def build(force=False, verbose=False):
     if os.environ.get("SMAT_DEFS"):
         for d in os.environ["SMAT_DEFS"].split():
             cmd.insert(1, "-D" + d)
-    if os.environ.get("SMAT_PROFILE"):
-        cmd.insert(1, "-DSMAT_PROFILE")
     subprocess.check_call(cmd, cwd=CSRC)
     return LIB
 

@@ -146,8 +146,7 @@ static int spmm_transient_plan(const void* vals, const int* rowptr, const int* c
     int rc = plan_count_async(rowptr, colidx, K, nnzb, brow_begin, brow_end, rg, reinterpret_cast<int*>(b), stream);
     if (rc == SMAT_OK)
         rc = plan_fill_async(rowptr, colidx, K, nnzb, brow_begin, brow_end, rg, v.gsp, b + sz.gsp_bytes,
-                             reinterpret_cast<int*>(b + sz.gsp_bytes + sz.steps_bytes),
-                             b + sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes, stream);
+                             reinterpret_cast<int*>(b + sz.gsp_bytes + sz.steps_bytes), stream);
     if (rc == SMAT_OK)
         rc = pack_values_async(rowptr, vals, v.gsp, v.steps, v.blk, b + sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes, brow_begin,
                                brow_end, rg, nnzb, stream);

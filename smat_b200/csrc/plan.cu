@@ -83,8 +83,7 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* total, int* sh) 
 template <bool FILL>
 __global__ void __launch_bounds__(kPlanThreads)
 plan_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx, int brow_begin, int brow_end, int rg, int Kb,
-            int n_groups, int* __restrict__ gsp, uint4* __restrict__ steps, int* __restrict__ blk,
-            uint8_t* __restrict__ packed) {
+            int n_groups, int* __restrict__ gsp, uint4* __restrict__ steps, int* __restrict__ blk) {
     extern __shared__ uint32_t sm[];
     uint32_t* masks = sm;                                 // [kWindow] row mask per block-column
     int* blk_pre = reinterpret_cast<int*>(sm + kWindow);  // [kWindow] exclusive block number (FILL only)
@@ -308,7 +307,7 @@ int plan_count_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb
     const size_t smem_count = (size_t)kWindow * 4;
     SMAT_CUDA_TRY(cudaFuncSetAttribute(plan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_count));
     plan_kernel<false><<<grid, kPlanThreads, smem_count, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, (int)rg,
-                                                                  (int)(K / 16), (int)n_groups, gsp, nullptr, nullptr, nullptr);
+                                                                  (int)(K / 16), (int)n_groups, gsp, nullptr, nullptr);
     count_launch();
     plan_scan_kernel<<<1, 1024, 0, stream>>>(gsp, (int)n_groups + 1);
     count_launch();
@@ -317,7 +316,7 @@ int plan_count_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb
 }
 
 int plan_fill_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
-                    size_t rg, const int* gsp, void* steps, int* blk, void* packed, cudaStream_t stream, const DeviceCtx* ctx_in) {
+                    size_t rg, const int* gsp, void* steps, int* blk, cudaStream_t stream, const DeviceCtx* ctx_in) {
     const DeviceCtx* ctx = nullptr;
     if (int rc = plan_launch_setup(ctx_in, &ctx)) return rc;
     const size_t n_groups = (brow_end - brow_begin + rg - 1) / rg;
@@ -327,8 +326,7 @@ int plan_fill_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb,
     SMAT_CUDA_TRY(cudaFuncSetAttribute(plan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fill));
     plan_kernel<true><<<grid, kPlanThreads, smem_fill, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, (int)rg,
                                                                  (int)(K / 16), (int)n_groups, const_cast<int*>(gsp),
-                                                                 reinterpret_cast<uint4*>(steps), blk,
-                                                                 reinterpret_cast<uint8_t*>(packed));
+                                                                 reinterpret_cast<uint4*>(steps), blk);
     count_launch();
     SMAT_CUDA_TRY(cudaGetLastError());
     return SMAT_OK;
@@ -475,7 +473,7 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
     p->v.total_steps = (size_t)(total_steps > 0 ? total_steps : 0);
     p->v.balanced = balanced;
     rc = plan_fill_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, rg, gsp, const_cast<void*>(p->v.steps),
-                         const_cast<int*>(p->v.blk), const_cast<void*>(p->v.packed), (cudaStream_t)stream);
+                         const_cast<int*>(p->v.blk), (cudaStream_t)stream);
     if (rc == SMAT_OK)
         rc = pack_values_async(bcsrRowPtrA, bcsrValuesA, gsp, p->v.steps, p->v.blk, const_cast<void*>(p->v.packed), brow_begin,
                                brow_end, rg, nnzb, (cudaStream_t)stream);

@@ -124,7 +124,7 @@ PlanSizes plan_sizes(size_t nnzb, size_t brow_begin, size_t brow_end, size_t rg,
 int plan_count_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
                      size_t rg, int* gsp, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
 int plan_fill_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
-                    size_t rg, const int* gsp, void* steps, int* blk, void* packed, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
+                    size_t rg, const int* gsp, void* steps, int* blk, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
 // Copies the value blocks of block-rows [brow_begin, brow_end) into their places in the packed stream.
 int pack_values_async(const int* rowptr, const void* vals, const int* gsp, const void* steps, const int* blk, void* packed,
                       size_t brow_begin, size_t brow_end, size_t rg, size_t nnzb, cudaStream_t stream,

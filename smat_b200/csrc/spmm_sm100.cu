@@ -60,13 +60,7 @@ namespace {
 
 constexpr int RG = kPlanRowsPerGroup;  // block-rows per work item
 constexpr int CAP = kPlanBlocksPerStep;  // most blocks a step can carry
-#ifndef SMAT_UNIFORM_ISSUE
-#define SMAT_UNIFORM_ISSUE 1
-#endif
-#ifndef SMAT_NL
-#define SMAT_NL 4
-#endif
-constexpr int NL = SMAT_NL;            // loader warps
+constexpr int NL = 4;                  // loader warps
 #ifndef SMAT_L2_PREFETCH
 #define SMAT_L2_PREFETCH 1
 #endif
@@ -108,26 +102,9 @@ __device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
 #ifdef SMAT_PROFILE2
 __device__ long long g_prof2[16];
 #endif
-#ifdef SMAT_PROFILE
-__device__ unsigned long long g_prof[16];
-#define PROF_ADD(code, t) atomicAdd(&g_prof[code], (unsigned long long)(t))
-#else
-#define PROF_ADD(code, t)
-#endif
 
 // Bounded mbarrier wait.  After the first time-out anywhere in the CTA every wait returns at once.
-__device__ __forceinline__ void wait_bar_impl(uint32_t bar, uint32_t parity, uint32_t abort_addr, int* status, int code);
 __device__ __forceinline__ void wait_bar(uint32_t bar, uint32_t parity, uint32_t abort_addr, int* status, int code) {
-#ifdef SMAT_PROFILE
-    const long long t0 = clock64();
-    wait_bar_impl(bar, parity, abort_addr, status, code);
-    PROF_ADD(code, clock64() - t0);
-    PROF_ADD(8 + code, 1);
-#else
-    wait_bar_impl(bar, parity, abort_addr, status, code);
-#endif
-}
-__device__ __forceinline__ void wait_bar_impl(uint32_t bar, uint32_t parity, uint32_t abort_addr, int* status, int code) {
     if (mbar_try_wait(bar, parity)) return;
     if (ld_shared_u32(abort_addr)) return;
     const long long t0 = clock64();
@@ -287,9 +264,6 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-#ifdef SMAT_PROFILE
-    const long long prof_t0 = clock64();
-#endif
 
     // The CTA's share of the work (every role walks the same sequence of segments).
     const int n_full = n_items / (int)gridDim.x * (int)gridDim.x;  // items of the complete rounds
@@ -651,9 +625,6 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
         }
     }
 
-#ifdef SMAT_PROFILE
-    if (threadIdx.x == 0) PROF_ADD(0, clock64() - prof_t0);
-#endif
     tc_fence_before();
     __syncthreads();
     if (ld_shared_u32(abort_addr)) {
@@ -755,13 +726,6 @@ __global__ void __launch_bounds__(512) sum_split_items_kernel(const float* __res
 extern "C" void smat_prof2_read(long long* out) {
     cudaDeviceSynchronize();
     cudaMemcpyFromSymbol(out, g_prof2, sizeof(long long) * 16);
-}
-#endif
-#ifdef SMAT_PROFILE
-extern "C" void smat_prof_read(unsigned long long* out, int reset) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, g_prof, sizeof(unsigned long long) * 16);
-    if (reset) { unsigned long long z[16] = {}; cudaMemcpyToSymbol(g_prof, z, sizeof(z)); }
 }
 #endif
 

@@ -118,7 +118,7 @@ extern "C" int smat_spmm_bcsr_f16_static(const void* vals, const int* rowptr, co
     // the status word shares the array with earlier calls: start from zero
     SMAT_CUDA_TRY(cudaMemsetAsync(d->ctx.d_status, 0, sizeof(int), stream));
     if (int rc = plan_count_async(rowptr, colidx, K, nnzb, 0, Mb, rg, gsp, stream, &d->ctx)) return rc;
-    if (int rc = plan_fill_async(rowptr, colidx, K, nnzb, 0, Mb, rg, gsp, steps, blk, packed, stream, &d->ctx)) return rc;
+    if (int rc = plan_fill_async(rowptr, colidx, K, nnzb, 0, Mb, rg, gsp, steps, blk, stream, &d->ctx)) return rc;
     if (int rc = pack_values_async(rowptr, vals, gsp, steps, blk, packed, 0, Mb, rg, nnzb, stream, &d->ctx)) return rc;
     return launch_spmm(v, B, C, N, stream, &d->ctx);
 }

@@ -49,6 +49,8 @@
 #include <cuda_fp16.h>
 #include <limits.h>
 
+#include <type_traits>
+
 #include "ptx_sm100.cuh"
 #include "smat_internal.h"
 
@@ -99,9 +101,6 @@ __device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
     asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 
-#ifdef SMAT_PROFILE2
-__device__ long long g_prof2[16];
-#endif
 
 // Bounded mbarrier wait.  After the first time-out anywhere in the CTA every wait returns at once.
 __device__ __forceinline__ void wait_bar(uint32_t bar, uint32_t parity, uint32_t abort_addr, int* status, int code) {
@@ -168,17 +167,19 @@ struct Flat {
 //    length of the items; an item that a range boundary falls into is computed in segments.
 // A cut item is assembled from fp32 partial tiles: each CTA stores its segment's result to a scratch tile (one
 // per CTA, two in the balanced schedule: the head and the tail of its range) and a small second kernel adds them.
+// SCHED: 0 = round-robin with a cut last round, 1 = listed, 2 = balanced ranges.
+template <int SCHED>
 struct SegGen {
     const int* gsp;
     int n_tiles, n_items, n_ctas, cta, item, n_full, P;
-    bool tail_done, balanced;
+    bool tail_done;
     Flat flat;
     long long p, p_begin, p_end;
     int g;
     const int* list;      // listed schedule: the groups of this CTA, else null
     int li, li_end, lt;   // position in the list, its end, next tile of the current group
     __device__ __forceinline__ bool next(Seg& s) {
-        if (list) {
+        if (SCHED == 1) {
             if (li >= li_end) return false;
             const int gg = __ldg(list + li);
             const int gs = __ldg(gsp + gg), ns = __ldg(gsp + gg + 1) - gs;
@@ -186,7 +187,7 @@ struct SegGen {
             if (++lt == n_tiles) { lt = 0; li++; }
             return true;
         }
-        if (balanced) {
+        if (SCHED == 2) {
             if (p >= p_end) return false;
             while (flat.first_of_group(g + 1) <= p) g++;  // groups without steps are passed over
             const int gs = __ldg(gsp + g), ns = __ldg(gsp + g + 1) - gs;
@@ -234,15 +235,18 @@ static_assert((size_t)kFixSlotFloats * sizeof(float) == (2 * 16 * 16 * 128) * si
 // NH = 1: a work item is 128 columns of C wide.  NH = 2: 256 columns -- every A block then feeds two
 //   independent MMAs (one per 128-column half, own accumulator), which doubles the MMA work per stage
 //   hand-over and halves the A traffic per MMA; the 32 accumulators fill tensor memory (one buffer).
-template <bool TS, int NH>
+template <bool TS, int NH, int SCHED>
 __global__ void __launch_bounds__(kThreads, 1)
 spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __restrict__ packed,
                     const uint4* __restrict__ steps, const int* __restrict__ gsp,
                     const int* __restrict__ rowptr, __half* __restrict__ C, int brow_begin, int brow_end, int rg, int N,
-                    int n_tiles, int n_items, int n_groups, int tail_parts, int balanced, uint32_t panel_bytes,
+                    int n_tiles, int n_items, int n_groups, int tail_parts, uint32_t panel_bytes,
                     float* __restrict__ fix_scratch, int* status, size_t ldc, const int* __restrict__ sched_off,
                     const int* __restrict__ sched_list) {
     static_assert(!(TS && NH == 2), "the panel ring and 32 accumulators do not fit tensor memory together");
+    // The schedule is a template parameter: measured, the code generated for the MMA issue loop changed by up to 35 %
+    // with the shape of the control flow around it, so each schedule gets a kernel with only its own loops.
+    constexpr bool listed = SCHED == 1, balanced = SCHED == 2;
     // A loader waits on a stage's `empty` barrier by parity, which only tells phases apart while the waiter is
     // less than two uses ahead of the consumers; with steps consumed in order that holds iff NL <= S.
     static_assert(NL <= (int)Cfg<NH>::S, "more loader warps than stages would alias barrier phases");
@@ -271,13 +275,13 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
     flat.gsp = gsp; flat.n_tiles = n_tiles; flat.n_groups = n_groups;
     flat.total = balanced ? (long long)(__ldg(gsp + n_groups) - __ldg(gsp)) * n_tiles : 0;
     auto make_gen = [&]() {
-        SegGen sg;
+        SegGen<SCHED> sg;
         sg.gsp = gsp; sg.n_tiles = n_tiles; sg.n_items = n_items; sg.n_ctas = (int)gridDim.x; sg.cta = (int)blockIdx.x;
         sg.item = (int)blockIdx.x; sg.n_full = n_full; sg.P = tail_parts; sg.tail_done = false;
-        sg.balanced = balanced != 0; sg.flat = flat; sg.g = 0;
+        sg.flat = flat; sg.g = 0;
         sg.p = sg.p_begin = sg.p_end = 0;
         sg.list = sched_list; sg.li = sg.li_end = 0; sg.lt = 0;
-        if (sched_list) { sg.li = __ldg(sched_off + blockIdx.x); sg.li_end = __ldg(sched_off + blockIdx.x + 1); }
+        if (listed) { sg.li = __ldg(sched_off + blockIdx.x); sg.li_end = __ldg(sched_off + blockIdx.x + 1); }
         if (balanced) {
             sg.p = sg.p_begin = flat.range_begin((int)gridDim.x, (int)blockIdx.x);
             sg.p_end = flat.range_begin((int)gridDim.x, (int)blockIdx.x + 1);
@@ -319,7 +323,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
         // registers (a record whose descriptor load is still in flight is never copied): the descriptor
         // of position i + U is requested while position i is consumed.  One thread per warp works.
         if (lane == 0) {
-            SegGen sg = make_gen();
+            SegGen<SCHED> sg = make_gen();
             Seg cs;
             bool have = sg.next(cs);
             uint32_t h_st0 = 0, h_next = (uint32_t)j;  // sequence position of the segment's first step; next position of this warp
@@ -353,27 +357,15 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
             for (int a = 0; a < U; a++) gen(rec[a]);
 #pragma unroll
             for (int a = 0; a < U / 2; a++) prefetch(rec[a]);
-#ifdef SMAT_PROFILE2
-            long long lw = 0, li = 0, lg = 0, ln = 0;
-#endif
             bool more = true;
             while (more) {
 #pragma unroll
                 for (int a = 0; a < U; a++) {
                     StepRec& r = rec[a];
                     if (!r.live) { more = false; break; }
-#ifdef SMAT_PROFILE2
-                    const long long l0 = clock64();
-#endif
                     prefetch(rec[(a + U / 2) % U]);
                     const uint32_t slot = r.st % S;
-#ifdef SMAT_PROFILE2
-                    const long long l1 = clock64();
-#endif
                     wait_bar(empty(slot), ((r.st / S) & 1) ^ 1, abort_addr, status, 1);
-#ifdef SMAT_PROFILE2
-                    const long long l2 = clock64();
-#endif
                     const uint32_t stage = base + OFF_STAGE + slot * STAGE_BYTES;
                     const uint32_t a_bytes = (uint32_t)(__popc(r.d.z) + __popc(r.d.w)) * ABLK_BYTES;
                     st_shared_u32(base + OFF_META + slot * 8, r.d.z);
@@ -381,19 +373,9 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                     mbar_arrive_expect_tx(full(slot), panel_bytes + a_bytes);
                     tma_load_2d(stage, &mapB, (int)r.d.x, r.tile * NT, full(slot));
                     bulk_load(stage + PANEL_BYTES, packed + (size_t)r.d.y * 256, a_bytes, full(slot));
-#ifdef SMAT_PROFILE2
-                    const long long l3 = clock64();
-#endif
                     gen(r);  // this register set now follows the warp's step U positions ahead
-#ifdef SMAT_PROFILE2
-                    const long long l4 = clock64();
-                    lg += (l1 - l0) + (l4 - l3); lw += l2 - l1; li += l3 - l2; ln++;
-#endif
                 }
             }
-#ifdef SMAT_PROFILE2
-            if (blockIdx.x == 0 && j == 0) { g_prof2[10] = lw; g_prof2[11] = li; g_prof2[12] = lg; g_prof2[13] = ln; }
-#endif
         }
         __syncwarp();
     } else if (warp < NL + NC) {
@@ -401,7 +383,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
         if (TS && lane == 0) {
             const uint32_t j = (uint32_t)(warp - NL);
             uint32_t st = 0;
-            SegGen sg = make_gen();
+            SegGen<SCHED> sg = make_gen();
             Seg cs;
             while (sg.next(cs)) {
                 for (int k = cs.k0; k < cs.k1; k++, st++) {
@@ -439,9 +421,6 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
             const uint32_t own32 = (rows_m & 0xffffu) | (rows_m << 16);  // this warp's rows in both sub-columns of a mask word
             const bool leader = elect_one();  // the lane that issues; fixed, so that its commits cover its MMAs
             uint32_t st = 0, it = 0;
-#ifdef SMAT_PROFILE2
-            long long pw = 0, ps = 0, pm = 0, pc = 0, pn = 0, pk = 0;
-#endif
             // One segment = steps [k0, k1) of an item.  Kept as a plain counted loop called from two plain loops
             // (measured: driving it from the segment generator's control flow made the issue loop ~35 % slower).
             auto run_segment = [&](const int k0, const int k1) {
@@ -453,14 +432,8 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                 const uint32_t acc0 = tmem_base + buf * RG * 16 * NH;
                 for (int k = k0; k < k1; k++, st++) {
                     const uint32_t slot = st % S;
-#ifdef SMAT_PROFILE2
-                    const long long m0 = clock64();
-#endif
                     wait_bar(TS ? tfull(slot) : full(slot), (st / S) & 1, abort_addr, status, 4);
                     tc_fence_after();
-#ifdef SMAT_PROFILE2
-                    const long long m1 = clock64();
-#endif
                     const uint32_t stage = base + OFF_STAGE + slot * STAGE_BYTES;
                     const uint32_t p_lo = (uint32_t)smem_desc_k_sw128(stage);               // panel, sub-column 0
                     const uint32_t tpanel = tmem_base + TMEM_PANELS + slot * 32;            // its copy in tensor memory
@@ -470,10 +443,6 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                     const uint32_t mw0 = __ballot_sync(0xffffffffu, (wlo >> lane) & 1u);
                     const uint32_t mw1 = __ballot_sync(0xffffffffu, (whi >> lane) & 1u);
                     uint32_t qbase = 0;
-#ifdef SMAT_PROFILE2
-                    const long long m2 = clock64() + (long long)(mw1 & 0u);
-                    pk += __popc(mw0 & own32) + __popc(mw1 & own32);
-#endif
 #pragma unroll
                     for (int half = 0; half < 2; half++) {
                         const uint32_t mw = half ? mw1 : mw0;
@@ -498,19 +467,12 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                         }
                         qbase += (uint32_t)__popc(mw);
                     }
-#ifdef SMAT_PROFILE2
-                    const long long m3 = clock64();
-#endif
                     if (leader) tc_commit(empty(slot));
-#ifdef SMAT_PROFILE2
-                    const long long m4 = clock64();
-                    pw += m1 - m0; ps += m2 - m1; pm += m3 - m2; pc += m4 - m3; pn++;
-#endif
                 }
                 if (leader) tc_commit(acc_full(buf));
                 ++it;
             };
-            if (sched_list) {  // this CTA's list of groups, every tile of each
+            if (listed) {  // this CTA's list of groups, every tile of each
                 const int l1 = __ldg(sched_off + blockIdx.x + 1);
                 for (int l = __ldg(sched_off + blockIdx.x); l < l1; l++) {
                     const int g = __ldg(sched_list + l);
@@ -531,11 +493,11 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                     pp += k1 - k0;
                 }
             }
-            for (int item = blockIdx.x; !balanced && !sched_list && item < n_full; item += gridDim.x) {  // the complete rounds: whole items
+            for (int item = blockIdx.x; SCHED == 0 && item < n_full; item += gridDim.x) {  // the complete rounds: whole items
                 const int g = item / n_tiles;
                 run_segment(0, __ldg(gsp + g + 1) - __ldg(gsp + g));
             }
-            if (!balanced && !sched_list && (int)blockIdx.x < (n_items - n_full) * tail_parts) {  // the last round: one segment of an item
+            if (SCHED == 0 && (int)blockIdx.x < (n_items - n_full) * tail_parts) {  // the last round: one segment of an item
                 const int i = (int)blockIdx.x / tail_parts, j = (int)blockIdx.x - i * tail_parts;
                 const int g = (n_full + i) / n_tiles;
                 const unsigned ns = (unsigned)(__ldg(gsp + g + 1) - __ldg(gsp + g));  // times j <= 4: fits 32 bits
@@ -543,9 +505,6 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                 const int k1 = __shfl_sync(0xffffffffu, (int)(ns * (unsigned)(j + 1) / (unsigned)tail_parts), 0);
                 run_segment(k0, k1);
             }
-#ifdef SMAT_PROFILE2
-            if (blockIdx.x == 0 && m == 0 && leader) { g_prof2[0] = pw; g_prof2[1] = ps; g_prof2[2] = pm; g_prof2[3] = pc; g_prof2[4] = pn; g_prof2[5] = pk; }
-#endif
         }
         __syncwarp();
     } else {
@@ -566,7 +525,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
             }
         }
         uint32_t it = 0;
-        SegGen sg = make_gen();
+        SegGen<SCHED> sg = make_gen();
         Seg cs;
         for (; sg.next(cs); ++it) {
             const int g = cs.item / n_tiles, t = cs.item - g * n_tiles;
@@ -722,12 +681,6 @@ __global__ void __launch_bounds__(512) sum_split_items_kernel(const float* __res
 
 }  // namespace
 
-#ifdef SMAT_PROFILE2
-extern "C" void smat_prof2_read(long long* out) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, g_prof2, sizeof(long long) * 16);
-}
-#endif
 
 int g_spmm_variant = 0;
 
@@ -807,16 +760,22 @@ int launch_spmm(const PlanView& whole, const void* B, void* C, size_t N, cudaStr
         kernel<<<grid, kThreads, smem_bytes, stream>>>(
             mapB, reinterpret_cast<const uint8_t*>(plan.packed), reinterpret_cast<const uint4*>(plan.steps), plan.gsp,
             plan.rowptr, reinterpret_cast<__half*>(C), (int)plan.brow_begin, (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles,
-            (int)n_items, (int)plan.n_groups, parts, balanced ? 1 : 0, panel_rows * 128u, plan.fix_scratch, ctx->d_status, ldc,
+            (int)n_items, (int)plan.n_groups, parts, panel_rows * 128u, plan.fix_scratch, ctx->d_status, ldc,
             listed ? plan.sched_off : nullptr, listed ? plan.sched_list : nullptr);
         count_launch();
         SMAT_CUDA_TRY(cudaGetLastError());
         return SMAT_OK;
     };
+    auto launch_sched = [&](auto sched) -> int {
+        constexpr int SCHED = decltype(sched)::value;
+        if (variant == 3) return launch(spmm_bcsr_tc_kernel<false, 2, SCHED>, Cfg<2>::SMEM_BYTES);
+        if (variant == 2) return launch(spmm_bcsr_tc_kernel<true, 1, SCHED>, Cfg<1>::SMEM_BYTES);
+        return launch(spmm_bcsr_tc_kernel<false, 1, SCHED>, Cfg<1>::SMEM_BYTES);
+    };
     int rc;
-    if (variant == 3) rc = launch(spmm_bcsr_tc_kernel<false, 2>, Cfg<2>::SMEM_BYTES);
-    else if (variant == 2) rc = launch(spmm_bcsr_tc_kernel<true, 1>, Cfg<1>::SMEM_BYTES);
-    else rc = launch(spmm_bcsr_tc_kernel<false, 1>, Cfg<1>::SMEM_BYTES);
+    if (listed) rc = launch_sched(std::integral_constant<int, 1>{});
+    else if (balanced) rc = launch_sched(std::integral_constant<int, 2>{});
+    else rc = launch_sched(std::integral_constant<int, 0>{});
     if (rc != SMAT_OK) return rc;
     if (balanced) {
         if (grid < 2) return SMAT_OK;

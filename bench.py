@@ -335,6 +335,25 @@ def main():
     e2e_ms = float(t.item())
     e2e_value = flops_total / (e2e_ms * 1e-3) * 1e-12
 
+    # ---------------- optional exchange step, reported beside the SpMM: all-gather of the C shards ----------------
+    gather = None
+    if dist is not None:
+        C_full = torch.empty((p.M, N), dtype=torch.float16, device="cuda")
+        for _ in range(2):
+            S.all_gather_rows(Cd, bounds, out=C_full)
+        barrier()
+        g_steps = 5
+        e0.record()
+        for _ in range(g_steps):
+            S.all_gather_rows(Cd, bounds, out=C_full)
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / g_steps], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        gather = {"ms": round(float(t.item()), 4), "bytes_received_per_rank": int(p.M * N * 2 - (b1 - b0) * 16 * N * 2),
+                  "note": "padded NCCL all_gather of the C shards + copy into place; not part of value or e2e"}
+        del C_full
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -398,6 +417,8 @@ def main():
     }
     if other is not None:
         out["gpu_baselines"] = other
+    if gather is not None:
+        out["c_allgather"] = gather
     print(json.dumps(out), flush=True)
     if dist is not None:
         dist.destroy_process_group()

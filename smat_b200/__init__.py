@@ -14,6 +14,7 @@ from .api import (  # noqa: F401
     SmatError,
     SparseMatrix,
     Tester,
+    all_gather_rows,
     apply_row_permutation,
     jaccard_group,
     launch_count,

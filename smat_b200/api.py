@@ -139,6 +139,33 @@ def partition_block_rows(bcsr_rowptr_host, parts):
     return bounds.astype(np.int64)
 
 
+def all_gather_rows(C_shard, bounds, out=None, group=None):
+    """Optional exchange step after a sharded SpMM: every rank ends up with all rows of C.
+
+    ``C_shard`` holds this rank's rows (block-rows [bounds[rank], bounds[rank + 1]) of the partition, 16 rows each);
+    shards differ in height, so each is padded to the tallest one for one all_gather (NCCL over NVLink for CUDA
+    tensors; any torch.distributed backend works) and the pieces are copied into ``out`` ([bounds[-1] * 16, N]).
+    Not part of the timed SpMM: C is left sharded unless the caller asks for this."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    rows = [int(bounds[r + 1] - bounds[r]) * 16 for r in range(world)]
+    N = C_shard.shape[1]
+    assert C_shard.shape[0] == rows[dist.get_rank(group)]
+    tallest = max(rows)
+    padded = C_shard if C_shard.shape[0] == tallest else torch.cat(
+        [C_shard, C_shard.new_zeros((tallest - C_shard.shape[0], N))])
+    pieces = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(pieces, padded.contiguous(), group=group)
+    if out is None:
+        out = C_shard.new_empty((sum(rows), N))
+    at = 0
+    for r in range(world):
+        out[at:at + rows[r]].copy_(pieces[r][:rows[r]])
+        at += rows[r]
+    return out
+
+
 # ------------------------------------------------------------------------------------------------
 # device objects
 # ------------------------------------------------------------------------------------------------

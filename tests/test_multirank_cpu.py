@@ -45,6 +45,9 @@ def _worker(rank, world, port, out_dir):
         np.save(os.path.join(out_dir, "ranges.npy"), torch.stack(allr).numpy())
         np.save(os.path.join(out_dir, "total.npy"), np.array([len(bci), p.M // 16]))
     np.save(os.path.join(out_dir, f"shard{rank}.npy"), shard)
+    # the optional exchange step: every rank assembles the whole C from the shards of unequal height
+    gathered = S.all_gather_rows(torch.from_numpy(shard), bounds)
+    np.save(os.path.join(out_dir, f"gathered{rank}.npy"), gathered.numpy())
     dist.barrier()
     dist.destroy_process_group()
 
@@ -60,3 +63,5 @@ def test_two_ranks_partition_and_tile_the_result(tmp_path):
     full = np.load(tmp_path / "full.npy")
     tiled = np.concatenate([np.load(tmp_path / f"shard{r}.npy") for r in range(world)])
     assert np.array_equal(tiled.view(np.uint32), full.view(np.uint32))
+    for r in range(world):
+        assert np.array_equal(np.load(tmp_path / f"gathered{r}.npy").view(np.uint32), full.view(np.uint32))

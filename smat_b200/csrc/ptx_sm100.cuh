@@ -64,6 +64,21 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
         ::"r"(dst_smem), "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
 }
+// Tiled 2D bulk store shared -> global of the box the tensor map describes, at element coordinates (x, y); x * element
+// size must be a multiple of 16 bytes and no coordinate negative.  Completion is tracked by bulk groups.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src_smem, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y),
+                 "r"(src_smem)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most `Pending` of this thread's bulk groups still READ their shared-memory source.
+template <int Pending>
+__device__ __forceinline__ void bulk_wait_group_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(Pending) : "memory");
+}
+// Waits until all of this thread's bulk groups have completed (their writes performed).
+__device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // Bulk copy of `bytes` contiguous bytes (multiple of 16, both addresses 16-byte aligned) global -> shared.
 __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),

@@ -63,6 +63,9 @@ namespace {
 constexpr int RG = kPlanRowsPerGroup;  // block-rows per work item
 constexpr int CAP = kPlanBlocksPerStep;  // most blocks a step can carry
 constexpr int NL = 4;                  // loader warps
+#ifndef SMAT_TMA_EPILOGUE
+#define SMAT_TMA_EPILOGUE 1
+#endif
 #ifndef SMAT_L2_PREFETCH
 #define SMAT_L2_PREFETCH 1
 #endif
@@ -84,7 +87,13 @@ struct Cfg {
     static constexpr uint32_t OFF_BAR = OFF_META + S * 8;
     static constexpr uint32_t N_BARS = 3 * S + 4;
     static constexpr uint32_t OFF_MISC = OFF_BAR + N_BARS * 8;
-    static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;  // slack for the manual 1024-byte alignment
+    // three fp16 tiles of 16 rows x 128 columns that the epilogue hands to TMA stores, 1024-byte aligned
+    static constexpr uint32_t OFF_EPI = (OFF_MISC + 16 + 1023) / 1024 * 1024;
+    static constexpr uint32_t EPI_TILE_BYTES = 16 * 128 * 2;
+    // (narrow items only: wide items have no room left for them beside five stages, and their items are long enough
+    // for the epilogue not to matter)
+    static constexpr bool TMA_EPILOGUE = SMAT_TMA_EPILOGUE && NH == 1;
+    static constexpr uint32_t SMEM_BYTES = (TMA_EPILOGUE ? OFF_EPI + 3 * EPI_TILE_BYTES : OFF_MISC + 16) + 1024;  // slack for the manual 1024-byte alignment
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
     static_assert(STAGE_BYTES % 1024 == 0 && CAP <= 32, "stage alignment");
 };
@@ -96,6 +105,9 @@ __device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
     uint32_t v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
     return v;
+}
+__device__ __forceinline__ void st_shared_u16(uint32_t addr, unsigned short v) {
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(v) : "memory");
 }
 __device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
     asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
@@ -237,7 +249,8 @@ static_assert((size_t)kFixSlotFloats * sizeof(float) == (2 * 16 * 16 * 128) * si
 //   hand-over and halves the A traffic per MMA; the 32 accumulators fill tensor memory (one buffer).
 template <bool TS, int NH, int SCHED>
 __global__ void __launch_bounds__(kThreads, 1)
-spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __restrict__ packed,
+spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapC,
+                    const uint8_t* __restrict__ packed,
                     const uint4* __restrict__ steps, const int* __restrict__ gsp,
                     const int* __restrict__ rowptr, __half* __restrict__ C, int brow_begin, int brow_end, int rg, int N,
                     int n_tiles, int n_items, int n_groups, int tail_parts, uint32_t panel_bytes,
@@ -297,6 +310,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
         fence_barrier_init();
         fence_proxy_async();
         prefetch_tensormap(&mapB);
+        prefetch_tensormap(&mapC);
     }
     if (warp == NL) {
         tmem_alloc(tmem_slot, 512);
@@ -524,7 +538,8 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                 }
             }
         }
-        uint32_t it = 0;
+        uint32_t it = 0, epi_n = 0;
+        const uint32_t c_pitch = (uint32_t)(N < 128 ? N : 128) * 2u;  // bytes per row of a tile = the box of mapC
         SegGen<SCHED> sg = make_gen();
         Seg cs;
         for (; sg.next(cs); ++it) {
@@ -568,6 +583,28 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
                         for (int i = 0; i < 16; i++) d[(size_t)i * 128] = __uint_as_float(v[i]);
                         continue;
                     }
+                    if constexpr (G::TMA_EPILOGUE) {
+                        // fp16 tile of this block-row (16 rows x 128 columns, row-major, `c_pitch` bytes per row) in shared
+                        // memory, handed to one TMA store; three tiles in rotation: the tile written now was last read by
+                        // the store issued three tiles ago, whose completion the issuing thread awaited before the
+                        // barrier of the previous tile.
+                        const uint32_t tile = base + G::OFF_EPI + (epi_n % 3u) * G::EPI_TILE_BYTES;
+                        if ((uint32_t)et * 2u < c_pitch) {  // C narrower than a tile: the rows of the box are N columns long
+#pragma unroll
+                            for (int i = 0; i < 16; i++)
+                                st_shared_u16(tile + (uint32_t)i * c_pitch + (uint32_t)et * 2u,
+                                              __half_as_ushort(__float2half_rn(__uint_as_float(v[i]))));
+                        }
+                        fence_proxy_async();
+                        if (et == 0) bulk_wait_group_read<1>();
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (et == 0) {
+                            tma_store_2d(&mapC, tile, t * NT + h * 128, (r0 - brow_begin + r) * 16);
+                            bulk_commit_group();
+                        }
+                        epi_n++;
+                        continue;
+                    }
                     __half* crow = C + ((size_t)(r0 - brow_begin + r) * 16 + (odd ? 8 : 0)) * ldc + (size_t)(n & ~1);
 #pragma unroll
                     for (int i = 0; i < 8; i++) {
@@ -584,6 +621,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __r
         }
     }
 
+    if (G::TMA_EPILOGUE && warp == NL + NC + NM && lane == 0) bulk_wait_group_all();  // the thread that issued the stores of C
     tc_fence_before();
     __syncthreads();
     if (ld_shared_u32(abort_addr)) {
@@ -748,6 +786,8 @@ int launch_spmm(const PlanView& whole, const void* B, void* C, size_t N, cudaStr
     const uint32_t panel_rows = (uint32_t)(N < NTI ? N : NTI);
     CUtensorMap mapB;
     if (int rc = encode_tensor_map_2d_f16(&mapB, B, plan.K, N, plan.K * 2, 64, panel_rows, 128, 0)) return rc;
+    CUtensorMap mapC;  // C as the epilogue stores it: boxes of 16 rows x 128 columns (N columns when C is narrower)
+    if (int rc = encode_tensor_map_2d_f16(&mapC, C, N, nb_rows * 16, ldc * 2, (uint32_t)(N < 128 ? N : 128), 16, 0, 0)) return rc;
     const int n_tiles = (int)((N + NTI - 1) / NTI);
     const size_t n_items = plan.n_groups * (size_t)n_tiles;
     if (n_items > (size_t)INT_MAX) return fail(SMAT_ERR_RANGE, "too many work items (%zu)", n_items);
@@ -758,7 +798,7 @@ int launch_spmm(const PlanView& whole, const void* B, void* C, size_t N, cudaStr
     auto launch = [&](auto kernel, uint32_t smem_bytes) -> int {
         SMAT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
         kernel<<<grid, kThreads, smem_bytes, stream>>>(
-            mapB, reinterpret_cast<const uint8_t*>(plan.packed), reinterpret_cast<const uint4*>(plan.steps), plan.gsp,
+            mapB, mapC, reinterpret_cast<const uint8_t*>(plan.packed), reinterpret_cast<const uint4*>(plan.steps), plan.gsp,
             plan.rowptr, reinterpret_cast<__half*>(C), (int)plan.brow_begin, (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles,
             (int)n_items, (int)plan.n_groups, parts, panel_rows * 128u, plan.fix_scratch, ctx->d_status, ldc,
             listed ? plan.sched_off : nullptr, listed ? plan.sched_list : nullptr);

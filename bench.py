@@ -35,10 +35,10 @@ METRIC = "SpMM effective TFLOP/s (nonzero-block FLOPs)"
 # DRAM bytes (read + write) per launch of the SpMM kernel from an ncu capture of the same workload
 # (see profiles/): filled per workload, None where no capture exists.
 NCU_TRAFFIC_BYTES = {
-    # 117.13 MB (113.68 read + 3.45 written) measured at scale 0.25 (nnzb 204859), scaled by nnzb to the
+    # 117.86 MB (113.68 read + 4.17 written, mean of two launches) measured at scale 0.25 (nnzb 204859), scaled by nnzb to the
     # full-size matrix (3548444 blocks): every block is read once per launch and dominates the traffic
-    ("uniform", 1.0, 1): int(117.13e6 * 3548444 / 204859),
-    ("uniform", 0.25, 1): int(117.13e6),
+    ("uniform", 1.0, 1): int(117.86e6 * 3548444 / 204859),
+    ("uniform", 0.25, 1): int(117.86e6),
 }
 
 

@@ -36,8 +36,9 @@
 // whatever their size, while different warps issue concurrently.  So issue is spread over warps:
 // 4 loader warps (each takes every 4th step: one TMA for the panel, one bulk copy for the step's A
 // blocks), 8 MMA warps (each owns two accumulator rows, so that every accumulator is updated by a
-// single thread, in order), 4 epilogue warps (tcgen05.ld -> zero the accumulator -> fp16 -> paired
-// coalesced stores) and, for the tensor-memory-operand variant, 4 panel-copier warps.
+// single thread, in order), 4 epilogue warps (tcgen05.ld -> zero the accumulator -> fp16 -> for narrow items a
+// shared-memory tile per block-row stored with one TMA store, for wide items paired coalesced stores) and, for
+// the tensor-memory-operand variant, 4 panel-copier warps.
 //
 // Scheduling.  Items go round-robin over the persistent CTAs while there is one for every CTA; the
 // items left for the last round are cut into equal segments so that it keeps every SM busy (SegGen

@@ -31,7 +31,6 @@ namespace {
 
 constexpr int RG = kPlanRowsPerGroup;
 constexpr int kPlanThreads = RG * 32;
-constexpr int CAP = kPlanBlocksPerStep;
 constexpr int kWindow = 16384;  // block-columns per pass: 64 KB of masks + 64 KB of block prefixes
 
 // Fills masks[0..kWindow) for block-columns [w0, w0 + kWindow) of the group; cursor[] (one per warp,
@@ -82,7 +81,7 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* total, int* sh) 
 
 template <bool FILL>
 __global__ void __launch_bounds__(kPlanThreads)
-plan_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx, int brow_begin, int brow_end, int rg, int Kb,
+plan_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx, int brow_begin, int brow_end, int rg, int CAP, int Kb,
             int n_groups, int* __restrict__ gsp, uint4* __restrict__ steps, int* __restrict__ blk) {
     extern __shared__ uint32_t sm[];
     uint32_t* masks = sm;                                 // [kWindow] row mask per block-column
@@ -294,7 +293,7 @@ static int plan_launch_setup(const DeviceCtx* ctx_in, const DeviceCtx** ctx) {
 }
 
 int plan_count_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
-                     size_t rg, int* gsp, cudaStream_t stream, const DeviceCtx* ctx_in) {
+                     size_t rg, int* gsp, cudaStream_t stream, const DeviceCtx* ctx_in, size_t cap) {
     const DeviceCtx* ctx = nullptr;
     if (int rc = plan_launch_setup(ctx_in, &ctx)) return rc;
     const size_t n_groups = (brow_end - brow_begin + rg - 1) / rg;
@@ -306,7 +305,7 @@ int plan_count_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb
     const int grid = (int)(n_groups < (size_t)ctx->sm_count ? n_groups : (size_t)ctx->sm_count);
     const size_t smem_count = (size_t)kWindow * 4;
     SMAT_CUDA_TRY(cudaFuncSetAttribute(plan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_count));
-    plan_kernel<false><<<grid, kPlanThreads, smem_count, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, (int)rg,
+    plan_kernel<false><<<grid, kPlanThreads, smem_count, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, (int)rg, (int)cap,
                                                                   (int)(K / 16), (int)n_groups, gsp, nullptr, nullptr);
     count_launch();
     plan_scan_kernel<<<1, 1024, 0, stream>>>(gsp, (int)n_groups + 1);
@@ -316,7 +315,7 @@ int plan_count_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb
 }
 
 int plan_fill_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
-                    size_t rg, const int* gsp, void* steps, int* blk, cudaStream_t stream, const DeviceCtx* ctx_in) {
+                    size_t rg, const int* gsp, void* steps, int* blk, cudaStream_t stream, const DeviceCtx* ctx_in, size_t cap) {
     const DeviceCtx* ctx = nullptr;
     if (int rc = plan_launch_setup(ctx_in, &ctx)) return rc;
     const size_t n_groups = (brow_end - brow_begin + rg - 1) / rg;
@@ -324,7 +323,7 @@ int plan_fill_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb,
     const int grid = (int)(n_groups < (size_t)ctx->sm_count ? n_groups : (size_t)ctx->sm_count);
     const size_t smem_fill = (size_t)kWindow * 8;
     SMAT_CUDA_TRY(cudaFuncSetAttribute(plan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fill));
-    plan_kernel<true><<<grid, kPlanThreads, smem_fill, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, (int)rg,
+    plan_kernel<true><<<grid, kPlanThreads, smem_fill, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, (int)rg, (int)cap,
                                                                  (int)(K / 16), (int)n_groups, const_cast<int*>(gsp),
                                                                  reinterpret_cast<uint4*>(steps), blk);
     count_launch();
@@ -390,6 +389,18 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
         e = cudaMemcpyAsync(total_and_max, gsp + sz.n_groups, 2 * sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
         if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan build failed: %s", cudaGetErrorString(e));
+    }
+    // Densely filled quads (config 4: every quad of a cluster holds all 64 blocks) are cut into pieces of at most 24
+    // blocks that each fetch the B panel again; when the steps are that full on average, recount with 32 per step.
+    size_t cap = kPlanBlocksPerStep;
+    if (rc == SMAT_OK && total_and_max[0] > 0 && nnzb >= 18 * (size_t)total_and_max[0]) {
+        cap = kPlanBlocksPerStepDense;
+        rc = plan_count_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, rg, gsp, (cudaStream_t)stream, nullptr, cap);
+        if (rc == SMAT_OK) {
+            e = cudaMemcpyAsync(total_and_max, gsp + sz.n_groups, 2 * sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+            if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+            if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan build failed: %s", cudaGetErrorString(e));
+        }
     }
     const int total_steps = total_and_max[0];
     // Schedule: when the heaviest group holds many times the average number of steps, items dealt out round-robin
@@ -472,8 +483,9 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
     p->v.fix_scratch = static_cast<float*>(p->fix_buffer);
     p->v.total_steps = (size_t)(total_steps > 0 ? total_steps : 0);
     p->v.balanced = balanced;
+    p->v.cap = cap;
     rc = plan_fill_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, rg, gsp, const_cast<void*>(p->v.steps),
-                         const_cast<int*>(p->v.blk), (cudaStream_t)stream);
+                         const_cast<int*>(p->v.blk), (cudaStream_t)stream, nullptr, cap);
     if (rc == SMAT_OK)
         rc = pack_values_async(bcsrRowPtrA, bcsrValuesA, gsp, p->v.steps, p->v.blk, const_cast<void*>(p->v.packed), brow_begin,
                                brow_end, rg, nnzb, (cudaStream_t)stream);

@@ -74,6 +74,9 @@ size_t choose_rows_per_group(size_t block_rows, size_t N, int sm_count, bool can
 inline size_t fix_scratch_bytes(int sm_count) { return (size_t)sm_count * (2 * 16 * 16 * 128) * sizeof(float); }
 // A step of the plan covers four consecutive block-columns and carries at most this many blocks.
 constexpr int kPlanBlocksPerStep = 24;
+// ... or this many, for plans of densely filled quads (most steps would otherwise be pieces of a cut quad): fewer,
+// fuller steps at the price of one pipeline stage.
+constexpr int kPlanBlocksPerStepDense = 32;
 // MMA-issuing warps of the kernel; each owns kPlanRowsPerGroup / kPlanOwners consecutive accumulators.
 #ifndef SMAT_OWNERS
 #define SMAT_OWNERS 8
@@ -102,6 +105,7 @@ struct PlanView {
     const void* packed = nullptr;
     size_t K = 0, nnzb = 0, brow_begin = 0, brow_end = 0, n_groups = 0, rg = kPlanRowsPerGroup;
     size_t total_steps = 0;  // number of steps of the range when the host knows it, else 0
+    size_t cap = kPlanBlocksPerStep;  // most blocks of a step: kPlanBlocksPerStep or kPlanBlocksPerStepDense
     // The heaviest group has many times the average number of steps: deal out equal step ranges instead of items
     // (needs fix_scratch of 2 x fix_scratch_bytes).
     bool balanced = false;
@@ -122,9 +126,10 @@ PlanSizes plan_sizes(size_t nnzb, size_t brow_begin, size_t brow_end, size_t rg,
 // `ctx` (here and below): per-device state to use; nullptr = the lazily created one of get_device_ctx.
 // Phase 1 fills gsp (step counts, scanned); phase 2 fills steps and blk.
 int plan_count_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
-                     size_t rg, int* gsp, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
+                     size_t rg, int* gsp, cudaStream_t stream, const DeviceCtx* ctx = nullptr, size_t cap = kPlanBlocksPerStep);
 int plan_fill_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
-                    size_t rg, const int* gsp, void* steps, int* blk, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
+                    size_t rg, const int* gsp, void* steps, int* blk, cudaStream_t stream, const DeviceCtx* ctx = nullptr,
+                    size_t cap = kPlanBlocksPerStep);
 // Copies the value blocks of block-rows [brow_begin, brow_end) into their places in the packed stream.
 int pack_values_async(const int* rowptr, const void* vals, const int* gsp, const void* steps, const int* blk, void* packed,
                       size_t brow_begin, size_t brow_end, size_t rg, size_t nnzb, cudaStream_t stream,

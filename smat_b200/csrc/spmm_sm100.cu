@@ -62,7 +62,6 @@ using namespace ptx;
 namespace {
 
 constexpr int RG = kPlanRowsPerGroup;  // block-rows per work item
-constexpr int CAP = kPlanBlocksPerStep;  // most blocks a step can carry
 constexpr int NL = 4;                  // loader warps
 #ifndef SMAT_TMA_EPILOGUE
 #define SMAT_TMA_EPILOGUE 1
@@ -77,10 +76,11 @@ constexpr uint32_t TMEM_PANELS = 256;  // first tensor-memory column of the pane
 constexpr uint32_t ABLK_BYTES = 16 * 16 * 2;
 constexpr long long WAIT_LIMIT = 4000000000LL;  // clock cycles (about two seconds)
 
-// Shared-memory plan of a kernel whose work item is NH x 128 columns of C wide.
-template <int NH>
+// Shared-memory plan of a kernel whose work item is NH x 128 columns of C wide, for plans with at most CAP blocks
+// per step.
+template <int NH, int CAP>
 struct Cfg {
-    static constexpr uint32_t S = NH == 1 ? 7 : 5;              // steps in flight (pipeline stages)
+    static constexpr uint32_t S = CAP <= 24 ? (NH == 1 ? 7 : 5) : (NH == 1 ? 6 : 4);              // steps in flight (pipeline stages)
     static constexpr uint32_t PANEL_BYTES = NH * 128 * 64 * 2;  // NH x (128 n x 64 k fp16)
     static constexpr uint32_t STAGE_BYTES = (PANEL_BYTES + CAP * ABLK_BYTES + 1023) / 1024 * 1024;
     static constexpr uint32_t OFF_STAGE = 0;
@@ -100,7 +100,7 @@ struct Cfg {
 };
 
 static_assert(RG == 16, "row masks and accumulator ownership below assume 16 block-rows per group");
-static_assert(RG * 2 * 16 <= 512 && TMEM_PANELS + Cfg<1>::S * 32 <= 512, "tensor-memory budget");
+static_assert(RG * 2 * 16 <= 512 && TMEM_PANELS + Cfg<1, kPlanBlocksPerStep>::S * 32 <= 512, "tensor-memory budget");
 
 __device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
     uint32_t v;
@@ -248,7 +248,7 @@ static_assert((size_t)kFixSlotFloats * sizeof(float) == (2 * 16 * 16 * 128) * si
 // NH = 1: a work item is 128 columns of C wide.  NH = 2: 256 columns -- every A block then feeds two
 //   independent MMAs (one per 128-column half, own accumulator), which doubles the MMA work per stage
 //   hand-over and halves the A traffic per MMA; the 32 accumulators fill tensor memory (one buffer).
-template <bool TS, int NH, int SCHED>
+template <bool TS, int NH, int SCHED, int CAP>
 __global__ void __launch_bounds__(kThreads, 1)
 spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapC,
                     const uint8_t* __restrict__ packed,
@@ -263,8 +263,8 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_const
     constexpr bool listed = SCHED == 1, balanced = SCHED == 2;
     // A loader waits on a stage's `empty` barrier by parity, which only tells phases apart while the waiter is
     // less than two uses ahead of the consumers; with steps consumed in order that holds iff NL <= S.
-    static_assert(NL <= (int)Cfg<NH>::S, "more loader warps than stages would alias barrier phases");
-    using G = Cfg<NH>;
+    static_assert(NL <= (int)Cfg<NH, CAP>::S, "more loader warps than stages would alias barrier phases");
+    using G = Cfg<NH, CAP>;
     constexpr uint32_t S = G::S, PANEL_BYTES = G::PANEL_BYTES, STAGE_BYTES = G::STAGE_BYTES, OFF_STAGE = G::OFF_STAGE,
                        OFF_META = G::OFF_META, OFF_BAR = G::OFF_BAR, OFF_MISC = G::OFF_MISC;
     constexpr int NT = 128 * NH;  // columns of C per work item
@@ -807,16 +807,22 @@ int launch_spmm(const PlanView& whole, const void* B, void* C, size_t N, cudaStr
         SMAT_CUDA_TRY(cudaGetLastError());
         return SMAT_OK;
     };
-    auto launch_sched = [&](auto sched) -> int {
-        constexpr int SCHED = decltype(sched)::value;
-        if (variant == 3) return launch(spmm_bcsr_tc_kernel<false, 2, SCHED>, Cfg<2>::SMEM_BYTES);
-        if (variant == 2) return launch(spmm_bcsr_tc_kernel<true, 1, SCHED>, Cfg<1>::SMEM_BYTES);
-        return launch(spmm_bcsr_tc_kernel<false, 1, SCHED>, Cfg<1>::SMEM_BYTES);
+    auto launch_sched = [&](auto sched, auto cap) -> int {
+        constexpr int SCHED = decltype(sched)::value, CAP = decltype(cap)::value;
+        if (variant == 3) return launch(spmm_bcsr_tc_kernel<false, 2, SCHED, CAP>, Cfg<2, CAP>::SMEM_BYTES);
+        if (variant == 2) return launch(spmm_bcsr_tc_kernel<true, 1, SCHED, CAP>, Cfg<1, CAP>::SMEM_BYTES);
+        return launch(spmm_bcsr_tc_kernel<false, 1, SCHED, CAP>, Cfg<1, CAP>::SMEM_BYTES);
     };
+    auto launch_cap = [&](auto sched) -> int {
+        if (plan.cap == (size_t)kPlanBlocksPerStepDense) return launch_sched(sched, std::integral_constant<int, kPlanBlocksPerStepDense>{});
+        return launch_sched(sched, std::integral_constant<int, kPlanBlocksPerStep>{});
+    };
+    if (plan.cap != (size_t)kPlanBlocksPerStep && plan.cap != (size_t)kPlanBlocksPerStepDense)
+        return fail(SMAT_ERR_BAD_ARG, "plan with %zu blocks per step: no kernel for it", plan.cap);
     int rc;
-    if (listed) rc = launch_sched(std::integral_constant<int, 1>{});
-    else if (balanced) rc = launch_sched(std::integral_constant<int, 2>{});
-    else rc = launch_sched(std::integral_constant<int, 0>{});
+    if (listed) rc = launch_cap(std::integral_constant<int, 1>{});
+    else if (balanced) rc = launch_cap(std::integral_constant<int, 2>{});
+    else rc = launch_cap(std::integral_constant<int, 0>{});
     if (rc != SMAT_OK) return rc;
     if (balanced) {
         if (grid < 2) return SMAT_OK;

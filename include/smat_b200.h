@@ -74,7 +74,7 @@ int smat_spmm_bcsr_f16_static(const void* bcsrValuesA, const int* bcsrRowPtrA, c
 
 /* Multiplication plan: what the kernel needs beyond the BCSR arrays, computed on the device and
  * reusable for any number of multiplications:
- *   - the walk order (per group of 16 block-rows, its block-columns four at a time in ascending
+ *   - the walk order (per group of up to 16 block-rows, its block-columns four at a time in ascending
  *     order with the blocks found there), and
  *   - a copy of the value blocks in that order, so that all blocks of a step arrive with one bulk
  *     copy (nonzeroBlocks * 512 bytes of device memory owned by the plan).
@@ -86,7 +86,10 @@ int smat_spmm_bcsr_f16_static(const void* bcsrValuesA, const int* bcsrRowPtrA, c
  * No counterpart in the reference (its kernel re-reads bcsrColIdx per tile, mmaCBT.cu:38-43). */
 typedef struct smat_plan smat_plan;
 /* N_hint: the number of columns of B the plan will mostly be used with (0 = unknown).  It only steers
- * how many block-rows form a work item (16, 8 or 4), so that small matrices or shards still fill the SMs. */
+ * how many block-rows form a work item (8 to 16), so that small matrices or shards still fill the SMs.
+ * A plan also owns scratch for work items that a launch computes in segments (38.8 MB on a 148-SM device, twice
+ * that for matrices whose work is very unevenly spread over the block-rows) and may be used by one stream at a
+ * time. */
 int smat_plan_create(smat_plan** plan, const void* bcsrValuesA, const int* bcsrRowPtrA, const int* bcsrColIdxA, size_t M,
                      size_t K, size_t nonzeroBlocks, size_t brow_begin, size_t brow_end, size_t N_hint, void* stream);
 int smat_plan_set_values(smat_plan* plan, const void* bcsrValuesA, void* stream);

@@ -2,8 +2,8 @@
 
 Run in a container that has the reference tree (it is not needed to run the tests):
 
-    make -C oracle ref REF=/root/reference
-    python tests/golden/make_golden.py
+    make -C oracle ref REF=<reference tree>
+    SMAT_REFERENCE=<reference tree> python tests/golden/make_golden.py
 
 It drives the reference's own code through oracle/_ref (built from the reference sources by
 oracle/Makefile): the Matrix_Blocking / TEST_similarities programs and, through the thin ctypes
@@ -149,7 +149,7 @@ def formats_fixtures():
     Matrix_Blocking program on a small pattern matrix: text converters, row pass, column pass."""
     import shutil
     import types
-    ref_src = "/root/reference/src"
+    ref_src = os.path.join(os.environ.get("SMAT_REFERENCE", "/root/reference"), "src")
     sys.modules.setdefault("utils", types.ModuleType("utils"))  # plotting helpers, not needed (matplotlib absent)
     sys.path.insert(0, ref_src)
     import reorder as ref_reorder  # the reference module
@@ -187,7 +187,7 @@ def formats_fixtures():
 
 
 if __name__ == "__main__":
-    assert oracle.have_ref(), "build oracle/_ref first: make -C oracle ref REF=/root/reference"
+    assert oracle.have_ref(), "build oracle/_ref first: make -C oracle ref REF=<reference tree>"
     similarities()
     reorder_fixtures()
     multiply_fixtures()

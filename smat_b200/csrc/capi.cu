@@ -176,7 +176,7 @@ int smat_spmm_bcsr_f16_rows(const void* vals, const int* rowptr, const int* coli
 
 int smat_spmm_set_variant(int variant) {
     clear_error();
-    if (variant < 0 || variant > 3) return fail(SMAT_ERR_BAD_ARG, "unknown SpMM variant %d", variant);
+    if (variant < 0 || variant > 4) return fail(SMAT_ERR_BAD_ARG, "unknown SpMM variant %d", variant);
     g_spmm_variant = variant;
     return SMAT_OK;
 }

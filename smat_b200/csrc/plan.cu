@@ -35,9 +35,10 @@ constexpr int kWindow = 16384;  // block-columns per pass: 64 KB of masks + 64 K
 
 // Fills masks[0..kWindow) for block-columns [w0, w0 + kWindow) of the group; cursor[] (one per warp,
 // kept by lane 0 semantics via registers) walks each row once over all windows.
+template <int THREADS = kPlanThreads>
 __device__ __forceinline__ void mark_window(const int* __restrict__ colidx, int& cur, int end, int w0, uint32_t* masks,
                                             int warp, int lane) {
-    for (int i = threadIdx.x; i < kWindow; i += kPlanThreads) masks[i] = 0u;
+    for (int i = threadIdx.x; i < kWindow; i += THREADS) masks[i] = 0u;
     __syncthreads();
     // every lane keeps the same `cur`; lanes stride over the row until the window ends
     for (;;) {
@@ -53,6 +54,7 @@ __device__ __forceinline__ void mark_window(const int* __restrict__ colidx, int&
 }
 
 // Block-wide exclusive scan of one int per thread; returns the exclusive prefix, *total gets the sum.
+template <int THREADS = kPlanThreads>
 __device__ __forceinline__ int block_exclusive_scan(int v, int* total, int* sh) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int inc = v;
@@ -64,7 +66,7 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* total, int* sh) 
     if (lane == 31) sh[warp] = inc;
     __syncthreads();
     if (warp == 0) {
-        int w = lane < (kPlanThreads >> 5) ? sh[lane] : 0;
+        int w = lane < (THREADS >> 5) ? sh[lane] : 0;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
             const int t = __shfl_up_sync(0xffffffffu, w, d);
@@ -74,7 +76,7 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* total, int* sh) 
     }
     __syncthreads();
     const int before = warp ? sh[32 + warp - 1] : 0;
-    *total = sh[32 + (kPlanThreads >> 5) - 1];
+    *total = sh[32 + (THREADS >> 5) - 1];
     __syncthreads();
     return before + inc - v;
 }
@@ -219,6 +221,138 @@ __global__ void __launch_bounds__(256) pack_kernel(const uint4* __restrict__ val
     }
 }
 
+
+// ---- tall plans: groups of up to 32 block-rows (the kernel uses at most kTallRows), 32-byte step records ----
+constexpr int kTallPlanThreads = 1024;  // warp w owns block-row w of the group
+static_assert(kTallRows == 24 && kTallBlocksPerStep <= 32, "the per-warp step words below are laid out for 12 warps of two rows and 5-bit block positions");
+
+template <bool FILL>
+__global__ void __launch_bounds__(kTallPlanThreads)
+plan_tall_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx, int brow_begin, int brow_end, int rg, int CAP, int Kb,
+                 int n_groups, int* __restrict__ gsp, uint4* __restrict__ steps, uint4* __restrict__ winfo, int* __restrict__ blk) {
+    extern __shared__ uint32_t sm[];
+    uint32_t* masks = sm;                                 // [kWindow] row mask per block-column
+    int* blk_pre = reinterpret_cast<int*>(sm + kWindow);  // [kWindow] exclusive block number (FILL only)
+    __shared__ int scan_sh[64];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
+        const int row = brow_begin + g * rg + warp;
+        const bool have = warp < rg && row < brow_end;
+        const int beg = have ? __ldg(rowptr + row) : 0;
+        const int end = have ? __ldg(rowptr + row + 1) : 0;
+        const int gfirst = __ldg(rowptr + brow_begin + g * rg);
+        const int rfirst = __ldg(rowptr + brow_begin);
+        int cur = beg;
+        int steps_done = 0, blocks_done = 0;
+        const int gs = FILL ? __ldg(gsp + g) : 0;
+        for (int w0 = 0; w0 < Kb; w0 += kWindow) {
+            const int cur_before = cur;
+            mark_window<kTallPlanThreads>(colidx, cur, end, w0, masks, warp, lane);
+            constexpr int PER = kWindow / kTallPlanThreads;
+            static_assert(PER % 4 == 0, "a thread owns whole quads");
+            const int i0 = threadIdx.x * PER;
+            int ns = 0, nb = 0;
+#pragma unroll
+            for (int qd = 0; qd < PER / 4; qd++) {
+                const int c = __popc(masks[i0 + 4 * qd]) + __popc(masks[i0 + 4 * qd + 1]) + __popc(masks[i0 + 4 * qd + 2]) +
+                              __popc(masks[i0 + 4 * qd + 3]);
+                ns += (c + CAP - 1) / CAP;
+                nb += c;
+            }
+            int tot_s, tot_b = 0;
+            const int pre_s = block_exclusive_scan<kTallPlanThreads>(ns, &tot_s, scan_sh);
+            if (FILL) {
+                const int pre_b = block_exclusive_scan<kTallPlanThreads>(nb, &tot_b, scan_sh);
+                int s = steps_done + pre_s, b = blocks_done + pre_b;
+                for (int qd = 0; qd < PER / 4; qd++) {
+                    uint32_t m[4];
+                    int c = 0;
+#pragma unroll
+                    for (int sub = 0; sub < 4; sub++) {
+                        m[sub] = masks[i0 + 4 * qd + sub];
+                        blk_pre[i0 + 4 * qd + sub] = b + c;
+                        c += __popc(m[sub]);
+                    }
+                    // cut the quad into steps of at most CAP blocks, in (sub-column, row) order
+                    while (c > 0) {
+                        uint32_t part[4] = {0u, 0u, 0u, 0u};
+                        int taken = 0;
+#pragma unroll
+                        for (int sub = 0; sub < 4; sub++) {
+                            while (m[sub] && taken < CAP) {
+                                const uint32_t low = m[sub] & (~m[sub] + 1u);
+                                part[sub] |= low;
+                                m[sub] ^= low;
+                                taken++;
+                            }
+                        }
+                        const uint32_t pos = 2u * (uint32_t)(gfirst - rfirst + b);
+                        steps[gs + s] = make_uint4((uint32_t)(w0 + i0 + 4 * qd) << 4, pos, (uint32_t)taken, 0u);
+                        // what each MMA-issuing warp needs of the step: warp m owns block-rows 2m, 2m + 1
+                        const uint32_t pre1 = (uint32_t)__popc(part[0]), pre2 = pre1 + (uint32_t)__popc(part[1]),
+                                       pre3 = pre2 + (uint32_t)__popc(part[2]);
+                        const uint32_t pre[4] = {0u, pre1, pre2, pre3};
+                        uint4* wdst = winfo + 4 * (size_t)(gs + s);
+#pragma unroll
+                        for (int v = 0; v < 3; v++) {
+                            uint32_t wi[4];
+#pragma unroll
+                            for (int mm = 0; mm < 4; mm++) {
+                                const int m = 4 * v + mm;
+                                uint32_t word = 0;
+#pragma unroll
+                                for (int sub = 0; sub < 4; sub++) {
+                                    const uint32_t own = (part[sub] >> (2 * m)) & 3u;
+                                    const uint32_t q = pre[sub] + (uint32_t)__popc(part[sub] & ((1u << (2 * m)) - 1u));
+                                    word |= own << (2 * sub);
+                                    word |= (q & 31u) << (8 + 5 * sub);
+                                }
+                                wi[mm] = word;
+                            }
+                            wdst[v] = make_uint4(wi[0], wi[1], wi[2], wi[3]);
+                        }
+                        wdst[3] = make_uint4((part[0] ? 1u : 0u) | (part[1] ? 2u : 0u) | (part[2] ? 4u : 0u) | (part[3] ? 8u : 0u), 0u, 0u, 0u);
+                        s++;
+                        b += taken;
+                        c -= taken;
+                    }
+                }
+                __syncthreads();
+                for (int j = cur_before + lane; j < cur; j += 32) {
+                    const int cb = (__ldg(colidx + j) >> 4) - w0;
+                    blk[gfirst + blk_pre[cb] + __popc(masks[cb] & ((1u << warp) - 1u))] = j;
+                }
+                blocks_done += tot_b;
+            }
+            steps_done += tot_s;
+            __syncthreads();
+        }
+        if (!FILL && threadIdx.x == 0) gsp[g + 1] = steps_done;
+    }
+    if (!FILL && blockIdx.x == 0 && threadIdx.x == 0) gsp[0] = 0;
+}
+
+// One warp per step of a tall plan: copies the step's value blocks to their place in the packed stream (32-byte swizzle).
+__global__ void __launch_bounds__(256) pack_tall_kernel(const uint4* __restrict__ vals, const int* __restrict__ blk,
+                                                       const int* __restrict__ gsp, const uint4* __restrict__ steps,
+                                                       uint8_t* __restrict__ packed, const int* __restrict__ rowptr, int brow_begin,
+                                                       int n_groups) {
+    const int rfirst = __ldg(rowptr + brow_begin);
+    const int total = __ldg(gsp + n_groups);
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    for (int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < total; i += warps) {
+        const uint4 d = __ldg(steps + i);
+        const int cnt = (int)d.z;
+        const int first = rfirst + (int)(d.y >> 1);
+        uint4* dst = reinterpret_cast<uint4*>(packed + (size_t)d.y * 256);
+        for (int q = 0; q < cnt; q++) {
+            const int src = __ldg(blk + first + q);
+            dst[q * 32 + (lane ^ ((lane >> 3) & 1))] = __ldg(vals + (size_t)src * 32 + lane);
+        }
+    }
+}
+
 }  // namespace
 
 int pack_values_async(const int* rowptr, const void* vals, const int* gsp, const void* steps, const int* blk, void* packed,
@@ -331,6 +465,63 @@ int plan_fill_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb,
     return SMAT_OK;
 }
 
+
+int plan_count_tall_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
+                          size_t rg, int* gsp, cudaStream_t stream, const DeviceCtx* ctx_in) {
+    const DeviceCtx* ctx = nullptr;
+    if (int rc = plan_launch_setup(ctx_in, &ctx)) return rc;
+    const size_t n_groups = (brow_end - brow_begin + rg - 1) / rg;
+    if (n_groups == 0) return SMAT_OK;
+    if (nnzb == 0) {
+        SMAT_CUDA_TRY(cudaMemsetAsync(gsp, 0, (n_groups + 1) * sizeof(int), stream));
+        return SMAT_OK;
+    }
+    const int grid = (int)(n_groups < (size_t)ctx->sm_count ? n_groups : (size_t)ctx->sm_count);
+    const size_t smem_count = (size_t)kWindow * 4;
+    SMAT_CUDA_TRY(cudaFuncSetAttribute(plan_tall_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_count));
+    plan_tall_kernel<false><<<grid, kTallPlanThreads, smem_count, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, (int)rg,
+                                                                           kTallBlocksPerStep, (int)(K / 16), (int)n_groups, gsp, nullptr,
+                                                                           nullptr, nullptr);
+    count_launch();
+    plan_scan_kernel<<<1, 1024, 0, stream>>>(gsp, (int)n_groups + 1);
+    count_launch();
+    SMAT_CUDA_TRY(cudaGetLastError());
+    return SMAT_OK;
+}
+
+int plan_fill_tall_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
+                         size_t rg, const int* gsp, void* steps, void* winfo, int* blk, cudaStream_t stream, const DeviceCtx* ctx_in) {
+    const DeviceCtx* ctx = nullptr;
+    if (int rc = plan_launch_setup(ctx_in, &ctx)) return rc;
+    const size_t n_groups = (brow_end - brow_begin + rg - 1) / rg;
+    if (n_groups == 0 || nnzb == 0) return SMAT_OK;
+    const int grid = (int)(n_groups < (size_t)ctx->sm_count ? n_groups : (size_t)ctx->sm_count);
+    const size_t smem_fill = (size_t)kWindow * 8;
+    SMAT_CUDA_TRY(cudaFuncSetAttribute(plan_tall_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fill));
+    plan_tall_kernel<true><<<grid, kTallPlanThreads, smem_fill, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, (int)rg,
+                                                                         kTallBlocksPerStep, (int)(K / 16), (int)n_groups,
+                                                                         const_cast<int*>(gsp), reinterpret_cast<uint4*>(steps),
+                                                                         reinterpret_cast<uint4*>(winfo), blk);
+    count_launch();
+    SMAT_CUDA_TRY(cudaGetLastError());
+    return SMAT_OK;
+}
+
+int pack_values_tall_async(const int* rowptr, const void* vals, const int* gsp, const void* steps, const int* blk, void* packed,
+                           size_t brow_begin, size_t brow_end, size_t rg, size_t nnzb, cudaStream_t stream,
+                           const DeviceCtx* ctx_in) {
+    if (nnzb == 0 || brow_end == brow_begin) return SMAT_OK;
+    const DeviceCtx* ctx = nullptr;
+    if (int rc = plan_launch_setup(ctx_in, &ctx)) return rc;
+    const size_t n_groups = (brow_end - brow_begin + rg - 1) / rg;
+    pack_tall_kernel<<<ctx->sm_count * 8, 256, 0, stream>>>(reinterpret_cast<const uint4*>(vals), blk, gsp,
+                                                            reinterpret_cast<const uint4*>(steps), reinterpret_cast<uint8_t*>(packed),
+                                                            rowptr, (int)brow_begin, (int)n_groups);
+    count_launch();
+    SMAT_CUDA_TRY(cudaGetLastError());
+    return SMAT_OK;
+}
+
 }  // namespace smat
 
 using namespace smat;
@@ -402,7 +593,7 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
             if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan build failed: %s", cudaGetErrorString(e));
         }
     }
-    const int total_steps = total_and_max[0];
+    const int total_steps = total_and_max[0];  // of the 16-row plan
     // Schedule: when the heaviest group holds many times the average number of steps, items dealt out round-robin
     // leave most SMs waiting for the one with the heaviest item; such plans deal out equal step ranges instead.
     bool balanced = (size_t)total_and_max[1] * sz.n_groups > 4 * (size_t)total_steps &&
@@ -450,6 +641,48 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
             }
         }
     }
+    // Tall plan: when a group's quads hold several blocks each but are far from full, and a work item is long, the
+    // tensor-memory-operand kernel with taller groups (fewer panel fetches per block, no panel traffic through the
+    // shared-memory operand port) is the faster one.  smat_spmm_set_variant(4) forces it, 1..3 exclude it.
+    bool tall = false;
+    size_t rg_used = rg;
+    if (rc == SMAT_OK && !balanced && !p->v.sched_list && total_steps > 0) {
+        // (measured so far the 16-row kernels are still the faster ones on every configuration of the benchmark, so
+        // a tall plan is only made on request)
+        tall = g_spmm_variant == 4 && brow_end > brow_begin;
+    }
+    if (tall) {
+        const size_t rows = brow_end - brow_begin, tiles = ((N_hint ? N_hint : 128) + 127) / 128;
+        double best = 0.0;
+        for (size_t r = kTallRows; r >= 16; r--) {
+            const size_t groups = (rows + r - 1) / r;
+            const double cost = rounds_for(groups * tiles, (size_t)ctx->sm_count, true, (size_t)total_steps / sz.n_groups, false);
+            if (r == (size_t)kTallRows || cost < best * 0.97) {
+                best = cost;
+                rg_used = r;
+            }
+        }
+        if (const char* ev = std::getenv("SMAT_TALL_ROWS")) {
+            const int v = std::atoi(ev);
+            if (v >= 1 && v <= kTallRows) rg_used = (size_t)v;
+        }
+        // the group count changes with the height: count again into a buffer of the right size
+        cudaFree(p->gsp_buffer);
+        p->gsp_buffer = nullptr;
+        sz = plan_sizes(nnzb, brow_begin, brow_end, rg_used);
+        e = cudaMalloc(&p->gsp_buffer, sz.gsp_bytes);
+        if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan allocation failed: %s", cudaGetErrorString(e));
+        gsp = static_cast<int*>(p->gsp_buffer);
+        if (rc == SMAT_OK)
+            rc = plan_count_tall_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, rg_used, gsp, (cudaStream_t)stream);
+        if (rc == SMAT_OK) {
+            e = cudaMemcpyAsync(total_and_max, gsp + sz.n_groups, 2 * sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+            if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+            if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan build failed: %s", cudaGetErrorString(e));
+        }
+        cap = kTallBlocksPerStep;
+    }
+    const int steps_final = total_and_max[0];
     if (rc == SMAT_OK && balanced) {  // two partial tiles per CTA
         cudaFree(p->fix_buffer);
         p->fix_buffer = nullptr;
@@ -457,7 +690,7 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
         if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan allocation failed: %s", cudaGetErrorString(e));
     }
     if (rc == SMAT_OK) {
-        sz = plan_sizes(nnzb, brow_begin, brow_end, rg, (size_t)(total_steps > 0 ? total_steps : 1));
+        sz = plan_sizes(nnzb, brow_begin, brow_end, rg_used, (size_t)(steps_final > 0 ? steps_final : 1) * (tall ? 5 : 1));
         e = cudaMalloc(&p->buffer, sz.steps_bytes + sz.blk_bytes + sz.packed_bytes);
         if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan allocation failed: %s", cudaGetErrorString(e));
     }
@@ -479,16 +712,26 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
     p->v.brow_begin = brow_begin;
     p->v.brow_end = brow_end;
     p->v.n_groups = sz.n_groups;
-    p->v.rg = rg;
+    p->v.rg = rg_used;
     p->v.fix_scratch = static_cast<float*>(p->fix_buffer);
-    p->v.total_steps = (size_t)(total_steps > 0 ? total_steps : 0);
+    p->v.total_steps = (size_t)(steps_final > 0 ? steps_final : 0);
     p->v.balanced = balanced;
     p->v.cap = cap;
-    rc = plan_fill_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, rg, gsp, const_cast<void*>(p->v.steps),
-                         const_cast<int*>(p->v.blk), (cudaStream_t)stream, nullptr, cap);
-    if (rc == SMAT_OK)
-        rc = pack_values_async(bcsrRowPtrA, bcsrValuesA, gsp, p->v.steps, p->v.blk, const_cast<void*>(p->v.packed), brow_begin,
-                               brow_end, rg, nnzb, (cudaStream_t)stream);
+    p->v.tall = tall;
+    if (tall) {
+        p->v.winfo = b + (size_t)(steps_final > 0 ? steps_final : 1) * 16;  // behind the step records, in the same region
+        rc = plan_fill_tall_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, rg_used, gsp, const_cast<void*>(p->v.steps),
+                                  const_cast<void*>(p->v.winfo), const_cast<int*>(p->v.blk), (cudaStream_t)stream);
+        if (rc == SMAT_OK)
+            rc = pack_values_tall_async(bcsrRowPtrA, bcsrValuesA, gsp, p->v.steps, p->v.blk, const_cast<void*>(p->v.packed),
+                                        brow_begin, brow_end, rg_used, nnzb, (cudaStream_t)stream);
+    } else {
+        rc = plan_fill_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, rg, gsp, const_cast<void*>(p->v.steps),
+                             const_cast<int*>(p->v.blk), (cudaStream_t)stream, nullptr, cap);
+        if (rc == SMAT_OK)
+            rc = pack_values_async(bcsrRowPtrA, bcsrValuesA, gsp, p->v.steps, p->v.blk, const_cast<void*>(p->v.packed), brow_begin,
+                                   brow_end, rg, nnzb, (cudaStream_t)stream);
+    }
     if (rc) {
         cudaFree(p->buffer);
         cudaFree(p->gsp_buffer);
@@ -505,6 +748,10 @@ int smat_plan_set_values(smat_plan* plan, const void* bcsrValuesA, void* stream)
     clear_error();
     if (!plan || (plan->v.nnzb && !bcsrValuesA)) return fail(SMAT_ERR_BAD_ARG, "NULL argument");
     if ((uintptr_t)bcsrValuesA & 15) return fail(SMAT_ERR_BAD_ARG, "bcsrValuesA must be 16-byte aligned");
+    if (plan->v.tall)
+        return pack_values_tall_async(plan->v.rowptr, bcsrValuesA, plan->v.gsp, plan->v.steps, plan->v.blk,
+                                      const_cast<void*>(plan->v.packed), plan->v.brow_begin, plan->v.brow_end, plan->v.rg,
+                                      plan->v.nnzb, (cudaStream_t)stream);
     return pack_values_async(plan->v.rowptr, bcsrValuesA, plan->v.gsp, plan->v.steps, plan->v.blk,
                              const_cast<void*>(plan->v.packed), plan->v.brow_begin, plan->v.brow_end, plan->v.rg,
                              plan->v.nnzb, (cudaStream_t)stream);

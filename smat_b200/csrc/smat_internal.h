@@ -77,6 +77,11 @@ constexpr int kPlanBlocksPerStep = 24;
 // ... or this many, for plans of densely filled quads (most steps would otherwise be pieces of a cut quad): fewer,
 // fuller steps at the price of one pipeline stage.
 constexpr int kPlanBlocksPerStepDense = 32;
+// The tall kernel (spmm_tall_sm100.cu) works on groups of up to kTallRows block-rows: a B panel fetched once feeds
+// half again as many rows, and the panels are read by the MMAs from tensor memory.  Its plans ("tall" plans) use
+// 32-byte step records and steps of at most kTallBlocksPerStep blocks.
+constexpr int kTallRows = 24;
+constexpr int kTallBlocksPerStep = 24;
 // MMA-issuing warps of the kernel; each owns kPlanRowsPerGroup / kPlanOwners consecutive accumulators.
 #ifndef SMAT_OWNERS
 #define SMAT_OWNERS 8
@@ -106,6 +111,13 @@ struct PlanView {
     size_t K = 0, nnzb = 0, brow_begin = 0, brow_end = 0, n_groups = 0, rg = kPlanRowsPerGroup;
     size_t total_steps = 0;  // number of steps of the range when the host knows it, else 0
     size_t cap = kPlanBlocksPerStep;  // most blocks of a step: kPlanBlocksPerStep or kPlanBlocksPerStepDense
+    // Tall plan: groups of rg <= kTallRows block-rows, at most kTallBlocksPerStep blocks per step.  A step record is
+    // {element column of the quad, position of the first block in the packed stream in 256-byte units, number of
+    // blocks, 0}; winfo holds 16 words per step: word m < 12 tells the warp that owns block-rows 2m, 2m + 1 what to
+    // multiply (bits 2s, 2s + 1: its rows that have a block in sub-column s; bits [8 + 5s, 13 + 5s): position in the
+    // step's block sequence of the first of them), word 12 the non-empty sub-columns (bit s).
+    bool tall = false;
+    const void* winfo = nullptr;
     // The heaviest group has many times the average number of steps: deal out equal step ranges instead of items
     // (needs fix_scratch of 2 x fix_scratch_bytes).
     bool balanced = false;
@@ -135,13 +147,35 @@ int pack_values_async(const int* rowptr, const void* vals, const int* gsp, const
                       size_t brow_begin, size_t brow_end, size_t rg, size_t nnzb, cudaStream_t stream,
                       const DeviceCtx* ctx = nullptr);
 
+// The same three phases for a tall plan.
+int plan_count_tall_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
+                          size_t rg, int* gsp, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
+int plan_fill_tall_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
+                         size_t rg, const int* gsp, void* steps, void* winfo, int* blk, cudaStream_t stream,
+                         const DeviceCtx* ctx = nullptr);
+int pack_values_tall_async(const int* rowptr, const void* vals, const int* gsp, const void* steps, const int* blk, void* packed,
+                           size_t brow_begin, size_t brow_end, size_t rg, size_t nnzb, cudaStream_t stream,
+                           const DeviceCtx* ctx = nullptr);
+
 // Launch of the SpMM kernel (spmm_sm100.cu).  `ldc`: elements between rows of C (0 = N, i.e. C is exactly N wide).
 // [group_begin, group_end): the groups of the plan to multiply (default: all); C points at the first row of
 // group_begin.
 int launch_spmm(const PlanView& plan, const void* B, void* C, size_t N, cudaStream_t stream,
                 const DeviceCtx* ctx = nullptr, size_t ldc = 0, size_t group_begin = 0, size_t group_end = (size_t)-1);
 
-// 0 = choose per call, 1 = shared-memory-operand kernel, 2 = tensor-memory-operand kernel, 3 = 256-column items.
+// The view of groups [group_begin, group_end) of a plan (steps, blocks and row pointers are addressed absolutely, so
+// a sub-range is the same plan with its first group, first block-row and group count moved).
+PlanView plan_group_range(const PlanView& whole, size_t group_begin, size_t group_end);
+// Launch of the tall kernel (spmm_tall_sm100.cu) for a tall plan; same arguments.
+int launch_spmm_tall(const PlanView& plan, const void* B, void* C, size_t N, cudaStream_t stream,
+                     const DeviceCtx* ctx = nullptr, size_t ldc = 0, size_t group_begin = 0, size_t group_end = (size_t)-1);
+// Adds up the fp32 partial tiles of the `cut_items` work items that a launch computed in `parts` segments each (the
+// items of its last round) and writes their part of C (spmm_sm100.cu); wide: items are 256 columns wide.
+int launch_sum_cut_items(bool wide, int cut_items, const float* scratch, void* C, int brow_begin, int brow_end, int rg, int N,
+                         int n_tiles, int n_full, int parts, size_t ldc, cudaStream_t stream);
+
+// 0 = choose per call, 1 = shared-memory-operand kernel, 2 = tensor-memory-operand kernel, 3 = 256-column items,
+// 4 = plans created from now on are tall plans (tall kernel).
 extern int g_spmm_variant;
 
 }  // namespace smat

@@ -49,11 +49,15 @@
 // SMAT_ERR_DEVICE_WAIT).
 #include <cuda_fp16.h>
 #include <limits.h>
+#include <stdlib.h>
+
+#include <cstdlib>
 
 #include <type_traits>
 
 #include "ptx_sm100.cuh"
 #include "smat_internal.h"
+#include "spmm_sched.cuh"
 
 namespace smat {
 
@@ -61,7 +65,6 @@ using namespace ptx;
 
 namespace {
 
-constexpr int RG = kPlanRowsPerGroup;  // block-rows per work item
 constexpr int NL = 4;                  // loader warps
 #ifndef SMAT_TMA_EPILOGUE
 #define SMAT_TMA_EPILOGUE 1
@@ -74,7 +77,6 @@ constexpr int NC = 4;                  // panel-copier warps (used by the tensor
 constexpr int kThreads = (NL + NC + NM + 4) * 32;
 constexpr uint32_t TMEM_PANELS = 256;  // first tensor-memory column of the panel ring (TS variant): S x 32 columns
 constexpr uint32_t ABLK_BYTES = 16 * 16 * 2;
-constexpr long long WAIT_LIMIT = 4000000000LL;  // clock cycles (about two seconds)
 
 // Shared-memory plan of a kernel whose work item is NH x 128 columns of C wide, for plans with at most CAP blocks
 // per step.
@@ -88,48 +90,20 @@ struct Cfg {
     static constexpr uint32_t OFF_BAR = OFF_META + S * 8;
     static constexpr uint32_t N_BARS = 3 * S + 4;
     static constexpr uint32_t OFF_MISC = OFF_BAR + N_BARS * 8;
-    // three fp16 tiles of 16 rows x 128 columns that the epilogue hands to TMA stores, 1024-byte aligned
+    // fp16 tiles of 16 rows x 128 columns that the epilogue hands to TMA stores (three per group of four epilogue
+    // warps), 1024-byte aligned
     static constexpr uint32_t OFF_EPI = (OFF_MISC + 16 + 1023) / 1024 * 1024;
     static constexpr uint32_t EPI_TILE_BYTES = 16 * 128 * 2;
     // (narrow items only: wide items have no room left for them beside five stages, and their items are long enough
     // for the epilogue not to matter)
     static constexpr bool TMA_EPILOGUE = SMAT_TMA_EPILOGUE && NH == 1;
-    static constexpr uint32_t SMEM_BYTES = (TMA_EPILOGUE ? OFF_EPI + 3 * EPI_TILE_BYTES : OFF_MISC + 16) + 1024;  // slack for the manual 1024-byte alignment
+    static constexpr uint32_t SMEM_BYTES = (TMA_EPILOGUE ? OFF_EPI + 6 * EPI_TILE_BYTES : OFF_MISC + 16) + 1024;  // slack for the manual 1024-byte alignment
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
     static_assert(STAGE_BYTES % 1024 == 0 && CAP <= 32, "stage alignment");
 };
 
 static_assert(RG == 16, "row masks and accumulator ownership below assume 16 block-rows per group");
 static_assert(RG * 2 * 16 <= 512 && TMEM_PANELS + Cfg<1, kPlanBlocksPerStep>::S * 32 <= 512, "tensor-memory budget");
-
-__device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_shared_u16(uint32_t addr, unsigned short v) {
-    asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(v) : "memory");
-}
-__device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
-    asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
-}
-
-
-// Bounded mbarrier wait.  After the first time-out anywhere in the CTA every wait returns at once.
-__device__ __forceinline__ void wait_bar(uint32_t bar, uint32_t parity, uint32_t abort_addr, int* status, int code) {
-    if (mbar_try_wait(bar, parity)) return;
-    if (ld_shared_u32(abort_addr)) return;
-    const long long t0 = clock64();
-    // suspended waits: the warp sleeps in hardware until the phase completes or ~2 us pass
-    while (!mbar_try_wait_suspend(bar, parity, 2000u)) {
-        if (ld_shared_u32(abort_addr)) return;
-        if (clock64() - t0 > WAIT_LIMIT) {
-            st_shared_u32(abort_addr, 1);
-            atomicCAS(status, 0, code);
-            return;
-        }
-    }
-}
 
 // One loader-warp pipeline record: a step on its way from "descriptor requested" to "copies issued".
 struct StepRec {
@@ -138,106 +112,6 @@ struct StepRec {
     uint32_t st;  // position of the step in this CTA's step sequence (selects the stage)
     uint4 d;      // {element column of the quad, first packed block, mask bits 0..31, mask bits 32..63}
 };
-
-// A segment: steps [k0, k1) of the ns steps of work item `item` (the first step of the item is steps[gs]).
-// cut: the item is computed in several segments by as many CTAs and this segment goes to scratch tile `slot`.
-struct Seg {
-    int item, k0, k1, ns, gs, slot;
-    bool cut;
-};
-
-// The (item, step) pairs of a launch flattened in item order; position 0 is the first step of the first item.
-struct Flat {
-    const int* gsp;
-    int n_tiles, n_groups;
-    long long total;  // number of positions
-    __device__ __forceinline__ long long first_of_group(int g) const { return (long long)(__ldg(gsp + g) - __ldg(gsp)) * n_tiles; }
-    // first position of CTA c's range when the positions are dealt out in `parts` equal contiguous ranges
-    __device__ __forceinline__ long long range_begin(int parts, int c) const { return total * c / parts; }
-    // the CTA whose range holds position p: the largest c with range_begin(c) <= p
-    __device__ __forceinline__ int range_owner(int parts, long long p) const { return (int)(((p + 1) * parts - 1) / total); }
-    // last group whose first position is <= p (groups without steps share their successor's first position)
-    __device__ __forceinline__ int group_of(long long p) const {
-        int lo = 0, hi = n_groups - 1;
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (first_of_group(mid) <= p) lo = mid; else hi = mid - 1;
-        }
-        return lo;
-    }
-};
-
-// What a CTA works on, in order.  Three schedules:
-//  * round-robin (default): work items go round-robin over the CTAs as long as there is one for every CTA.  The
-//    items left for the last round (fewer than CTAs) are each cut into P = #CTAs / #items-left segments of equal
-//    step count, one per CTA, so that the last round keeps every SM busy and takes 1/P of an item's time.  All
-//    items are cut at the same fractions and consecutive CTAs take consecutive segments, so the CTAs of a round
-//    still walk the block-columns in step (what they fetch is shared through L2).
-//  * listed (plans whose heaviest group holds many times the average number of steps): every CTA has a fixed list
-//    of whole groups, dealt out at plan time heaviest first to the least loaded CTA;
-//  * balanced (such plans when whole groups cannot be dealt out evenly, e.g. one group outweighs a CTA's share): the flattened
-//    (item, step) sequence is dealt out in equal contiguous ranges, one per CTA, whatever the number and the
-//    length of the items; an item that a range boundary falls into is computed in segments.
-// A cut item is assembled from fp32 partial tiles: each CTA stores its segment's result to a scratch tile (one
-// per CTA, two in the balanced schedule: the head and the tail of its range) and a small second kernel adds them.
-// SCHED: 0 = round-robin with a cut last round, 1 = listed, 2 = balanced ranges.
-template <int SCHED>
-struct SegGen {
-    const int* gsp;
-    int n_tiles, n_items, n_ctas, cta, item, n_full, P;
-    bool tail_done;
-    Flat flat;
-    long long p, p_begin, p_end;
-    int g;
-    const int* list;      // listed schedule: the groups of this CTA, else null
-    int li, li_end, lt;   // position in the list, its end, next tile of the current group
-    __device__ __forceinline__ bool next(Seg& s) {
-        if (SCHED == 1) {
-            if (li >= li_end) return false;
-            const int gg = __ldg(list + li);
-            const int gs = __ldg(gsp + gg), ns = __ldg(gsp + gg + 1) - gs;
-            s.item = gg * n_tiles + lt; s.k0 = 0; s.k1 = ns; s.ns = ns; s.gs = gs; s.cut = false; s.slot = 0;
-            if (++lt == n_tiles) { lt = 0; li++; }
-            return true;
-        }
-        if (SCHED == 2) {
-            if (p >= p_end) return false;
-            while (flat.first_of_group(g + 1) <= p) g++;  // groups without steps are passed over
-            const int gs = __ldg(gsp + g), ns = __ldg(gsp + g + 1) - gs;
-            const long long item_p0 = flat.first_of_group(g);
-            const long long off = p - item_p0;
-            const int t = (int)(off / ns), k0 = (int)(off - (long long)t * ns);
-            const long long left = p_end - p;
-            const int k1 = (left < (long long)(ns - k0)) ? k0 + (int)left : ns;
-            s.item = g * n_tiles + t; s.k0 = k0; s.k1 = k1; s.ns = ns; s.gs = gs;
-            s.cut = k0 != 0 || k1 != ns;
-            // the tail of this CTA's range (the item began inside the range) goes to its second tile
-            s.slot = cta * 2 + ((p_begin < item_p0 + (long long)t * ns) ? 1 : 0);
-            p += k1 - k0;
-            return true;
-        }
-        if (item < n_full) {
-            const int gg = item / n_tiles;
-            const int gs = __ldg(gsp + gg), ns = __ldg(gsp + gg + 1) - gs;
-            s.item = item; s.k0 = 0; s.k1 = ns; s.ns = ns; s.gs = gs; s.cut = false; s.slot = 0;
-            item += n_ctas;
-            return true;
-        }
-        if (tail_done) return false;
-        tail_done = true;
-        if (cta >= (n_items - n_full) * P) return false;
-        const int i = cta / P, j = cta - i * P;
-        const int gg = (n_full + i) / n_tiles;
-        const int gs = __ldg(gsp + gg), ns = __ldg(gsp + gg + 1) - gs;
-        s.item = n_full + i; s.gs = gs; s.ns = ns; s.cut = P > 1; s.slot = cta;
-        s.k0 = (int)((unsigned)ns * (unsigned)j / (unsigned)P);  // P <= kMaxTailParts: the products fit 32 bits
-        s.k1 = (int)((unsigned)ns * (unsigned)(j + 1) / (unsigned)P);
-        return true;
-    }
-};
-
-constexpr int kFixSlotFloats = 2 * RG * 16 * 128;  // one partial tile: up to 2 halves x 16 block-rows x 16 rows x 128 columns
-static_assert((size_t)kFixSlotFloats * sizeof(float) == (2 * 16 * 16 * 128) * sizeof(float), "fix_scratch_bytes() assumes this tile size");
 
 // TS = false: both MMA operands from shared memory, two accumulator buffers (the epilogue of an item
 //   overlaps the main loop of the next).
@@ -256,7 +130,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_const
                     const int* __restrict__ rowptr, __half* __restrict__ C, int brow_begin, int brow_end, int rg, int N,
                     int n_tiles, int n_items, int n_groups, int tail_parts, uint32_t panel_bytes,
                     float* __restrict__ fix_scratch, int* status, size_t ldc, const int* __restrict__ sched_off,
-                    const int* __restrict__ sched_list) {
+                    const int* __restrict__ sched_list, int nm) {
     static_assert(!(TS && NH == 2), "the panel ring and 32 accumulators do not fit tensor memory together");
     // The schedule is a template parameter: measured, the code generated for the MMA issue loop changed by up to 35 %
     // with the shape of the control flow around it, so each schedule gets a kernel with only its own loops.
@@ -277,6 +151,10 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_const
     auto acc_full = [&](uint32_t b) { return bar0 + 8 * (3 * S + b); };
     auto acc_empty = [&](uint32_t b) { return bar0 + 8 * (3 * S + 2 + b); };
     constexpr uint32_t NBUF = (TS || NH == 2) ? 1 : 2;
+    // Epilogue groups of four warps (one per tensor-memory lane quarter); group g takes block-rows g, g + EG, ...  The
+    // panel-copier warps, idle unless the panels go through tensor memory, form the second group: measured on work items
+    // of a dozen steps (dense clusters) the epilogue, not the main loop, bounds the kernel.
+    constexpr int EG = TS ? 1 : 2;
     const uint32_t tmem_slot = base + OFF_MISC;
     const uint32_t abort_addr = base + OFF_MISC + 4;
 
@@ -305,8 +183,10 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_const
     };
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < S; s++) { mbar_init(full(s), 1); mbar_init(empty(s), NM); mbar_init(tfull(s), 1); }
-        for (uint32_t b = 0; b < 2; b++) { mbar_init(acc_full(b), NM); mbar_init(acc_empty(b), 4); }
+        // nm <= NM of the MMA warps take part (fewer warps own more rows each, so that runs of vertically adjacent
+        // blocks -- one MMA each -- can be longer: plans of densely filled quads)
+        for (uint32_t s = 0; s < S; s++) { mbar_init(full(s), 1); mbar_init(empty(s), (uint32_t)nm); mbar_init(tfull(s), 1); }
+        for (uint32_t b = 0; b < 2; b++) { mbar_init(acc_full(b), (uint32_t)nm); mbar_init(acc_empty(b), 4 * EG); }
         st_shared_u32(abort_addr, 0);
         fence_barrier_init();
         fence_proxy_async();
@@ -330,6 +210,110 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_const
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+
+    // ------------------------------ epilogue: tensor memory -> fp16 -> C ------------------------------
+    auto epilogue = [&](const int grp) {
+        const int quarter = warp & 3;  // a warp may only read tensor-memory lanes [32*(warp%4), +32)
+        const bool odd = lane & 1;
+        const int et = quarter * 32 + lane;  // index among the 128 epilogue threads = column within a 128-column half
+        if (balanced && grp == 0) {
+            // groups without any block have no steps, so no range reaches them: their rows of C are zeroed here
+            for (int g = (int)blockIdx.x; g < n_groups; g += (int)gridDim.x) {
+                if (__ldg(gsp + g + 1) != __ldg(gsp + g)) continue;
+                const int r0 = brow_begin + g * rg;
+                const int nrows = min(rg, brow_end - r0);
+                for (int row = 0; row < nrows * 16; row++) {
+                    uint4* dst = reinterpret_cast<uint4*>(C + ((size_t)(r0 - brow_begin) * 16 + row) * ldc);
+                    for (int i = et; i < N / 8; i += 128) dst[i] = make_uint4(0, 0, 0, 0);
+                }
+            }
+        }
+        uint32_t it = 0, epi_n = 0;
+        const uint32_t c_pitch = (uint32_t)(N < 128 ? N : 128) * 2u;  // bytes per row of a tile = the box of mapC
+        SegGen<SCHED> sg = make_gen();
+        Seg cs;
+        for (; sg.next(cs); ++it) {
+            const int g = cs.item / n_tiles, t = cs.item - g * n_tiles;
+            const int r0 = brow_begin + g * rg;
+            const int nrows = min(rg, brow_end - r0);
+            const int lo = (lane < nrows) ? __ldg(rowptr + r0 + lane) : 0;
+            const int hi = (lane < nrows) ? __ldg(rowptr + r0 + lane + 1) : 0;
+            const uint32_t nonempty = __ballot_sync(0xffffffffu, hi > lo);
+            const uint32_t buf = it % NBUF;
+            const bool partial = cs.cut;
+            float* part_dst = fix_scratch + (size_t)cs.slot * (size_t)kFixSlotFloats;  // scratch tile of this segment
+            if (lane == 0) wait_bar(acc_full(buf), (it / NBUF) & 1, abort_addr, status, 6);
+            __syncwarp();
+            tc_fence_after();
+            int last_r = -1;  // last block-row this group handles
+            for (int r = grp; r < nrows; r += EG) last_r = r;
+            if (last_r < 0 && lane == 0) mbar_arrive(acc_empty(buf));  // nothing to read: hand the accumulators back at once
+            for (int r = grp; r < nrows; r += EG) {
+#pragma unroll
+                for (int h = 0; h < NH; h++) {
+                    const int n = t * NT + h * 128 + et;
+                    uint32_t v[16];
+                    if ((nonempty >> r) & 1u) {
+                        const uint32_t taddr =
+                            tmem_base + ((uint32_t)(quarter * 32) << 16) + ((buf * NH + h) * RG + (uint32_t)r) * 16;
+                        tmem_ld_x16(taddr, v);
+                        tmem_ld_wait();
+                        tmem_zero_x16(taddr);  // leave the accumulator zeroed for the next segment that uses this buffer
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; i++) v[i] = 0u;
+                    }
+                    if (r == last_r && h == NH - 1) {
+                        // this warp has read and zeroed its share of the buffer: hand it back to the MMA warps
+                        tmem_st_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acc_empty(buf));
+                    }
+                    if (partial) {
+                        float* d = part_dst + ((size_t)(h * RG + r) * 16) * 128 + et;
+#pragma unroll
+                        for (int i = 0; i < 16; i++) d[(size_t)i * 128] = __uint_as_float(v[i]);
+                        continue;
+                    }
+                    if constexpr (G::TMA_EPILOGUE) {
+                        // fp16 tile of this block-row (16 rows x 128 columns, row-major, `c_pitch` bytes per row) in shared
+                        // memory, handed to one TMA store; three tiles in rotation: the tile written now was last read by
+                        // the store issued three tiles ago, whose completion the issuing thread awaited before the
+                        // barrier of the previous tile.
+                        const uint32_t tile = base + G::OFF_EPI + ((uint32_t)grp * 3u + epi_n % 3u) * G::EPI_TILE_BYTES;
+                        if ((uint32_t)et * 2u < c_pitch) {  // C narrower than a tile: the rows of the box are N columns long
+#pragma unroll
+                            for (int i = 0; i < 16; i++)
+                                st_shared_u16(tile + (uint32_t)i * c_pitch + (uint32_t)et * 2u,
+                                              __half_as_ushort(__float2half_rn(__uint_as_float(v[i]))));
+                        }
+                        fence_proxy_async();
+                        if (et == 0) bulk_wait_group_read<1>();
+                        if (grp == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+                        else asm volatile("bar.sync 2, 128;" ::: "memory");
+                        if (et == 0) {
+                            tma_store_2d(&mapC, tile, t * NT + h * 128, (r0 - brow_begin + r) * 16);
+                            bulk_commit_group();
+                        }
+                        epi_n++;
+                        continue;
+                    }
+                    __half* crow = C + ((size_t)(r0 - brow_begin + r) * 16 + (odd ? 8 : 0)) * ldc + (size_t)(n & ~1);
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        // lane pairs exchange halves: even lanes keep rows 0..7, odd lanes rows 8..15,
+                        // each for the two adjacent columns (n & ~1, n | 1) -> one 4-byte store per row
+                        const float keep = __uint_as_float(odd ? v[i + 8] : v[i]);
+                        const float send = __uint_as_float(odd ? v[i] : v[i + 8]);
+                        const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+                        const __half2 hh = odd ? __floats2half2_rn(recv, keep) : __floats2half2_rn(keep, recv);
+                        if (n < N) *reinterpret_cast<__half2*>(crow + (size_t)i * ldc) = hh;
+                    }
+                }
+            }
+        }
+    };
 
     if (warp < NL) {
         // ------------------------------ loader warp j: every NL-th step ------------------------------
@@ -395,6 +379,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_const
         __syncwarp();
     } else if (warp < NL + NC) {
         // ------------------------------ panel copier j (TS only): shared -> tensor memory, every NC-th step ------------------------------
+        if constexpr (!TS) epilogue(1);
         if (TS && lane == 0) {
             const uint32_t j = (uint32_t)(warp - NL);
             uint32_t st = 0;
@@ -427,11 +412,11 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_const
         // The whole warp walks the step's (sub-column, row) mask in lock-step and one elected lane issues;
         // the mask words reach the loop as ballots, i.e. as values the compiler knows to be warp-uniform.
         // (Measured: a single lane walking a precomputed list of MMAs from shared memory was ~20 % slower.)
-        {
+        if (warp - NL - NC < nm) {
             const uint32_t m = (uint32_t)__shfl_sync(0xffffffffu, warp - NL - NC, 0);
             const uint32_t P_HI = (uint32_t)(smem_desc_k_sw128(0) >> 32), B_HI = (uint32_t)(smem_desc_k_sw32(0) >> 32);
             constexpr uint32_t IDESC_N0 = idesc_f16_f32(128, 0);  // the N field is added per run: N = 16 * length
-            const uint32_t rpo = (uint32_t)((rg + NM - 1) / NM);  // rows per owning warp (the last warps may own none)
+            const uint32_t rpo = (uint32_t)((rg + nm - 1) / nm);  // rows per owning warp (the last warps may own none)
             const uint32_t rows_m = ((1u << rpo) - 1u) << (m * rpo);
             const uint32_t own32 = (rows_m & 0xffffu) | (rows_m << 16);  // this warp's rows in both sub-columns of a mask word
             const bool leader = elect_one();  // the lane that issues; fixed, so that its commits cover its MMAs
@@ -464,7 +449,8 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_const
                         uint32_t own = mw & own32;
                         while (own) {
                             const uint32_t b = (uint32_t)__ffs((int)own) - 1u;
-                            const uint32_t len = min((uint32_t)__ffs((int)~(own >> b)) - 1u, 4u);  // run of adjacent rows
+                            // run of adjacent rows of this sub-column (a mask word holds two sub-columns of 16 rows)
+                            const uint32_t len = min((uint32_t)__ffs((int)~(own >> b)) - 1u, 16u - (b & 15u));
                             const uint32_t q = qbase + (uint32_t)__popc(mw & ((1u << b) - 1u));   // blocks are stored in mask-bit order
                             const uint32_t r0 = b & 15u, sub = (uint32_t)half * 2u + (b >> 4);
                             const uint32_t idesc = IDESC_N0 + ((2u * len) << 17);
@@ -523,106 +509,11 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_const
         }
         __syncwarp();
     } else {
-        // ------------------------------ epilogue: tensor memory -> fp16 -> C ------------------------------
-        const int quarter = warp & 3;  // a warp may only read tensor-memory lanes [32*(warp%4), +32)
-        const bool odd = lane & 1;
-        const int et = quarter * 32 + lane;  // index among the 128 epilogue threads = column within a 128-column half
-        if (balanced) {
-            // groups without any block have no steps, so no range reaches them: their rows of C are zeroed here
-            for (int g = (int)blockIdx.x; g < n_groups; g += (int)gridDim.x) {
-                if (__ldg(gsp + g + 1) != __ldg(gsp + g)) continue;
-                const int r0 = brow_begin + g * rg;
-                const int nrows = min(rg, brow_end - r0);
-                for (int row = 0; row < nrows * 16; row++) {
-                    uint4* dst = reinterpret_cast<uint4*>(C + ((size_t)(r0 - brow_begin) * 16 + row) * ldc);
-                    for (int i = et; i < N / 8; i += 128) dst[i] = make_uint4(0, 0, 0, 0);
-                }
-            }
-        }
-        uint32_t it = 0, epi_n = 0;
-        const uint32_t c_pitch = (uint32_t)(N < 128 ? N : 128) * 2u;  // bytes per row of a tile = the box of mapC
-        SegGen<SCHED> sg = make_gen();
-        Seg cs;
-        for (; sg.next(cs); ++it) {
-            const int g = cs.item / n_tiles, t = cs.item - g * n_tiles;
-            const int r0 = brow_begin + g * rg;
-            const int nrows = min(rg, brow_end - r0);
-            const int lo = (lane < nrows) ? __ldg(rowptr + r0 + lane) : 0;
-            const int hi = (lane < nrows) ? __ldg(rowptr + r0 + lane + 1) : 0;
-            const uint32_t nonempty = __ballot_sync(0xffffffffu, hi > lo);
-            const uint32_t buf = it % NBUF;
-            const bool partial = cs.cut;
-            float* part_dst = fix_scratch + (size_t)cs.slot * (size_t)kFixSlotFloats;  // scratch tile of this segment
-            if (lane == 0) wait_bar(acc_full(buf), (it / NBUF) & 1, abort_addr, status, 6);
-            __syncwarp();
-            tc_fence_after();
-            for (int r = 0; r < nrows; r++) {
-#pragma unroll
-                for (int h = 0; h < NH; h++) {
-                    const int n = t * NT + h * 128 + et;
-                    uint32_t v[16];
-                    if ((nonempty >> r) & 1u) {
-                        const uint32_t taddr =
-                            tmem_base + ((uint32_t)(quarter * 32) << 16) + ((buf * NH + h) * RG + (uint32_t)r) * 16;
-                        tmem_ld_x16(taddr, v);
-                        tmem_ld_wait();
-                        tmem_zero_x16(taddr);  // leave the accumulator zeroed for the next segment that uses this buffer
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 16; i++) v[i] = 0u;
-                    }
-                    if (r == nrows - 1 && h == NH - 1) {
-                        // every accumulator of this buffer has been read and zeroed: hand it back to the MMA warps
-                        tmem_st_wait();
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(acc_empty(buf));
-                    }
-                    if (partial) {
-                        float* d = part_dst + ((size_t)(h * RG + r) * 16) * 128 + et;
-#pragma unroll
-                        for (int i = 0; i < 16; i++) d[(size_t)i * 128] = __uint_as_float(v[i]);
-                        continue;
-                    }
-                    if constexpr (G::TMA_EPILOGUE) {
-                        // fp16 tile of this block-row (16 rows x 128 columns, row-major, `c_pitch` bytes per row) in shared
-                        // memory, handed to one TMA store; three tiles in rotation: the tile written now was last read by
-                        // the store issued three tiles ago, whose completion the issuing thread awaited before the
-                        // barrier of the previous tile.
-                        const uint32_t tile = base + G::OFF_EPI + (epi_n % 3u) * G::EPI_TILE_BYTES;
-                        if ((uint32_t)et * 2u < c_pitch) {  // C narrower than a tile: the rows of the box are N columns long
-#pragma unroll
-                            for (int i = 0; i < 16; i++)
-                                st_shared_u16(tile + (uint32_t)i * c_pitch + (uint32_t)et * 2u,
-                                              __half_as_ushort(__float2half_rn(__uint_as_float(v[i]))));
-                        }
-                        fence_proxy_async();
-                        if (et == 0) bulk_wait_group_read<1>();
-                        asm volatile("bar.sync 1, 128;" ::: "memory");
-                        if (et == 0) {
-                            tma_store_2d(&mapC, tile, t * NT + h * 128, (r0 - brow_begin + r) * 16);
-                            bulk_commit_group();
-                        }
-                        epi_n++;
-                        continue;
-                    }
-                    __half* crow = C + ((size_t)(r0 - brow_begin + r) * 16 + (odd ? 8 : 0)) * ldc + (size_t)(n & ~1);
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        // lane pairs exchange halves: even lanes keep rows 0..7, odd lanes rows 8..15,
-                        // each for the two adjacent columns (n & ~1, n | 1) -> one 4-byte store per row
-                        const float keep = __uint_as_float(odd ? v[i + 8] : v[i]);
-                        const float send = __uint_as_float(odd ? v[i] : v[i + 8]);
-                        const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
-                        const __half2 hh = odd ? __floats2half2_rn(recv, keep) : __floats2half2_rn(keep, recv);
-                        if (n < N) *reinterpret_cast<__half2*>(crow + (size_t)i * ldc) = hh;
-                    }
-                }
-            }
-        }
+        epilogue(0);
     }
 
-    if (G::TMA_EPILOGUE && warp == NL + NC + NM && lane == 0) bulk_wait_group_all();  // the thread that issued the stores of C
+    // the threads that issued the stores of C (one per epilogue group)
+    if (G::TMA_EPILOGUE && (warp == NL + NC + NM || (!TS && warp == NL)) && lane == 0) bulk_wait_group_all();
     tc_fence_before();
     __syncthreads();
     if (ld_shared_u32(abort_addr)) {
@@ -723,6 +614,33 @@ __global__ void __launch_bounds__(512) sum_split_items_kernel(const float* __res
 
 int g_spmm_variant = 0;
 
+PlanView plan_group_range(const PlanView& whole, size_t group_begin, size_t group_end) {
+    PlanView plan = whole;
+    if (group_begin > 0 || group_end < whole.n_groups) {
+        plan.gsp = whole.gsp + group_begin;
+        plan.n_groups = group_end - group_begin;
+        plan.brow_begin = whole.brow_begin + group_begin * whole.rg;
+        if (whole.brow_begin + group_end * whole.rg < whole.brow_end) plan.brow_end = whole.brow_begin + group_end * whole.rg;
+        plan.nnzb = whole.nnzb * plan.n_groups / whole.n_groups;  // only steers the choice of the variant
+        if (plan.nnzb == 0 && whole.nnzb) plan.nnzb = 1;
+        plan.total_steps = whole.total_steps * plan.n_groups / whole.n_groups;
+    }
+    return plan;
+}
+
+int launch_sum_cut_items(bool wide, int cut_items, const float* scratch, void* C, int brow_begin, int brow_end, int rg, int N,
+                         int n_tiles, int n_full, int parts, size_t ldc, cudaStream_t stream) {
+    if (wide)
+        sum_cut_items_kernel<2><<<cut_items, dim3(128, 4), 0, stream>>>(scratch, reinterpret_cast<__half*>(C), brow_begin, brow_end, rg, N,
+                                                                       n_tiles, n_full, parts, ldc);
+    else
+        sum_cut_items_kernel<1><<<cut_items, dim3(128, 4), 0, stream>>>(scratch, reinterpret_cast<__half*>(C), brow_begin, brow_end, rg, N,
+                                                                       n_tiles, n_full, parts, ldc);
+    count_launch();
+    SMAT_CUDA_TRY(cudaGetLastError());
+    return SMAT_OK;
+}
+
 int launch_spmm(const PlanView& whole, const void* B, void* C, size_t N, cudaStream_t stream, const DeviceCtx* ctx_in,
                 size_t ldc, size_t group_begin, size_t group_end) {
     const DeviceCtx* ctx = ctx_in;
@@ -734,18 +652,10 @@ int launch_spmm(const PlanView& whole, const void* B, void* C, size_t N, cudaStr
     if (ldc == 0) ldc = N;
     // the view of the groups asked for: steps, blocks and row pointers are addressed absolutely, so a sub-range is
     // the same plan with its first group, first block-row and group count moved
-    PlanView plan = whole;
+    if (whole.tall) return launch_spmm_tall(whole, B, C, N, stream, ctx, ldc, group_begin, group_end);
     if (group_end > whole.n_groups) group_end = whole.n_groups;
-    if (group_begin > 0 || group_end < whole.n_groups) {
-        if (group_begin >= group_end) return SMAT_OK;
-        plan.gsp = whole.gsp + group_begin;
-        plan.n_groups = group_end - group_begin;
-        plan.brow_begin = whole.brow_begin + group_begin * whole.rg;
-        if (whole.brow_begin + group_end * whole.rg < whole.brow_end) plan.brow_end = whole.brow_begin + group_end * whole.rg;
-        plan.nnzb = whole.nnzb * plan.n_groups / whole.n_groups;  // only steers the choice of the variant
-        if (plan.nnzb == 0 && whole.nnzb) plan.nnzb = 1;
-        plan.total_steps = whole.total_steps * plan.n_groups / whole.n_groups;
-    }
+    if (group_begin >= group_end) return SMAT_OK;
+    const PlanView plan = plan_group_range(whole, group_begin, group_end);
     const size_t nb_rows = plan.brow_end - plan.brow_begin;
     if (nb_rows == 0 || N == 0) return SMAT_OK;
     if (plan.nnzb == 0) {
@@ -796,13 +706,24 @@ int launch_spmm(const PlanView& whole, const void* B, void* C, size_t N, cudaStr
     const int parts = (balanced || listed) ? 1 : (int)tail_parts(n_items);
     const int grid = (int)((balanced || listed || parts > 1 || n_items > sms) ? sms : n_items);
     const int n_full = (int)(n_items / (size_t)grid * (size_t)grid);
+    // MMA-issuing warps: 8 own two accumulator rows each; plans whose steps are nearly full use fewer warps with more
+    // rows each, so that a column of vertically adjacent blocks is multiplied by one MMA (N up to 256) instead of eight
+    int nm = NM;
+    if (plan.total_steps) {
+        const size_t per_step = plan.nnzb / plan.total_steps;
+        nm = per_step >= 40 ? 1 : per_step >= 20 ? 2 : NM;
+    }
+    if (const char* ev = std::getenv("SMAT_MMA_WARPS")) {  // tuning knob
+        const int v = std::atoi(ev);
+        if (v == 1 || v == 2 || v == 4 || v == 8) nm = v;
+    }
     auto launch = [&](auto kernel, uint32_t smem_bytes) -> int {
         SMAT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
         kernel<<<grid, kThreads, smem_bytes, stream>>>(
             mapB, mapC, reinterpret_cast<const uint8_t*>(plan.packed), reinterpret_cast<const uint4*>(plan.steps), plan.gsp,
             plan.rowptr, reinterpret_cast<__half*>(C), (int)plan.brow_begin, (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles,
             (int)n_items, (int)plan.n_groups, parts, panel_rows * 128u, plan.fix_scratch, ctx->d_status, ldc,
-            listed ? plan.sched_off : nullptr, listed ? plan.sched_list : nullptr);
+            listed ? plan.sched_off : nullptr, listed ? plan.sched_list : nullptr, nm);
         count_launch();
         SMAT_CUDA_TRY(cudaGetLastError());
         return SMAT_OK;
@@ -839,16 +760,8 @@ int launch_spmm(const PlanView& whole, const void* B, void* C, size_t N, cudaStr
         return SMAT_OK;
     }
     if (parts == 1) return rc;
-    const int cut_items = (int)n_items - n_full;
-    if (variant == 3)
-        sum_cut_items_kernel<2><<<cut_items, dim3(128, 4), 0, stream>>>(plan.fix_scratch, reinterpret_cast<__half*>(C), (int)plan.brow_begin,
-                                                                       (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles, n_full, parts, ldc);
-    else
-        sum_cut_items_kernel<1><<<cut_items, dim3(128, 4), 0, stream>>>(plan.fix_scratch, reinterpret_cast<__half*>(C), (int)plan.brow_begin,
-                                                                       (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles, n_full, parts, ldc);
-    count_launch();
-    SMAT_CUDA_TRY(cudaGetLastError());
-    return SMAT_OK;
+    return launch_sum_cut_items(variant == 3, (int)n_items - n_full, plan.fix_scratch, C, (int)plan.brow_begin, (int)plan.brow_end,
+                                (int)plan.rg, (int)N, n_tiles, n_full, parts, ldc, stream);
 }
 
 }  // namespace smat

@@ -1,0 +1,433 @@
+// Block-sparse SpMM for NVIDIA B200 (sm_100a), "tall" variant: work items of up to 24 block-rows x 128 columns of C,
+// B panels read by the MMAs from TENSOR memory.  Same boundary, layouts and transposed mapping as spmm_sm100.cu
+// (replaces mmaCBTKernel, src/cuda_hgemm/src/mma/mmaCBT.cu:13-88); chosen by the plan for matrices whose groups hold
+// several blocks per four block-columns without being dense (a block-sparse weight matrix, a reordered random matrix).
+//
+// Why a second kernel.  Measured on B200 (148 SMs, 1965 MHz):
+//   * tcgen05.mma M128 x N16 x K16 with the "A" operand (the 128 n x 16 k panel slice of B) in SHARED memory takes
+//     ~39 cycles per SM -- the 4 KB slice crosses the shared-memory operand port once per 16x16 block -- against ~9
+//     cycles with the slice in TENSOR memory ([tmem] operand; N = 32: ~9, N = 64: 32).  A 16-row work item of the
+//     shared-memory kernel is bound by exactly that port.
+//   * Streaming the panels L2 -> shared memory sustains ~70 bytes/cycle/SM (19-20 TB/s over the chip).  The panel
+//     traffic of a launch is (block-rows / rows per group) x K x N x 2 bytes, so taller groups cut it in proportion;
+//     tensor memory (512 columns) holds 24 accumulators of 16 columns plus a ring of four panels.
+//   * A thread can issue a tcgen05.mma only every ~70-190 cycles, different warps issue concurrently, and
+//     tcgen05.commit costs the tensor pipe nothing measurable.  So 12 warps issue, each owning two accumulator rows
+//     (all MMAs into one accumulator come from one thread, in order: results do not depend on warp timing), and
+//     each computes the operands of a step's (at most four) MMAs first and then issues them back to back.
+//
+// Pipeline per step (four block-columns of a group), all hand-overs by mbarriers, every wait bounded:
+//   loader warps (4, one thread each, every 4th step): TMA box {64 k, 128 n} -> panel slot (4 slots), bulk copy of the
+//     step's packed A blocks -> block slot (8 slots), the step's row masks -> a meta slot;
+//   copier warps (4, one thread each, warp j owns panel slot j): wait panel + blocks, tcgen05.cp the non-empty
+//     sub-columns shared -> tensor memory ring (slot j), commit -> cp_done of the step's pair.  That frees the shared panel
+//     slot for the loader and tells the MMA warps that panel AND blocks of the step are in place;
+//   MMA warps (12): per PAIR of steps wait cp_done once, read the masks, issue, commit -> step_done (a plain arrive
+//     when the warp had no block in the pair); step_done frees the block slots (loader) and the tensor-memory panel
+//     slots (copier) of the pair;
+//   epilogue warps (8 = two per tensor-memory lane quarter, alternating block-rows): tcgen05.ld -> zero the
+//     accumulator -> fp16 -> shared-memory tile -> one TMA store per block-row; cut items write fp32 partial tiles.
+// Scheduling is the round-robin-with-cut-last-round scheme of spmm_sm100.cu (SegGen<0>).
+#include <cuda_fp16.h>
+#include <limits.h>
+
+#include "ptx_sm100.cuh"
+#include "smat_internal.h"
+#include "spmm_sched.cuh"
+
+namespace smat {
+
+using namespace ptx;
+
+namespace {
+
+constexpr int TRG = kTallRows;   // block-rows per work item (accumulators)
+constexpr int NLW = 4;           // loader warps
+constexpr int NCW = 4;           // copier warps = panel slots
+constexpr int NMW = TRG / 2;     // MMA warps, two accumulator rows each
+constexpr int NEW = 8;           // epilogue warps
+constexpr int kTallThreads = (NLW + NCW + NMW + NEW) * 32;
+constexpr uint32_t PS = 8;                                   // panel slots in shared memory
+constexpr uint32_t TS_ = 4;                                  // panel slots in tensor memory
+constexpr uint32_t BS = 8;                                   // block slots
+constexpr uint32_t PANEL_BYTES = 128 * 64 * 2;               // 128 n x 64 k fp16
+constexpr uint32_t BLK_SLOT_BYTES = kTallBlocksPerStep * 512;
+constexpr uint32_t OFF_PANEL = 0;
+constexpr uint32_t OFF_BLK = OFF_PANEL + PS * PANEL_BYTES;
+constexpr uint32_t META_BYTES = 64;                           // per step: 12 per-warp words + the non-empty sub-columns
+constexpr uint32_t OFF_META = OFF_BLK + BS * BLK_SLOT_BYTES;
+constexpr uint32_t OFF_BAR = OFF_META + BS * META_BYTES;
+constexpr uint32_t NPAIR = BS / 2;                            // pairs of steps whose blocks are in flight
+constexpr uint32_t N_BARS = PS + BS + NPAIR + NPAIR + 2;
+constexpr uint32_t OFF_MISC = OFF_BAR + N_BARS * 8;
+constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;        // slack for the manual 1024-byte alignment
+constexpr uint32_t TMEM_ACC = 0;                             // accumulators: TRG x 16 columns
+constexpr uint32_t TMEM_PANELS = TRG * 16;                   // panel ring: TS_ x 32 columns
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+static_assert(TMEM_PANELS + TS_ * 32 <= 512, "tensor-memory budget");
+static_assert(PS % NCW == 0 && BS % NCW == 0 && PS % NLW == 0 && BS % NLW == 0 && PS == BS && TS_ == 4 && NCW == 4,
+              "the barrier phase arithmetic below assumes these (a thread must see every phase of a barrier it waits on)");
+static_assert(TRG * 16 * 128 <= kFixSlotFloats, "a partial tile must fit a scratch slot");
+
+struct TallStep {
+    int live;
+    int tile;
+    int idx;      // index of the step in the plan
+    uint32_t st;  // its position in this CTA's sequence
+    uint4 a;      // {element column, packed position (256-byte units), blocks, 0}
+};
+
+__global__ void __launch_bounds__(kTallThreads, 1)
+spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __restrict__ packed,
+                      const uint4* __restrict__ steps, const uint4* __restrict__ winfo, const int* __restrict__ gsp,
+                      const int* __restrict__ rowptr,
+                      __half* __restrict__ C, size_t ldc, int brow_begin, int brow_end, int rg, int N, int n_tiles, int n_items,
+                      int tail_parts, uint32_t panel_bytes, float* __restrict__ fix_scratch, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar0 = base + OFF_BAR;
+    auto full_p = [&](uint32_t s) { return bar0 + 8 * s; };
+    auto full_b = [&](uint32_t s) { return bar0 + 8 * (PS + s); };
+    // The MMA warps are handed the steps two at a time (pair p = steps 2p, 2p + 1 of the CTA's sequence, whatever
+    // work items they belong to): measured, a barrier wait or a commit costs the issuing thread about as much as an
+    // MMA (~100 cycles), so one of each per step and warp would hold the whole pipeline back.
+    auto cp_done = [&](uint32_t p) { return bar0 + 8 * (PS + BS + p); };            // both panels of pair p (mod NPAIR) copied
+    auto step_done = [&](uint32_t p) { return bar0 + 8 * (PS + BS + NPAIR + p); };  // all MMAs of pair p (mod NPAIR) completed
+    const uint32_t acc_full = bar0 + 8 * (PS + BS + 2 * NPAIR), acc_empty = acc_full + 8;
+    const uint32_t tmem_slot = base + OFF_MISC;
+    const uint32_t abort_addr = base + OFF_MISC + 4;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+#ifdef SMAT_PROFILE
+    const long long t_kernel0 = clock64();
+#endif
+    const int n_full = n_items / (int)gridDim.x * (int)gridDim.x;  // items of the complete rounds
+    auto make_gen = [&]() {
+        SegGen<0> sg;
+        sg.gsp = gsp; sg.n_tiles = n_tiles; sg.n_items = n_items; sg.n_ctas = (int)gridDim.x; sg.cta = (int)blockIdx.x;
+        sg.item = (int)blockIdx.x; sg.n_full = n_full; sg.P = tail_parts; sg.tail_done = false;
+        sg.flat.gsp = gsp; sg.flat.n_tiles = n_tiles; sg.flat.n_groups = 0; sg.flat.total = 0; sg.g = 0;
+        sg.p = sg.p_begin = sg.p_end = 0;
+        sg.list = nullptr; sg.li = sg.li_end = 0; sg.lt = 0;
+        return sg;
+    };
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < PS; s++) mbar_init(full_p(s), 1);
+        for (uint32_t s = 0; s < BS; s++) mbar_init(full_b(s), 1);
+        for (uint32_t s = 0; s < NPAIR; s++) { mbar_init(cp_done(s), 2); mbar_init(step_done(s), NMW); }
+        mbar_init(acc_full, NMW);
+        mbar_init(acc_empty, NEW);
+        st_shared_u32(abort_addr, 0);
+        fence_barrier_init();
+        fence_proxy_async();
+        prefetch_tensormap(&mapB);
+    }
+    if (warp == NLW) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ld_shared_u32(tmem_slot);
+    if (warp < 4) {  // all accumulators start at zero (later the epilogue re-zeroes what it reads)
+#pragma unroll 4
+        for (uint32_t c = 0; c < (uint32_t)TRG * 16; c += 16) tmem_zero_x16(tmem_base + ((uint32_t)(warp * 32) << 16) + TMEM_ACC + c);
+        tmem_st_wait();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    if (warp < NLW) {
+        // ------------------------------ loader warp j: steps j, j + NLW, ... ------------------------------
+        if (lane == 0) {
+            const int j = warp;
+            SegGen<0> sg = make_gen();
+            Seg cs;
+            bool have = sg.next(cs);
+            uint32_t h_st0 = 0, h_next = (uint32_t)j;
+#ifndef SMAT_TALL_PF
+#define SMAT_TALL_PF 2
+#endif
+            constexpr int U = 4;  // step records in flight per loader (their descriptors are requested U positions ahead)
+            constexpr int PF = SMAT_TALL_PF;  // records ahead (of this loader) whose data is prefetched into L2; 0 = none
+            TallStep rec[U];
+            auto gen = [&](TallStep& r) {
+                while (have && h_next >= h_st0 + (uint32_t)(cs.k1 - cs.k0)) {
+                    h_st0 += (uint32_t)(cs.k1 - cs.k0);
+                    have = sg.next(cs);
+                }
+                r.live = have;
+                if (have) {
+                    r.tile = cs.item % n_tiles;
+                    r.st = h_next;
+                    r.idx = cs.gs + cs.k0 + (int)(h_next - h_st0);
+                    r.a = __ldg(steps + r.idx);
+                    h_next += NLW;
+                }
+            };
+            auto prefetch = [&](const TallStep& r) {  // HBM latency is hidden in L2: fetched PF records ahead of the copies
+                if (PF > 0 && r.live) {
+                    tma_prefetch_l2_2d(&mapB, (int)r.a.x, r.tile * 128);
+                    bulk_prefetch_l2(packed + (size_t)r.a.y * 256, r.a.z * 512u);
+                }
+            };
+#pragma unroll
+            for (int a = 0; a < U; a++) gen(rec[a]);
+#pragma unroll
+            for (int a = 0; a < PF; a++) prefetch(rec[a]);
+            bool more = true;
+            while (more) {
+#pragma unroll
+                for (int a = 0; a < U; a++) {
+                    TallStep& r = rec[a];
+                    if (!r.live) { more = false; break; }
+                    const uint32_t ps = r.st % PS, bs = r.st % BS, pi = r.st >> 1;
+                    // Blocks first: their slot (and the meta slot) is free once the MMAs of the step BS positions back
+                    // (pair pi - NPAIR) have completed; it rarely has to be waited for.
+                    if (pi >= NPAIR) wait_bar(step_done(pi % NPAIR), ((pi - NPAIR) / NPAIR) & 1, abort_addr, status, 2);
+                    const uint32_t a_bytes = r.a.z * 512u;
+                    mbar_arrive_expect_tx(full_b(bs), a_bytes + META_BYTES);
+                    bulk_load(base + OFF_META + bs * META_BYTES, winfo + 4 * (size_t)r.idx, META_BYTES, full_b(bs));
+                    bulk_load(base + OFF_BLK + bs * BLK_SLOT_BYTES, packed + (size_t)r.a.y * 256, a_bytes, full_b(bs));
+                    // Then the panel, whose slot is what the pipeline usually waits for: it is free once the copy of the
+                    // step PS positions back (pair pi - PS / 2) has left it; nothing but the copy itself follows the wait.
+                    if (pi >= PS / 2) wait_bar(cp_done((pi - PS / 2) % NPAIR), ((pi - PS / 2) / NPAIR) & 1, abort_addr, status, 1);
+                    mbar_arrive_expect_tx(full_p(ps), panel_bytes);
+                    tma_load_2d(base + OFF_PANEL + ps * PANEL_BYTES, &mapB, (int)r.a.x, r.tile * 128, full_p(ps));
+                    prefetch(rec[(a + PF) % U]);
+                    gen(r);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp < NLW + NCW) {
+        // ------------------------------ copier j: panel slot j, steps j, j + NCW, ... ------------------------------
+        if (lane == 0) {
+            const uint32_t j = (uint32_t)(warp - NLW);
+            uint32_t total = 0;  // steps of this CTA
+            {
+                SegGen<0> sg = make_gen();
+                Seg cs;
+                while (sg.next(cs)) total += (uint32_t)(cs.k1 - cs.k0);
+            }
+            for (uint32_t st = j; st < total; st += NCW) {
+                const uint32_t ps = st % PS, bs = st % BS, pi = st >> 1;
+                // everything that is usually there already first, so that only the copies follow the panel's arrival
+                wait_bar(full_b(bs), (st / BS) & 1, abort_addr, status, 4);
+                // the tensor-memory slot is free once the MMAs of the step TS_ positions back (pair pi - 2) have completed
+                if (pi >= TS_ / 2) wait_bar(step_done((pi - TS_ / 2) % NPAIR), ((pi - TS_ / 2) / NPAIR) & 1, abort_addr, status, 5);
+                const uint32_t subs = ld_shared_u32(base + OFF_META + bs * META_BYTES + 48);  // non-empty sub-columns
+                const uint64_t pdesc = smem_desc_k_sw128(base + OFF_PANEL + ps * PANEL_BYTES);
+                const uint32_t tdst = tmem_base + TMEM_PANELS + (st % TS_) * 32;
+                wait_bar(full_p(ps), (st / PS) & 1, abort_addr, status, 3);
+                tc_fence_after();
+#ifndef SMAT_TALL_NOCP
+                if (subs & 1u) tc_cp_128x256b(tdst, pdesc);
+                if (subs & 2u) tc_cp_128x256b(tdst + 8, pdesc + 2);
+                if (subs & 4u) tc_cp_128x256b(tdst + 16, pdesc + 4);
+                if (subs & 8u) tc_cp_128x256b(tdst + 24, pdesc + 6);
+#endif
+                tc_commit(cp_done(pi % NPAIR));
+            }
+            // an odd number of steps leaves the last pair with one step: the copier whose turn the missing step would
+            // have been stands in for its arrival
+            if ((total & 1u) && total % NCW == j) mbar_arrive(cp_done((total >> 1) % NPAIR));
+        }
+        __syncwarp();
+    } else if (warp < NLW + NCW + NMW) {
+        // ------------------------------ MMA warp m: accumulator rows 2m, 2m + 1 ------------------------------
+        // The whole warp runs the loop converged and one elected lane issues.  Every operand of a tcgen05.mma must
+        // be a value the compiler knows to be warp-uniform (the instruction reads uniform registers): measured, the
+        // same loop run by a single lane on values loaded from shared memory issues an MMA every ~270 cycles instead
+        // of every ~80.  So the mask words, read from shared memory, are turned into ballots before anything is
+        // derived from them.
+        {
+            const uint32_t m = (uint32_t)__shfl_sync(0xffffffffu, warp - NLW - NCW, 0);
+            const bool leader = elect_one();
+            const uint32_t B_HI = (uint32_t)(smem_desc_k_sw32(0) >> 32);
+            const uint32_t b_lo0 = (uint32_t)smem_desc_k_sw32(base + OFF_BLK);
+            constexpr uint32_t IDESC16 = idesc_f16_f32(128, 16), IDESC32 = idesc_f16_f32(128, 32);
+            const uint32_t acc_m = tmem_base + TMEM_ACC + 2u * m * 16u;  // this warp's two accumulators
+            uint32_t st = 0, it = 0;
+            bool any = false;  // this warp issued an MMA in the current pair
+            SegGen<0> sg = make_gen();
+            Seg cs;
+            while (sg.next(cs)) {
+                wait_bar(acc_empty, (it & 1) ^ 1, abort_addr, status, 6);
+                tc_fence_after();
+                for (int k = cs.k0; k < cs.k1; k++, st++) {
+                    const uint32_t ps = st % TS_, bs = st % BS, pi = st >> 1;
+                    if ((st & 1u) == 0u) {
+                        wait_bar(cp_done(pi % NPAIR), (pi / NPAIR) & 1, abort_addr, status, 7);
+                        tc_fence_after();
+                    }
+                    // this warp's word of the step: bits 2s, 2s + 1 = its rows with a block in sub-column s, bits
+                    // [8 + 5s, 13 + 5s) = position of the first of them among the step's blocks.  (Measured: working the
+                    // four sub-columns out on four lanes and broadcasting the operands by shuffles was 20 % slower --
+                    // a shuffled value is not warp-uniform to the compiler.)
+                    const uint32_t xl = ld_shared_u32(base + OFF_META + bs * META_BYTES + m * 4u);
+                    const uint32_t x = __ballot_sync(0xffffffffu, (xl >> lane) & 1u);
+                    const uint32_t tpanel = tmem_base + TMEM_PANELS + ps * 32;
+                    const uint32_t b_lo = b_lo0 + bs * (BLK_SLOT_BYTES >> 4);
+                    uint32_t subs = (x | (x >> 1)) & 0x55u;  // bit 2s: sub-column s holds a block of this warp
+                    while (subs) {
+                        const uint32_t s2 = (uint32_t)__ffs((int)subs) - 1u;  // 2 * sub-column
+                        subs &= subs - 1u;
+                        const uint32_t own = (x >> s2) & 3u;
+                        const uint32_t q = (x >> (8u + (s2 >> 1) * 5u)) & 31u;
+                        const uint32_t d = acc_m + (own == 2u ? 16u : 0u);
+#ifndef SMAT_TALL_NOMMA
+                        if (leader) mma_f16_ts_lohi(d, tpanel + s2 * 4u, b_lo + q * 32u, B_HI, own == 3u ? IDESC32 : IDESC16, 1u);
+#endif
+                        any = true;
+                    }
+                    if (st & 1u) {
+                        if (leader) {
+                            if (any) tc_commit(step_done(pi % NPAIR));
+                            else mbar_arrive(step_done(pi % NPAIR));
+                        }
+                        any = false;
+                    }
+                }
+                if (leader) tc_commit(acc_full);
+                ++it;
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------ epilogue: tensor memory -> fp16 -> C ------------------------------
+        const int e = warp - (NLW + NCW + NMW);
+        const int quarter = warp & 3;  // a warp may only read tensor-memory lanes [32 * (warp % 4), +32)
+        const int grp = e >> 2;        // two groups of four warps; group g takes block-rows g, g + 2, ...
+        const int et = quarter * 32 + lane;
+        static_assert((NLW + NCW + NMW) % 4 == 0, "epilogue warp e must sit on lane quarter e % 4");
+        uint32_t it = 0;
+        SegGen<0> sg = make_gen();
+        Seg cs;
+        for (; sg.next(cs); ++it) {
+            const int g = cs.item / n_tiles, t = cs.item - g * n_tiles;
+            const int r0 = brow_begin + g * rg;
+            const int nrows = min(rg, brow_end - r0);
+            const int lo = (lane < nrows) ? __ldg(rowptr + r0 + lane) : 0;
+            const int hi = (lane < nrows) ? __ldg(rowptr + r0 + lane + 1) : 0;
+            const uint32_t nonempty = __ballot_sync(0xffffffffu, hi > lo);
+            const bool partial = cs.cut;
+            float* part_dst = fix_scratch + (size_t)cs.slot * (size_t)kFixSlotFloats;
+            if (lane == 0) wait_bar(acc_full, it & 1, abort_addr, status, 8);
+            __syncwarp();
+            tc_fence_after();
+            int last_r = -1;  // last block-row this warp's group handles
+            for (int r = grp; r < nrows; r += 2) last_r = r;
+            if (last_r < 0) {  // nothing to read for this group: hand the accumulators back at once
+                if (lane == 0) mbar_arrive(acc_empty);
+            }
+            for (int r = grp; r < nrows; r += 2) {
+                uint32_t v[16];
+                if ((nonempty >> r) & 1u) {
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + TMEM_ACC + (uint32_t)r * 16;
+                    tmem_ld_x16(taddr, v);
+                    tmem_ld_wait();
+                    tmem_zero_x16(taddr);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; i++) v[i] = 0u;
+                }
+                if (r == last_r) {
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_empty);
+                }
+                if (partial) {
+                    float* dd = part_dst + ((size_t)r * 16) * 128 + et;
+#pragma unroll
+                    for (int i = 0; i < 16; i++) dd[(size_t)i * 128] = __uint_as_float(v[i]);
+                    continue;
+                }
+                // lane pairs exchange halves: even lanes keep rows 0..7, odd lanes rows 8..15, each for the two adjacent
+                // columns (n & ~1, n | 1) -> one 4-byte store per row, 128 contiguous bytes per warp
+                const int n = t * 128 + et;
+                const bool odd = lane & 1;
+                __half* crow = C + ((size_t)(r0 - brow_begin + r) * 16 + (odd ? 8 : 0)) * ldc + (size_t)(n & ~1);
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const float keep = __uint_as_float(odd ? v[i + 8] : v[i]);
+                    const float send = __uint_as_float(odd ? v[i] : v[i + 8]);
+                    const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+                    const __half2 hh = odd ? __floats2half2_rn(recv, keep) : __floats2half2_rn(keep, recv);
+                    if (n < N) *reinterpret_cast<__half2*>(crow + (size_t)i * ldc) = hh;
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+#ifdef SMAT_PROFILE
+    if (threadIdx.x == 0) { atomicAdd(&g_wait_prof[15], (unsigned long long)(clock64() - t_kernel0)); atomicAdd(&g_wait_prof[47], 1ull); }
+#endif
+    if (ld_shared_u32(abort_addr)) {
+        // a wait ran out somewhere: give copies still in flight time to land before the CTA retires
+        for (int i = 0; i < 64; i++) __nanosleep(1000);
+    }
+    if (warp == NLW) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+}  // namespace
+
+int launch_spmm_tall(const PlanView& whole, const void* B, void* C, size_t N, cudaStream_t stream, const DeviceCtx* ctx_in,
+                     size_t ldc, size_t group_begin, size_t group_end) {
+    const DeviceCtx* ctx = ctx_in;
+    if (!ctx) {
+        DeviceCtx* c = nullptr;
+        if (int rc = get_device_ctx(&c)) return rc;
+        ctx = c;
+    }
+    if (ldc == 0) ldc = N;
+    if (!whole.tall || whole.rg > (size_t)kTallRows) return fail(SMAT_ERR_BAD_ARG, "not a tall plan");
+    if (group_end > whole.n_groups) group_end = whole.n_groups;
+    if (group_begin >= group_end) return SMAT_OK;
+    const PlanView plan = plan_group_range(whole, group_begin, group_end);
+    const size_t nb_rows = plan.brow_end - plan.brow_begin;
+    if (nb_rows == 0 || N == 0) return SMAT_OK;
+    if (plan.fix_scratch == nullptr || plan.winfo == nullptr) return fail(SMAT_ERR_BAD_ARG, "incomplete tall plan");
+    const size_t sms = (size_t)ctx->sm_count;
+    const uint32_t panel_rows = (uint32_t)(N < 128 ? N : 128);
+    CUtensorMap mapB;
+    if (int rc = encode_tensor_map_2d_f16(&mapB, B, plan.K, N, plan.K * 2, 64, panel_rows, 128, 0)) return rc;
+    const int n_tiles = (int)((N + 127) / 128);
+    const size_t n_items = plan.n_groups * (size_t)n_tiles;
+    if (n_items > (size_t)INT_MAX) return fail(SMAT_ERR_RANGE, "too many work items (%zu)", n_items);
+    size_t est_steps = plan.total_steps ? plan.total_steps / plan.n_groups : plan.K / 64;
+    const int parts = (int)tail_parts_for(n_items, sms, true, est_steps);
+    const int grid = (int)((parts > 1 || n_items > sms) ? sms : n_items);
+    const int n_full = (int)(n_items / (size_t)grid * (size_t)grid);
+    SMAT_CUDA_TRY(cudaFuncSetAttribute(spmm_bcsr_tall_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+    spmm_bcsr_tall_kernel<<<grid, kTallThreads, SMEM_BYTES, stream>>>(
+        mapB, reinterpret_cast<const uint8_t*>(plan.packed), reinterpret_cast<const uint4*>(plan.steps),
+        reinterpret_cast<const uint4*>(plan.winfo), plan.gsp, plan.rowptr,
+        reinterpret_cast<__half*>(C), ldc, (int)plan.brow_begin, (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles, (int)n_items, parts, panel_rows * 128u,
+        plan.fix_scratch, ctx->d_status);
+    count_launch();
+    SMAT_CUDA_TRY(cudaGetLastError());
+    if (parts == 1) return SMAT_OK;
+    return launch_sum_cut_items(false, (int)n_items - n_full, plan.fix_scratch, C, (int)plan.brow_begin, (int)plan.brow_end,
+                                (int)plan.rg, (int)N, n_tiles, n_full, parts, ldc, stream);
+}
+
+#ifdef SMAT_PROFILE
+extern "C" int smat_debug_tall_profile(unsigned long long* out64, int reset) {
+    if (out64) cudaMemcpyFromSymbol(out64, g_wait_prof, sizeof(g_wait_prof));
+    if (reset) { unsigned long long z[64] = {}; cudaMemcpyToSymbol(g_wait_prof, z, sizeof(z)); }
+    return 0;
+}
+#endif
+
+}  // namespace smat

@@ -61,11 +61,12 @@ int smat_spmm_bcsr_f16_rows(const void* bcsrValuesA, const int* bcsrRowPtrA, con
  * instead of freshly allocated scratch, so the call performs no allocation and no free.
  * No counterpart in the reference (its launcher needs no scratch, mmaCBT.cu:83-88).
  * Limits: nonzeroBlocks <= SMAT_STATIC_MAX_BLOCKS and M <= SMAT_STATIC_MAX_ROWS, else SMAT_ERR_RANGE;
- * the array (about 25 MB) stays resident on every GPU that loads the library.
+ * the array (17.5 MB) stays resident on every GPU that loads the library.
  * All calls on a device share the array: calls that overlap on the GPU race; calls on one stream do
  * not.  The first call on a device also looks up the array's device address -- make it before
- * starting a stream capture.  Bounded-wait time-outs are recorded in the array, not in the word
- * smat_device_status reads. */
+ * starting a stream capture.  Device-side errors (a bounded wait that ran out, row pointers that
+ * disagree with nonzeroBlocks) are recorded in a word of the array that stays set until
+ * smat_device_status reports and clears it. */
 #define SMAT_STATIC_MAX_BLOCKS 32768
 #define SMAT_STATIC_MAX_ROWS 1048576
 int smat_spmm_bcsr_f16_static(const void* bcsrValuesA, const int* bcsrRowPtrA, const int* bcsrColIdxA, const void* B,
@@ -111,14 +112,26 @@ int smat_plan_destroy(smat_plan* plan);
 /* Kernel variant used by every multiplication of this process: 0 = chosen per matrix (default),
  * 1 = both MMA operands from shared memory (two accumulator buffers, epilogue overlapped),
  * 2 = B panels copied to tensor memory and read from there (one accumulator buffer),
- * 3 = work items 256 columns of C wide: two MMAs per block, one accumulator buffer (default for N >= 256).
+ * 3 = work items 256 columns of C wide: two MMAs per block, one accumulator buffer (default for N >= 256),
+ * 4 = plans created from now on use work items of up to 24 block-rows and the kernel that reads the B panels
+ *     from tensor memory (affects smat_plan_create, not plans that exist).
  * Meant for benchmarks and tests; no counterpart in the reference. */
 int smat_spmm_set_variant(int variant);
 
 /* Synchronises `stream` and reports whether any kernel launched by this library on the current
- * device recorded a device-side error (a bounded wait that ran out).  Clears the device status word.
+ * device recorded a device-side error: a bounded wait that ran out (SMAT_ERR_DEVICE_WAIT), or BCSR
+ * arrays found inconsistent while a plan was built -- row pointers that are not monotone or exceed
+ * nonzeroBlocks, a block column outside the matrix or out of order (SMAT_ERR_RANGE; such input gets
+ * an empty or partial plan instead of an out-of-bounds write).  Clears the device status words (the
+ * allocating entry points' and the static entry point's).
  * The reference never checks its launches (src/cuda_hgemm/src/mma/mmaCBT.cu:87). */
 int smat_device_status(void* stream);
+
+/* Self-test of the error path above: launches a one-thread kernel that waits, with the SpMM kernels' own bounded
+ * wait and a limit of about 0.2 ms, on a barrier that nothing completes.  The kernel ends by itself with the device
+ * status word set (site code 90); the next smat_device_status on the device returns SMAT_ERR_DEVICE_WAIT and clears
+ * it.  Nothing faults and the context stays usable.  No counterpart in the reference. */
+int smat_selftest_wait_timeout(void* stream);
 
 /* Number of this library's kernels launched so far by the calling process (all devices). */
 long long smat_launch_count(void);

@@ -21,9 +21,13 @@ u16p = np.ctypeslib.ndpointer(dtype=np.uint16, flags="C_CONTIGUOUS")
 f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
 
 
-def build(ref_root="/root/reference"):
-    """Compile the oracle; also the reference-backed library/programs when the reference tree exists."""
+def build(ref_root=None):
+    """Compile the oracle; also the reference-backed libraries/programs when a reference tree is named (argument, or
+    the SMAT_REFERENCE environment variable) and exists."""
     subprocess.check_call(["make", "-s", "-C", _HERE, "all"])
+    ref_root = ref_root or os.environ.get("SMAT_REFERENCE")
+    if not ref_root:
+        return
     if os.path.isdir(os.path.join(ref_root, "preprocess", "src", "general")):
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REF={ref_root}"])
     if os.path.isdir(os.path.join(ref_root, "src", "cuda_hgemm", "src", "mma")):
@@ -84,6 +88,9 @@ def ref():
         L.ref_fixed_size_grouping.argtypes = [C.c_long, i64p, C.c_long, i64p]
         L.ref_vbr_multiply.argtypes = [C.c_long, C.c_long, C.c_long, C.c_long, i64p, i64p, f32p, C.c_long, C.c_long,
                                        f32p, C.c_int, f32p]
+        if hasattr(L, "ref_vbr_from_csr"):
+            L.ref_vbr_from_csr.restype = C.c_long
+            L.ref_vbr_from_csr.argtypes = [C.c_long, C.c_long, i32p, i32p, f32p, C.c_long, C.c_long, C.c_long, i64p, i64p, f32p]
         _REF = L
     return _REF
 
@@ -103,6 +110,10 @@ def ref_gpu():
         L.ref_gpu_launch.argtypes = [C.c_int, vp, vp, vp, vp, vp, sz, sz, sz, sz, vp, vp, C.c_int, C.c_int]
         L.cusparse_csr_spmm_f16.restype = C.c_float
         L.cusparse_csr_spmm_f16.argtypes = [vp, vp, vp, sz, vp, vp, sz, sz, sz, C.c_int, C.c_int]
+        if hasattr(L, "ref_sparse_matrix_load"):
+            psz, pip, pup = C.POINTER(sz), C.POINTER(C.POINTER(C.c_int)), C.POINTER(C.POINTER(C.c_uint16))
+            L.ref_sparse_matrix_load.argtypes = [C.c_char_p, C.c_int, C.c_int, psz, psz, psz, psz, pip, pip, pup, pip, pip, pup]
+            L.ref_free.argtypes = [vp]
         _REF_GPU = L
     return _REF_GPU
 
@@ -190,3 +201,65 @@ def reorder_rows(rowptr, cols, tau=0.5, col_block=16, row_block=16):
     p = np.zeros(max(rows, 1), np.int64)
     lib().orc_reorder_rows(rows, _i64(rowptr), _i64(cols), tau, col_block, row_block, g, p)
     return g[:rows], p[:rows]
+
+
+def ref_bcsr_via_vbr(M, K, rowptr, colidx, vals):
+    """16x16 blocking of a CSR matrix by the UNMODIFIED reference code VBR::fill_from_CSR_inplace (oracle/_ref), restated
+    in the BCSR layout of the GPU path: (bcsr_rowptr int32, bcsr_colidx int32 = element columns, bcsr_vals float16
+    row-major blocks).  The reference stores a block column-major with its rows in the order of its own (unstable)
+    argsort of the grouping i // 16; that order is obtained from the reference's get_permutation and undone here.
+    Costs O(nnz * K / 16) in the reference (a std::count per entry): small matrices only."""
+    R = ref()
+    if R is None or not hasattr(R, "ref_vbr_from_csr"):
+        raise RuntimeError("oracle/_ref/libsmat_ref.so with ref_vbr_from_csr is not built")
+    rowptr = np.ascontiguousarray(rowptr, dtype=np.int32)
+    colidx = np.ascontiguousarray(colidx, dtype=np.int32)
+    vals32 = np.ascontiguousarray(np.asarray(vals, dtype=np.float16).astype(np.float32))
+    if colidx.size == 0:
+        colidx, vals32 = np.zeros(1, np.int32), np.zeros(1, np.float32)
+    Mb = M // 16
+    max_blocks = int(min(len(colidx), Mb * (K // 16))) + 1
+    nzc = np.zeros(max(Mb, 1), np.int64)
+    jab = np.zeros(max_blocks, np.int64)
+    mab = np.zeros(max_blocks * 256, np.float32)
+    nb = R.ref_vbr_from_csr(M, K, rowptr, colidx, vals32, 16, 16, max_blocks, nzc, jab, mab)
+    if nb < 0:
+        raise RuntimeError("ref_vbr_from_csr: block bound too small")
+    perm = np.zeros(M, np.int64)
+    R.ref_get_permutation(M, np.ascontiguousarray(np.arange(M, dtype=np.int64) // 16), perm)
+    brp = np.zeros(Mb + 1, np.int32)
+    brp[1:] = np.cumsum(nzc[:Mb])
+    bci = (jab[:nb] * 16).astype(np.int32)
+    blocks = mab[: nb * 256].reshape(nb, 16, 16)  # [block][column][position of the row in the reference's order]
+    out = np.zeros((nb, 16, 16), np.float32)       # [block][row][column]
+    brow_of_block = np.repeat(np.arange(Mb), nzc[:Mb])
+    for pos in range(16):
+        rows_here = perm[brow_of_block * 16 + pos] - brow_of_block * 16  # the original row (within the block) at this position
+        out[np.arange(nb), rows_here, :] = blocks[:, :, pos]
+    return brp, bci, out.reshape(-1).astype(np.float16)
+
+
+def ref_sparse_matrix(path, host_only=True, export_magicube=False):
+    """Runs the reference's own reader and blocked-format builder, unmodified: mmio_allinone
+    (src/cuda_hgemm/src/common/mmio_highlevel.h:619-786) + SparseMatrix::csrToBcsr (matrix.h:376-502).  host_only: just
+    those two host steps (no GPU needed); else the class's full constructor, which also uploads (needs a GPU).
+    Returns (M, K, csr_rowptr, csr_colidx, csr_vals f16, bcsr_rowptr, bcsr_colidx, bcsr_vals f16)."""
+    G = ref_gpu()
+    if G is None or not hasattr(G, "ref_sparse_matrix_load"):
+        raise RuntimeError("oracle/_ref/libsmat_ref_gpu.so with ref_sparse_matrix_load is not built")
+    sz = C.c_size_t
+    M, K, nnz, nnzb = sz(), sz(), sz(), sz()
+    ip, up = C.POINTER(C.c_int), C.POINTER(C.c_uint16)
+    crp, cci, cv, brp, bci, bv = ip(), ip(), up(), ip(), ip(), up()
+    rc = G.ref_sparse_matrix_load(path.encode(), 1 if host_only else 0, 1 if export_magicube else 0, C.byref(M), C.byref(K), C.byref(nnz), C.byref(nnzb),
+                                  C.byref(crp), C.byref(cci), C.byref(cv), C.byref(brp), C.byref(bci), C.byref(bv))
+    if rc != 0:
+        raise RuntimeError(f"ref_sparse_matrix_load -> {rc}")
+
+    def take(ptr, n, dtype):
+        a = np.ctypeslib.as_array(ptr, shape=(max(n, 1),))[:n].copy()
+        G.ref_free(C.cast(ptr, C.c_void_p))
+        return a.view(dtype) if dtype is not None else a
+    out = (M.value, K.value, take(crp, M.value + 1, None), take(cci, nnz.value, None), take(cv, nnz.value, np.float16),
+           take(brp, M.value // 16 + 1, None), take(bci, nnzb.value, None), take(bv, nnzb.value * 256, np.float16))
+    return out

@@ -85,3 +85,58 @@ float cusparse_csr_spmm_f16(int* rowptr, int* colidx, void* vals, size_t nnz, vo
 }
 
 }  // extern "C"
+
+// ---- the reference's own reader + blocked-format builder, run unmodified -------------------------------------------
+// SparseMatrix(name, file) (src/cuda_hgemm/src/common/matrix.h:145-202) reads the .mtx file with mmio_allinone
+// (mmio_highlevel.h:619-786), converts CSR -> BCSR with csrToBcsr (matrix.h:376-502) and uploads both.  Its arrays are
+// private and have no host getters, so the class is compiled here with its access specifiers opened; nothing else changes.
+#define private public
+#include "matrix.h"
+#undef private
+
+#include <stdlib.h>
+#include <string.h>
+
+extern "C" {
+
+// Builds a SparseMatrix from `mtx_path` and hands back malloc'ed copies of its host arrays (free them with
+// ref_free).  host_only == 0: through the class's constructor, which also uploads everything (needs a GPU).
+// host_only != 0: the two host steps the constructor performs, readCsr() and csrToBcsr(), on a zero-filled object
+// whose constructor is not run -- neither step touches CUDA, so this works on a machine without a GPU.
+// With export_magicube != 0 it also calls SparseMatrix::outputCsr (matrix.h:321-348), which writes
+// ./data/magicube_cop20k_A.mtx relative to the current directory.  The object is leaked on purpose: its destructor frees
+// only part of what the constructor allocates and the process is short-lived.
+int ref_sparse_matrix_load(const char* mtx_path, int host_only, int export_magicube, size_t* M, size_t* K, size_t* nnz,
+                           size_t* nnzb, int** csr_rowptr, int** csr_colidx, unsigned short** csr_vals, int** bcsr_rowptr,
+                           int** bcsr_colidx, unsigned short** bcsr_vals) {
+    SparseMatrix* sm;
+    if (host_only) {
+        sm = static_cast<SparseMatrix*>(calloc(1, sizeof(SparseMatrix)));
+        sm->filename = const_cast<char*>(mtx_path);
+        sm->readCsr();
+        sm->csrToBcsr();
+    } else {
+        sm = new SparseMatrix("A", const_cast<char*>(mtx_path));
+    }
+    if (export_magicube) sm->outputCsr();
+    *M = sm->m_row;
+    *K = sm->m_col;
+    *nnz = sm->nnz;
+    *nnzb = sm->nonzeroBlocks;
+    auto dup = [](const void* src, size_t bytes) {
+        void* p = malloc(bytes ? bytes : 1);
+        memcpy(p, src, bytes);
+        return p;
+    };
+    *csr_rowptr = (int*)dup(sm->csrRowPtr_host, (sm->m_row + 1) * sizeof(int));
+    *csr_colidx = (int*)dup(sm->csrColIdx_host, sm->nnz * sizeof(int));
+    *csr_vals = (unsigned short*)dup(sm->csrVal_host, sm->nnz * sizeof(half));
+    *bcsr_rowptr = (int*)dup(sm->bcsrRowPtr_host, (sm->m_row / 16 + 1) * sizeof(int));
+    *bcsr_colidx = (int*)dup(sm->bcsrColIdx_host, sm->nonzeroBlocks * sizeof(int));
+    *bcsr_vals = (unsigned short*)dup(sm->bcsrVal_host, sm->nonzeroBlocks * 256 * sizeof(half));
+    return 0;
+}
+
+void ref_free(void* p) { free(p); }
+
+}  // extern "C"

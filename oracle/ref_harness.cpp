@@ -12,6 +12,7 @@
 //   get_permutation / get_fixed_size_grouping     preprocess/src/general/utilities.cpp:8-20, 45-54
 //   CSR(ifstream) = read_from_edgelist            preprocess/src/general/csr.cpp:166-290
 //   VBR::multiply                                 preprocess/src/general/vbr.cpp:323-372
+//   VBR::fill_from_CSR_inplace (fixed-size blocks) preprocess/src/general/vbr.cpp:118-237
 
 #include <cstdint>
 #include <cstring>
@@ -97,6 +98,51 @@ int ref_vbr_multiply(long rows, long cols, long block_rows, long block_col_size,
     memcpy(v.mab, mab, sizeof(DataT) * (size_t)v.nztot);
     v.multiply(B, B_cols, C);
     return 0;
+}
+
+// Blocks a CSR matrix (32-bit row pointers and columns, fp32 values, rows and cols as given) with the reference's
+// VBR::fill_from_CSR_inplace(cmat, row_block, col_block, force_fixed_size = true) and copies out the structure
+// (nzcount per block-row, block-column index per block) and the block values (column-major inside a block, rows of a
+// block in the order of the reference's own get_permutation of the grouping i / row_block).  Returns the number of
+// blocks, or -1 when max_blocks is too small.  The CSR object is laid out by hand: the reference's struct has no
+// constructor from arrays, and its destructor must not run on memory it did not allocate.
+long ref_vbr_from_csr(long rows, long cols, const int* rowptr, const int* colidx, const float* vals, long row_block,
+                      long col_block, long max_blocks, long* nzcount_out, long* jab_out, float* mab_out) {
+    CSR* c = static_cast<CSR*>(::operator new(sizeof(CSR)));
+    c->rows = rows;
+    c->cols = cols;
+    c->pattern_only = false;
+    c->nzcount = new intT[rows];
+    c->ja = new intT*[rows];
+    c->ma = new DataT*[rows];
+    for (long r = 0; r < rows; r++) {
+        const long n = rowptr[r + 1] - rowptr[r];
+        c->nzcount[r] = n;
+        c->ja[r] = new intT[n > 0 ? n : 1];
+        c->ma[r] = new DataT[n > 0 ? n : 1];
+        for (long j = 0; j < n; j++) {
+            c->ja[r][j] = colidx[rowptr[r] + j];
+            c->ma[r][j] = vals[rowptr[r] + j];
+        }
+    }
+    VBR v;
+    v.fill_from_CSR_inplace(*c, (intT)row_block, (intT)col_block, true);
+    long nb = 0;
+    for (long ib = 0; ib < v.block_rows; ib++) nb += v.nzcount[ib];
+    long rc = nb;
+    if (nb > max_blocks) {
+        rc = -1;
+    } else {
+        for (long ib = 0; ib < v.block_rows; ib++) nzcount_out[ib] = v.nzcount[ib];
+        for (long i = 0; i < nb; i++) jab_out[i] = v.jab[i];
+        memcpy(mab_out, v.mab, sizeof(DataT) * (size_t)v.nztot);
+    }
+    for (long r = 0; r < rows; r++) { delete[] c->ja[r]; delete[] c->ma[r]; }
+    delete[] c->nzcount;
+    delete[] c->ja;
+    delete[] c->ma;
+    ::operator delete(c);
+    return rc;
 }
 
 }  // extern "C"

@@ -40,6 +40,7 @@ def lib():
     L.smat_plan_destroy.argtypes = [vp]
     L.smat_spmm_set_variant.argtypes = [C.c_int]
     L.smat_device_status.argtypes = [vp]
+    L.smat_selftest_wait_timeout.argtypes = [vp]
     L.smat_launch_count.restype = C.c_longlong
     L.smat_bcsr_count.argtypes = [ip, ip, sz, sz, sz, ip, C.POINTER(sz), vp]
     L.smat_bcsr_fill.argtypes = [ip, ip, vp, sz, sz, sz, ip, ip, vp, sz, vp]

@@ -70,7 +70,7 @@ bcsr_count_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx
 }
 
 // In-place inclusive scan of data[0..n) by a single CTA (n = Mb + 1 is small next to nnz).
-__global__ void __launch_bounds__(1024) scan_inplace_kernel(int* data, int n, unsigned long long* total_out) {
+__global__ void __launch_bounds__(1024) scan_inplace_kernel(int* data, int n) {
     __shared__ int warp_tot[32];
     __shared__ int carry_s;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -103,7 +103,6 @@ __global__ void __launch_bounds__(1024) scan_inplace_kernel(int* data, int n, un
         if (threadIdx.x == 1023) carry_s = v;
         __syncthreads();
     }
-    if (threadIdx.x == 0) *total_out = (unsigned long long)(unsigned)carry_s;
 }
 
 __global__ void __launch_bounds__(kBuildThreads)
@@ -203,7 +202,6 @@ int smat_bcsr_count(const int* csr_rowptr, const int* csr_colidx, size_t M, size
     int words = 1;
     if (int rc = bitmap_words(K, &words, 2)) return rc;
     const int Mb = (int)(M / 16);
-    unsigned long long* d_total = reinterpret_cast<unsigned long long*>(ctx->d_status + 2);
     if (Mb > 0) {
         const size_t smem = (size_t)words * 4;
         SMAT_CUDA_TRY(cudaFuncSetAttribute(bcsr_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -214,11 +212,12 @@ int smat_bcsr_count(const int* csr_rowptr, const int* csr_colidx, size_t M, size
     } else {
         SMAT_CUDA_TRY(cudaMemsetAsync(bcsr_rowptr, 0, sizeof(int), stream));
     }
-    scan_inplace_kernel<<<1, 1024, 0, stream>>>(bcsr_rowptr, Mb + 1, d_total);
+    scan_inplace_kernel<<<1, 1024, 0, stream>>>(bcsr_rowptr, Mb + 1);
     count_launch();
     SMAT_CUDA_TRY(cudaGetLastError());
-    unsigned long long total = 0;
-    SMAT_CUDA_TRY(cudaMemcpyAsync(&total, d_total, sizeof(total), cudaMemcpyDeviceToHost, stream));
+    // the total is the last entry of the scanned array (the caller's own buffer: concurrent calls do not meet)
+    int total = 0;
+    SMAT_CUDA_TRY(cudaMemcpyAsync(&total, bcsr_rowptr + Mb, sizeof(total), cudaMemcpyDeviceToHost, stream));
     SMAT_CUDA_TRY(cudaStreamSynchronize(stream));
     *nnzb_out = (size_t)total;
     return SMAT_OK;

@@ -8,6 +8,7 @@
 #include <mutex>
 
 #include "smat_internal.h"
+#include "spmm_sched.cuh"
 
 namespace smat {
 
@@ -17,6 +18,20 @@ std::atomic<long long> g_launches{0};
 std::mutex g_ctx_mutex;
 constexpr int kMaxDevices = 64;
 DeviceCtx g_ctx[kMaxDevices];
+}  // namespace
+
+namespace {
+// One thread waits, with the kernels' bounded wait and a short limit, on a barrier that nothing ever completes.
+__global__ void wait_selftest_kernel(int* status, long long limit) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(ptx::smem_u32(&bar), 1);
+        abort_flag = 0;
+        ptx::fence_barrier_init();
+        wait_bar(ptx::smem_u32(&bar), 0, ptx::smem_u32(&abort_flag), status, 90, limit);
+    }
+}
 }  // namespace
 
 int fail(int code, const char* fmt, ...) {
@@ -41,12 +56,18 @@ int get_device_ctx(DeviceCtx** out) {
         if (prop.major != 10)
             return fail(SMAT_ERR_CUDA, "device %d is sm_%d%d; this library holds sm_100a code only", dev, prop.major,
                         prop.minor);
-        // keep stream-ordered scratch (the per-call plans of smat_spmm_bcsr_f16) cached in the pool
-        cudaMemPool_t pool;
-        if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
-            unsigned long long keep = ~0ull;
-            cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
-        }
+        // Stream-ordered scratch (the per-call plans of smat_spmm_bcsr_f16) comes from a pool of the library's own,
+        // which keeps what it has been given; the process's default pool is left as the application configured it.
+        cudaMemPoolProps props = {};
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = dev;
+        cudaMemPool_t pool = nullptr;
+        SMAT_CUDA_TRY(cudaMemPoolCreate(&pool, &props));
+        unsigned long long keep = ~0ull;
+        SMAT_CUDA_TRY(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+        c.pool = pool;
         int* st = nullptr;
         SMAT_CUDA_TRY(cudaMalloc(&st, 64));
         SMAT_CUDA_TRY(cudaMemset(st, 0, 64));
@@ -136,7 +157,7 @@ static int spmm_transient_plan(const void* vals, const int* rowptr, const int* c
     if (nnzb == 0) return launch_spmm(v, B, C, N, stream);
     void* buf = nullptr;
     const size_t plan_bytes = (sz.gsp_bytes + sz.steps_bytes + sz.blk_bytes + sz.packed_bytes + 255) / 256 * 256;
-    SMAT_CUDA_TRY(cudaMallocAsync(&buf, plan_bytes + fix_scratch_bytes(ctx->sm_count), stream));
+    SMAT_CUDA_TRY(cudaMallocFromPoolAsync(&buf, plan_bytes + fix_scratch_bytes(ctx->sm_count), ctx->pool, stream));
     char* b = static_cast<char*>(buf);
     v.fix_scratch = reinterpret_cast<float*>(b + plan_bytes);
     v.gsp = reinterpret_cast<int*>(b);
@@ -188,10 +209,25 @@ int smat_device_status(void* stream) {
     SMAT_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
     int st = 0;
     SMAT_CUDA_TRY(cudaMemcpy(&st, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
-    if (st != 0) {
-        SMAT_CUDA_TRY(cudaMemset(ctx->d_status, 0, sizeof(int)));
-        return fail(SMAT_ERR_DEVICE_WAIT, "a kernel gave up a bounded wait (site code %d); its output is invalid", st);
-    }
+    if (st != 0) SMAT_CUDA_TRY(cudaMemset(ctx->d_status, 0, sizeof(int)));
+    int st_static = 0;  // the word of the allocation-free entry point lives in its fixed array
+    if (int rc = static_status_take(&st_static)) return rc;
+    if (st == 0) st = st_static;
+    if (st >= 100)
+        return fail(SMAT_ERR_RANGE, "the BCSR arrays are inconsistent (device check %d: %s); the output is invalid", st,
+                    st == kStatusBadRowptr ? "bcsrRowPtr disagrees with nonzeroBlocks"
+                                           : "a block column is out of range or a block-row's columns are not ascending");
+    if (st != 0) return fail(SMAT_ERR_DEVICE_WAIT, "a kernel gave up a bounded wait (site code %d); its output is invalid", st);
+    return SMAT_OK;
+}
+
+int smat_selftest_wait_timeout(void* stream) {
+    clear_error();
+    DeviceCtx* ctx = nullptr;
+    if (int rc = get_device_ctx(&ctx)) return rc;
+    wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ctx->d_status, 400000LL);  // about 0.2 ms
+    count_launch();
+    SMAT_CUDA_TRY(cudaGetLastError());
     return SMAT_OK;
 }
 

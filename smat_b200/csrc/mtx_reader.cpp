@@ -14,6 +14,7 @@
 #include <string.h>
 
 #include <string>
+#include <new>
 #include <vector>
 
 #include "smat_internal.h"
@@ -60,9 +61,20 @@ int smat_read_mtx(const char* filename, size_t* M, size_t* K, size_t* nnz, int* 
     fseek(f, 0, SEEK_END);
     const long fsize = ftell(f);
     fseek(f, 0, SEEK_SET);
-    std::vector<char> text((size_t)fsize + 1);
+    if (fsize < 0) {
+        fclose(f);
+        return fail(SMAT_ERR_IO, "%s: cannot determine the file size", filename);
+    }
+    std::vector<char> text;
+    try {
+        text.resize((size_t)fsize + 1);
+    } catch (const std::bad_alloc&) {
+        fclose(f);
+        return fail(SMAT_ERR_NOMEM, "%s: %ld bytes do not fit in host memory", filename, fsize);
+    }
     const size_t got = fread(text.data(), 1, (size_t)fsize, f);
     fclose(f);
+    if (got != (size_t)fsize) return fail(SMAT_ERR_IO, "%s: short read (%zu of %ld bytes)", filename, got, fsize);
     text[got] = 0;
     char* cur = text.data();
     char* const end = text.data() + got;
@@ -101,6 +113,9 @@ int smat_read_mtx(const char* filename, size_t* M, size_t* K, size_t* nnz, int* 
         cur = eol + 1;
     }
     if (rows < 0 || cols < 0 || entries < 0) return fail(SMAT_ERR_IO, "%s: negative size", filename);
+    // mirroring writes entry (a, b) again as (b, a): only a square matrix has room for it (the reference reads past its
+    // arrays here, mmio_highlevel.h:714-758)
+    if (mirror && rows != cols) return fail(SMAT_ERR_IO, "%s: a symmetric or hermitian matrix must be square (%ld x %ld)", filename, rows, cols);
     const long rows_p = (rows + 15) / 16 * 16, cols_p = (cols + 15) / 16 * 16;
 
     std::vector<int> er((size_t)entries), ec((size_t)entries);

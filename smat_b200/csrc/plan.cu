@@ -35,22 +35,36 @@ constexpr int kWindow = 16384;  // block-columns per pass: 64 KB of masks + 64 K
 
 // Fills masks[0..kWindow) for block-columns [w0, w0 + kWindow) of the group; cursor[] (one per warp,
 // kept by lane 0 semantics via registers) walks each row once over all windows.
+// A block column below the window start (columns not ascending, or negative) or beyond the matrix is not marked; the
+// status word then tells the host that the structure is inconsistent.
 template <int THREADS = kPlanThreads>
-__device__ __forceinline__ void mark_window(const int* __restrict__ colidx, int& cur, int end, int w0, uint32_t* masks,
-                                            int warp, int lane) {
+__device__ __forceinline__ void mark_window(const int* __restrict__ colidx, int& cur, int end, int w0, int Kb, uint32_t* masks,
+                                            int warp, int lane, int* status) {
     for (int i = threadIdx.x; i < kWindow; i += THREADS) masks[i] = 0u;
     __syncthreads();
     // every lane keeps the same `cur`; lanes stride over the row until the window ends
     for (;;) {
         const int j = cur + lane;
         int cb = (j < end) ? (__ldg(colidx + j) >> 4) : INT_MAX;
+        if (j < end && cb >= Kb) {  // beyond the last block-column: consume it without marking
+            if (status) atomicCAS(status, 0, kStatusBadColumns);
+            cb = w0 - 1;
+        }
         const bool in = cb < w0 + kWindow;
-        if (in) atomicOr(&masks[cb - w0], 1u << warp);
+        if (in && cb >= w0) atomicOr(&masks[cb - w0], 1u << warp);
+        else if (in && status) atomicCAS(status, 0, kStatusBadColumns);
         const uint32_t b = __ballot_sync(0xffffffffu, in);
         cur += __popc(b);
         if (b != 0xffffffffu) break;
     }
     __syncthreads();
+}
+
+// True when row pointers [brow_begin, brow_end] cannot belong to a matrix of nnzb blocks (checked by every thread on the two
+// ends; a dip in between shows up as a block-row whose end lies before its start and contributes nothing).
+__device__ __forceinline__ bool range_is_bad(const int* __restrict__ rowptr, int brow_begin, int brow_end, int nnzb) {
+    const int first = __ldg(rowptr + brow_begin), last = __ldg(rowptr + brow_end);
+    return first < 0 || last < first || last > nnzb;
 }
 
 // Block-wide exclusive scan of one int per thread; returns the exclusive prefix, *total gets the sum.
@@ -84,25 +98,35 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* total, int* sh) 
 template <bool FILL>
 __global__ void __launch_bounds__(kPlanThreads)
 plan_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx, int brow_begin, int brow_end, int rg, int CAP, int Kb,
-            int n_groups, int* __restrict__ gsp, uint4* __restrict__ steps, int* __restrict__ blk) {
+            int n_groups, int* __restrict__ gsp, uint4* __restrict__ steps, int* __restrict__ blk, int nnzb, int* status) {
     extern __shared__ uint32_t sm[];
     uint32_t* masks = sm;                                 // [kWindow] row mask per block-column
     int* blk_pre = reinterpret_cast<int*>(sm + kWindow);  // [kWindow] exclusive block number (FILL only)
     __shared__ int scan_sh[64];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // The buffers of the plan are sized from the caller's block count: a range of row pointers that is not monotone or
+    // holds more blocks than that would be written past their end.  Such a range gets an empty plan and a status code.
+    if (range_is_bad(rowptr, brow_begin, brow_end, nnzb)) {
+        if (!FILL) {
+            for (int g = blockIdx.x * blockDim.x + threadIdx.x; g <= n_groups; g += gridDim.x * blockDim.x) gsp[g] = 0;
+            if (blockIdx.x == 0 && threadIdx.x == 0 && status) atomicCAS(status, 0, kStatusBadRowptr);
+        }
+        return;
+    }
     for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
         const int row = brow_begin + g * rg + warp;  // warps >= rg hold no row
         const bool have = warp < rg && row < brow_end;
-        const int beg = have ? __ldg(rowptr + row) : 0;
-        const int end = have ? __ldg(rowptr + row + 1) : 0;
-        const int gfirst = __ldg(rowptr + brow_begin + g * rg);  // first block of the group
+        const int r_lo = __ldg(rowptr + brow_begin), r_hi = __ldg(rowptr + brow_end);
+        const int beg = have ? min(max(__ldg(rowptr + row), r_lo), r_hi) : 0;  // clamped: a dip inside the range reads nothing outside it
+        const int end = have ? min(max(__ldg(rowptr + row + 1), beg), r_hi) : 0;
+        const int gfirst = min(max(__ldg(rowptr + brow_begin + g * rg), r_lo), r_hi);  // first block of the group
         const int rfirst = __ldg(rowptr + brow_begin);           // first block of the whole range
         int cur = beg;
         int steps_done = 0, blocks_done = 0;
         const int gs = FILL ? __ldg(gsp + g) : 0;
         for (int w0 = 0; w0 < Kb; w0 += kWindow) {
             const int cur_before = cur;
-            mark_window(colidx, cur, end, w0, masks, warp, lane);
+            mark_window(colidx, cur, end, w0, Kb, masks, warp, lane, status);
             // per-thread chunk of the window: PER consecutive block-columns = PER / 4 quads
             constexpr int PER = kWindow / kPlanThreads;
             static_assert(PER % 4 == 0, "a thread owns whole quads");
@@ -146,7 +170,9 @@ plan_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx, int 
                 __syncthreads();
                 // scatter: block j of this warp's row goes to its (column, row) rank inside the group
                 for (int j = cur_before + lane; j < cur; j += 32) {
-                    const int cb = (__ldg(colidx + j) >> 4) - w0;
+                    const int cbx = __ldg(colidx + j) >> 4;
+                    const int cb = cbx - w0;
+                    if (cb < 0 || cb >= kWindow || cbx >= Kb) continue;  // not marked above (status set there)
                     blk[gfirst + blk_pre[cb] + __popc(masks[cb] & ((1u << warp) - 1u))] = j;
                 }
                 blocks_done += tot_b;
@@ -229,25 +255,36 @@ static_assert(kTallRows == 24 && kTallBlocksPerStep <= 32, "the per-warp step wo
 template <bool FILL>
 __global__ void __launch_bounds__(kTallPlanThreads)
 plan_tall_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx, int brow_begin, int brow_end, int rg, int CAP, int Kb,
-                 int n_groups, int* __restrict__ gsp, uint4* __restrict__ steps, uint4* __restrict__ winfo, int* __restrict__ blk) {
+                 int n_groups, int* __restrict__ gsp, uint4* __restrict__ steps, uint4* __restrict__ winfo, int* __restrict__ blk,
+                 int nnzb, int* status) {
     extern __shared__ uint32_t sm[];
     uint32_t* masks = sm;                                 // [kWindow] row mask per block-column
     int* blk_pre = reinterpret_cast<int*>(sm + kWindow);  // [kWindow] exclusive block number (FILL only)
     __shared__ int scan_sh[64];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // The buffers of the plan are sized from the caller's block count: a range of row pointers that is not monotone or
+    // holds more blocks than that would be written past their end.  Such a range gets an empty plan and a status code.
+    if (range_is_bad(rowptr, brow_begin, brow_end, nnzb)) {
+        if (!FILL) {
+            for (int g = blockIdx.x * blockDim.x + threadIdx.x; g <= n_groups; g += gridDim.x * blockDim.x) gsp[g] = 0;
+            if (blockIdx.x == 0 && threadIdx.x == 0 && status) atomicCAS(status, 0, kStatusBadRowptr);
+        }
+        return;
+    }
     for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
         const int row = brow_begin + g * rg + warp;
         const bool have = warp < rg && row < brow_end;
-        const int beg = have ? __ldg(rowptr + row) : 0;
-        const int end = have ? __ldg(rowptr + row + 1) : 0;
-        const int gfirst = __ldg(rowptr + brow_begin + g * rg);
+        const int r_lo = __ldg(rowptr + brow_begin), r_hi = __ldg(rowptr + brow_end);
+        const int beg = have ? min(max(__ldg(rowptr + row), r_lo), r_hi) : 0;
+        const int end = have ? min(max(__ldg(rowptr + row + 1), beg), r_hi) : 0;
+        const int gfirst = min(max(__ldg(rowptr + brow_begin + g * rg), r_lo), r_hi);
         const int rfirst = __ldg(rowptr + brow_begin);
         int cur = beg;
         int steps_done = 0, blocks_done = 0;
         const int gs = FILL ? __ldg(gsp + g) : 0;
         for (int w0 = 0; w0 < Kb; w0 += kWindow) {
             const int cur_before = cur;
-            mark_window<kTallPlanThreads>(colidx, cur, end, w0, masks, warp, lane);
+            mark_window<kTallPlanThreads>(colidx, cur, end, w0, Kb, masks, warp, lane, status);
             constexpr int PER = kWindow / kTallPlanThreads;
             static_assert(PER % 4 == 0, "a thread owns whole quads");
             const int i0 = threadIdx.x * PER;
@@ -319,7 +356,9 @@ plan_tall_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx,
                 }
                 __syncthreads();
                 for (int j = cur_before + lane; j < cur; j += 32) {
-                    const int cb = (__ldg(colidx + j) >> 4) - w0;
+                    const int cbx = __ldg(colidx + j) >> 4;
+                    const int cb = cbx - w0;
+                    if (cb < 0 || cb >= kWindow || cbx >= Kb) continue;  // not marked above (status set there)
                     blk[gfirst + blk_pre[cb] + __popc(masks[cb] & ((1u << warp) - 1u))] = j;
                 }
                 blocks_done += tot_b;
@@ -440,7 +479,8 @@ int plan_count_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb
     const size_t smem_count = (size_t)kWindow * 4;
     SMAT_CUDA_TRY(cudaFuncSetAttribute(plan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_count));
     plan_kernel<false><<<grid, kPlanThreads, smem_count, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, (int)rg, (int)cap,
-                                                                  (int)(K / 16), (int)n_groups, gsp, nullptr, nullptr);
+                                                                  (int)(K / 16), (int)n_groups, gsp, nullptr, nullptr, (int)nnzb,
+                                                                  ctx->d_status);
     count_launch();
     plan_scan_kernel<<<1, 1024, 0, stream>>>(gsp, (int)n_groups + 1);
     count_launch();
@@ -459,7 +499,7 @@ int plan_fill_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb,
     SMAT_CUDA_TRY(cudaFuncSetAttribute(plan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fill));
     plan_kernel<true><<<grid, kPlanThreads, smem_fill, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, (int)rg, (int)cap,
                                                                  (int)(K / 16), (int)n_groups, const_cast<int*>(gsp),
-                                                                 reinterpret_cast<uint4*>(steps), blk);
+                                                                 reinterpret_cast<uint4*>(steps), blk, (int)nnzb, ctx->d_status);
     count_launch();
     SMAT_CUDA_TRY(cudaGetLastError());
     return SMAT_OK;
@@ -481,7 +521,7 @@ int plan_count_tall_async(const int* rowptr, const int* colidx, size_t K, size_t
     SMAT_CUDA_TRY(cudaFuncSetAttribute(plan_tall_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_count));
     plan_tall_kernel<false><<<grid, kTallPlanThreads, smem_count, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, (int)rg,
                                                                            kTallBlocksPerStep, (int)(K / 16), (int)n_groups, gsp, nullptr,
-                                                                           nullptr, nullptr);
+                                                                           nullptr, nullptr, (int)nnzb, ctx->d_status);
     count_launch();
     plan_scan_kernel<<<1, 1024, 0, stream>>>(gsp, (int)n_groups + 1);
     count_launch();
@@ -501,7 +541,7 @@ int plan_fill_tall_async(const int* rowptr, const int* colidx, size_t K, size_t 
     plan_tall_kernel<true><<<grid, kTallPlanThreads, smem_fill, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, (int)rg,
                                                                          kTallBlocksPerStep, (int)(K / 16), (int)n_groups,
                                                                          const_cast<int*>(gsp), reinterpret_cast<uint4*>(steps),
-                                                                         reinterpret_cast<uint4*>(winfo), blk);
+                                                                         reinterpret_cast<uint4*>(winfo), blk, (int)nnzb, ctx->d_status);
     count_launch();
     SMAT_CUDA_TRY(cudaGetLastError());
     return SMAT_OK;
@@ -541,6 +581,15 @@ struct smat_plan {
     cudaEvent_t ev_start = nullptr;
     std::vector<cudaEvent_t> ev_in, ev_done, ev_out;
 };
+
+// A plan's memory and tuning belong to the device it was created on.
+static int check_plan_device(const smat_plan* plan) {
+    int dev = -1;
+    SMAT_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev != plan->device)
+        return fail(SMAT_ERR_BAD_ARG, "the plan belongs to device %d but device %d is current", plan->device, dev);
+    return SMAT_OK;
+}
 
 extern "C" {
 
@@ -748,6 +797,7 @@ int smat_plan_set_values(smat_plan* plan, const void* bcsrValuesA, void* stream)
     clear_error();
     if (!plan || (plan->v.nnzb && !bcsrValuesA)) return fail(SMAT_ERR_BAD_ARG, "NULL argument");
     if ((uintptr_t)bcsrValuesA & 15) return fail(SMAT_ERR_BAD_ARG, "bcsrValuesA must be 16-byte aligned");
+    if (int rc = check_plan_device(plan)) return rc;
     if (plan->v.tall)
         return pack_values_tall_async(plan->v.rowptr, bcsrValuesA, plan->v.gsp, plan->v.steps, plan->v.blk,
                                       const_cast<void*>(plan->v.packed), plan->v.brow_begin, plan->v.brow_end, plan->v.rg,
@@ -765,6 +815,7 @@ int smat_plan_spmm(const smat_plan* plan, const void* B, void* C, size_t N, void
         return fail(SMAT_ERR_BAD_ARG, "B or C is NULL");
     if (((uintptr_t)B | (uintptr_t)C) & 15) return fail(SMAT_ERR_BAD_ARG, "B and C must be 16-byte aligned");
     if (N >= ((size_t)1 << 31)) return fail(SMAT_ERR_RANGE, "N beyond 2^31");
+    if (int rc = check_plan_device(plan)) return rc;
     return launch_spmm(plan->v, B, C, N, (cudaStream_t)stream);
 }
 
@@ -776,6 +827,7 @@ int smat_plan_spmm_host(smat_plan* plan, const void* B_host, void* C_host, size_
     const size_t rows = (plan->v.brow_end - plan->v.brow_begin) * 16, K = plan->v.K;
     if (rows == 0 || N == 0) return SMAT_OK;
     if (!B_host || !C_host) return fail(SMAT_ERR_BAD_ARG, "B_host or C_host is NULL");
+    if (int rc = check_plan_device(plan)) return rc;
     cudaStream_t s = (cudaStream_t)stream;
     // B comes in by column chunks as wide as the kernel's widest work item (rows of the [N][K] array: contiguous);
     // every chunk but the last is multiplied for all block-rows as soon as it has arrived; the last chunk is

@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the SpMM kernels use: mbarrier, TMA tiled loads
-// (cp.async.bulk.tensor, never with cluster multicast), cp.async, tcgen05 (alloc / mma / commit / ld /
+// (cp.async.bulk.tensor, never with cluster multicast), bulk copies, tcgen05 (alloc / mma / commit / ld /
 // fences) and the shared-memory / instruction descriptors tcgen05.mma consumes.
 //
 // These replace the sm_80 wrappers of the reference (src/cuda_hgemm/src/common/ptx.h:3-38: ldmatrix,
@@ -96,25 +96,6 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 
-// ---- cp.async (4-byte), per-thread groups -----------------------------------------------------
-__device__ __forceinline__ void cp_async_4(uint32_t dst_smem, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst_smem), "l"(src) : "memory");
-}
-// 16-byte copy that bypasses L1; completion can be attached to an mbarrier (below).
-__device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
-}
-// The mbarrier receives one arrival (counted against its expected-arrival count) once every cp.async
-// issued so far by this thread has completed.
-__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
-    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
 // ---- tcgen05: tensor memory allocation -----------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
@@ -130,18 +111,9 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 // ---- tcgen05.mma, fp16 inputs, fp32 accumulate in tensor memory ---------------------------------
-// D[tmem] (+)= A[smem desc] * B[smem desc];  accumulate == 0 overwrites D.
-__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                           uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Same, with each 64-bit descriptor given as (low word, high word): the low word carries the start address
-// and is the only part that changes between MMAs, so callers keep the high words in registers and update
-// the low words with 32-bit adds.
+// D[tmem] (+)= A[smem desc] * B[smem desc];  accumulate == 0 overwrites D.  Each 64-bit descriptor is given as
+// (low word, high word): the low word carries the start address and is the only part that changes between MMAs,
+// so callers keep the high words in registers and update the low words with 32-bit adds.
 __device__ __forceinline__ void mma_f16_ss_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
                                                 uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -152,6 +124,7 @@ __device__ __forceinline__ void mma_f16_ss_lohi(uint32_t d_tmem, uint32_t a_lo, 
         "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Same with the A operand resident in tensor memory (128 lanes x K/2 32-bit columns).
 __device__ __forceinline__ void mma_f16_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
                                                 uint32_t accumulate) {
     asm volatile(
@@ -160,15 +133,6 @@ __device__ __forceinline__ void mma_f16_ts_lohi(uint32_t d_tmem, uint32_t a_tmem
         "setp.ne.b32 p, %5, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
         "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Same with the A operand resident in tensor memory (128 lanes x K/2 32-bit columns).
-__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                           uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // Arrive on an mbarrier once every tcgen05 operation issued so far by this thread has completed.
@@ -195,17 +159,6 @@ __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&v)[16]) {
           "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr)
         : "memory");
-}
-__device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t (&v)[8]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                 : "r"(taddr)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint32_t (&v)[8]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
-                 "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
-                 : "memory");
 }
 // Writes zero to 16 consecutive 32-bit columns of the calling thread's lane.
 __device__ __forceinline__ void tmem_zero_x16(uint32_t taddr) {

@@ -149,6 +149,47 @@ struct Engine {
 
 using namespace smat;
 
+
+#ifndef __GLIBCXX__
+#error "reorder.cpp reproduces a libstdc++-specific effect of the reference (see trim_count); build it with libstdc++"
+#endif
+
+namespace {
+using CandSet = std::set<std::pair<float, long>>;
+
+// The reference trims its candidate set with `it = end(); advance(it, k); erase(it, end())`
+// (preprocess/src/general/blocking.cpp:504-510): it steps PAST end().  With libstdc++'s red-black tree, incrementing
+// from the header node goes to the rightmost node's subtree and cycles through the header, the rightmost node and (when
+// it has one) its left child, so the walk lands 0, 1 or 2 nodes before end() depending on k and on whether the rightmost
+// node has a left child.  This returns how many of the largest candidates that erase removes; it reads the tree's
+// node links, which is what the self-test below guards.
+inline int64_t trim_count(const CandSet& best, int64_t k) {
+    auto hdr = best.end()._M_node;
+    const bool has_left = hdr->_M_right->_M_left != nullptr;
+    const int64_t cyc = has_left ? 3 : 2;
+    const int64_t pos = k % cyc;
+    return pos ? cyc - pos : 0;
+}
+
+// First-call check that the model above is what this standard library does: for small sets, really walk k steps past
+// end() the way the reference does and compare the distance to end() with trim_count.  A library with another tree
+// layout fails here, loudly, instead of producing a different grouping.
+bool trim_model_holds() {
+    for (int n = 1; n <= 9; n++) {
+        CandSet s;
+        for (int i = 0; i < n; i++) s.insert({(float)((i * 7) % 11), (long)i});
+        for (int64_t k = 0; k <= 7; k++) {
+            auto it = s.end();
+            for (int64_t i = 0; i < k; i++) ++it;  // the reference's std::advance(it, k) from end()
+            int64_t dist = 0;
+            for (auto e = it; e != s.end() && dist <= n; ++e) dist++;
+            if (dist != trim_count(s, k)) return false;
+        }
+    }
+    return true;
+}
+}  // namespace
+
 extern "C" {
 
 float smat_jaccard_group(const int64_t* rowA, size_t sizeA, int64_t gA, const int64_t* rowB, size_t sizeB, int64_t gB,
@@ -177,6 +218,10 @@ int smat_reorder_rows(size_t rows_, const int64_t* rowptr, const int32_t* cols, 
         return fail(SMAT_ERR_BAD_ARG, "bad argument");
     const int64_t rows = (int64_t)rows_;
     if (rows == 0) return SMAT_OK;
+    static const bool model_ok = trim_model_holds();
+    if (!model_ok)
+        return fail(SMAT_ERR_RANGE, "this C++ standard library's std::set does not behave like the one the reference's "
+                                    "candidate trim was characterised with; groupings would differ from the reference");
     if (rowptr[rows] > 0 && !cols) return fail(SMAT_ERR_BAD_ARG, "cols is NULL");
     for (int64_t r = 0; r < rows; r++)
         for (int64_t j = rowptr[r] + 1; j < rowptr[r + 1]; j++)
@@ -295,11 +340,7 @@ int smat_reorder_rows(size_t rows_, const int64_t* rowptr, const int32_t* cols, 
                     best.insert({dist, (long)j});
                     const int64_t k = maxg - (int64_t)merged.size();
                     if ((int64_t)best.size() > k) {
-                        auto hdr = best.end()._M_node;
-                        const bool has_left = hdr->_M_right->_M_left != nullptr;
-                        const int64_t cyc = has_left ? 3 : 2;
-                        const int64_t pos = k % cyc;
-                        const int64_t n_erase = pos ? cyc - pos : 0;
+                        const int64_t n_erase = trim_count(best, k);
                         if (n_erase > 0) best.erase(std::prev(best.end(), n_erase), best.end());
                     }
                 }

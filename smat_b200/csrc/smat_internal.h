@@ -31,10 +31,20 @@ struct DeviceCtx {
     int device = -1;
     int sm_count = 0;
     int* d_status = nullptr;
+    cudaMemPool_t pool = nullptr;  // the library's own pool for stream-ordered scratch (null for the static entry point)
 };
 int get_device_ctx(DeviceCtx** out);
 
 void count_launch();
+
+// Status word of the allocation-free entry point's fixed array (spmm_static.cu); see there.
+int static_status_take(int* out);
+
+// Device status codes (the word kernels set): 1..99 a bounded wait ran out at that wait site; 100.. the input
+// structure is inconsistent (101: row pointers disagree with the number of blocks, 102: a block column is out of range
+// or the columns of a block-row are not ascending).
+constexpr int kStatusBadRowptr = 101;
+constexpr int kStatusBadColumns = 102;
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against libcuda).
 int encode_tensor_map_2d_f16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_pitch_bytes,

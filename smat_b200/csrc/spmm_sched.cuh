@@ -33,7 +33,8 @@ static __device__ unsigned long long g_wait_prof[64];
 #endif
 
 // Bounded mbarrier wait.  After the first time-out anywhere in the CTA every wait returns at once.
-__device__ __forceinline__ void wait_bar(uint32_t bar, uint32_t parity, uint32_t abort_addr, int* status, int code) {
+__device__ __forceinline__ void wait_bar(uint32_t bar, uint32_t parity, uint32_t abort_addr, int* status, int code,
+                                         long long limit = WAIT_LIMIT) {
     if (mbar_try_wait(bar, parity)) return;
     if (ld_shared_u32(abort_addr)) return;
     const long long t0 = clock64();
@@ -43,7 +44,7 @@ __device__ __forceinline__ void wait_bar(uint32_t bar, uint32_t parity, uint32_t
     // suspended waits: the warp sleeps in hardware until the phase completes or ~2 us pass
     while (!mbar_try_wait_suspend(bar, parity, 2000u)) {
         if (ld_shared_u32(abort_addr)) return;
-        if (clock64() - t0 > WAIT_LIMIT) {
+        if (clock64() - t0 > limit) {
             st_shared_u32(abort_addr, 1);
             atomicCAS(status, 0, code);
             return;

@@ -69,8 +69,11 @@ constexpr int NL = 4;                  // loader warps
 #ifndef SMAT_TMA_EPILOGUE
 #define SMAT_TMA_EPILOGUE 1
 #endif
+// L2 prefetches of the panel and the blocks a few steps ahead of their copies.  Off: measured on the final kernel they
+// change nothing where the copies are not the limit (uniform, block-sparse layer, power-law) and cost a third of the
+// time where they are (dense clusters: 0.335 -> 0.230 ms), because a prefetch occupies the copy engine like a copy.
 #ifndef SMAT_L2_PREFETCH
-#define SMAT_L2_PREFETCH 1
+#define SMAT_L2_PREFETCH 0
 #endif
 constexpr int NM = kPlanOwners;        // MMA-issuing warps; warp m owns accumulators [m * RG / NM, (m + 1) * RG / NM)
 constexpr int NC = 4;                  // panel-copier warps (used by the tensor-memory-operand variant)
@@ -341,9 +344,8 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_const
                     h_next += NL;
                 }
             };
-            // HBM latency is hidden in L2 rather than in shared memory: the panel and the blocks of the
-            // step U/2 positions ahead (of this warp; NL * U/2 steps ahead overall) are prefetched into
-            // L2, so the copies that fill a stage find their data there.
+            // Optional (SMAT_L2_PREFETCH, off by default): the panel and the blocks of the step U/2 positions ahead
+            // (of this warp; NL * U/2 steps ahead overall) are prefetched into L2.
             auto prefetch = [&](const StepRec& r) {
 #if SMAT_L2_PREFETCH
                 if (r.live) {

@@ -9,16 +9,20 @@
 // plan in a fixed array that is part of the library image, so the call itself allocates nothing
 // and frees nothing.
 //
-// Cost and limits: the array occupies kStaticScratchBytes (about 25 MB) on every GPU that loads
+// Cost and limits: the array occupies kStaticScratchBytes (17.5 MB) on every GPU that loads
 // the library, until the process exits, and therefore bounds the problem: at most
 // SMAT_STATIC_MAX_BLOCKS nonzero blocks and SMAT_STATIC_MAX_ROWS rows.  Larger inputs are refused
 // with SMAT_ERR_RANGE; use the plan API for them.
 //
 // Sharing: all calls on a device use the same array.  It keeps whatever the previous call left; the
-// plan build overwrites every entry the multiplication reads, and the status word is cleared on the
-// stream at the start of each call, so nothing stale is consumed -- but two calls that overlap on
-// the GPU (different streams, or different host threads without external ordering) race on it.
-// Calls on one stream are safe back to back.
+// plan build overwrites every entry the multiplication reads, so nothing stale is consumed -- but two
+// calls that overlap on the GPU (different streams, or different host threads without external
+// ordering) race on it.  Calls on one stream are safe back to back.
+//
+// Errors found on the device (a bounded wait that ran out, a row pointer that disagrees with
+// nonzeroBlocks) are recorded in a status word inside the array.  The word starts at zero when the
+// library is loaded and stays set until smat_device_status reads it, which reports and clears it
+// together with the word of the allocating entry points; a later static call never clears it.
 //
 // First call per device: looks up the device address of the array (cudaGetSymbolAddress, with that
 // device current) and the SM count.  No allocation happens, but it is a set-up step: make it before
@@ -32,7 +36,7 @@ namespace {
 
 constexpr size_t kMaxBlocks = 32768;          // SMAT_STATIC_MAX_BLOCKS
 constexpr size_t kMaxRows = 1048576;          // SMAT_STATIC_MAX_ROWS
-constexpr size_t kMaxGroups = kMaxRows / 16 / 4;  // the smallest group height is 4 block-rows
+constexpr size_t kMaxGroups = kMaxRows / 16 / 4;  // the smallest group height (SMAT_ROWS_PER_GROUP override) is 4 block-rows
 constexpr size_t kGspBytes = ((kMaxGroups + 2) * sizeof(int) + 255) / 256 * 256;  // prefix of step counts + the largest count
 constexpr size_t kStepsBytes = kMaxBlocks * 16;   // a group never has more steps than blocks
 constexpr size_t kBlkBytes = kMaxBlocks * sizeof(int);
@@ -77,6 +81,25 @@ int static_device(StaticDev** out) {
 }
 
 }  // namespace
+
+// Reads (and, when set, clears) the status word of the fixed array on the current device; 0 when the static entry
+// point has not been used on it.  The caller has synchronised the stream.  Allocates nothing.
+int static_status_take(int* out) {
+    *out = 0;
+    int dev = -1;
+    SMAT_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return SMAT_OK;
+    int* word = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        if (!g_dev[dev].ready) return SMAT_OK;
+        word = g_dev[dev].ctx.d_status;
+    }
+    SMAT_CUDA_TRY(cudaMemcpy(out, word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*out != 0) SMAT_CUDA_TRY(cudaMemset(word, 0, sizeof(int)));
+    return SMAT_OK;
+}
+
 }  // namespace smat
 
 using namespace smat;
@@ -115,8 +138,6 @@ extern "C" int smat_spmm_bcsr_f16_static(const void* vals, const int* rowptr, co
     v.steps = steps;
     v.blk = blk;
     v.packed = packed;
-    // the status word shares the array with earlier calls: start from zero
-    SMAT_CUDA_TRY(cudaMemsetAsync(d->ctx.d_status, 0, sizeof(int), stream));
     if (int rc = plan_count_async(rowptr, colidx, K, nnzb, 0, Mb, rg, gsp, stream, &d->ctx)) return rc;
     if (int rc = plan_fill_async(rowptr, colidx, K, nnzb, 0, Mb, rg, gsp, steps, blk, stream, &d->ctx)) return rc;
     if (int rc = pack_values_async(rowptr, vals, gsp, steps, blk, packed, 0, Mb, rg, nnzb, stream, &d->ctx)) return rc;

@@ -150,7 +150,7 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
             bool have = sg.next(cs);
             uint32_t h_st0 = 0, h_next = (uint32_t)j;
 #ifndef SMAT_TALL_PF
-#define SMAT_TALL_PF 2
+#define SMAT_TALL_PF 0
 #endif
             constexpr int U = 4;  // step records in flight per loader (their descriptors are requested U positions ahead)
             constexpr int PF = SMAT_TALL_PF;  // records ahead (of this loader) whose data is prefetched into L2; 0 = none

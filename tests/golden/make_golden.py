@@ -14,7 +14,10 @@ Outputs:
   similarities.json     stdout figures of TEST_similarities for -b 1, 3, 4, 16
   reorder_<name>.npz    CSR pattern + reference grouping (.g file of Matrix_Blocking) + permutation
                         (from its *_reordered.el) for -a 5 -F 1 runs
-  multiply_<name>.npz   BCSR arrays + B + fp32 C of the reference's VBR::multiply
+  multiply_<name>.npz   BCSR arrays (blocked by the reference's VBR::fill_from_CSR_inplace) + B + fp32 C of the
+                        reference's VBR::multiply
+  reader_<name>.npz     a Matrix-Market text + the CSR and BCSR arrays that the reference's mmio_allinone and
+                        SparseMatrix::csrToBcsr make of it (needs `make -C oracle ref_gpu REF=...` too)
   formats/*             outputs of the reference's Python glue (src/reorder.py: mtx2el, el2mtx, row pass,
                         transpose, column pass) on a small pattern matrix
 """
@@ -125,7 +128,8 @@ def multiply_fixtures():
     R = oracle.ref()
     for name, sc, N in (("band", 0.03125, 24), ("uniform", 0.00390625, 40), ("llm", 0.03125, 16)):
         p = gen.make_config(name, scale=sc)
-        brp, bci, bv = oracle.csr_to_bcsr(p.M, p.K, p.rowptr, p.colidx, p.vals)
+        # the blocked arrays come from the reference's own blocking code (VBR::fill_from_CSR_inplace), not from the oracle
+        brp, bci, bv = oracle.ref_bcsr_via_vbr(p.M, p.K, p.rowptr, p.colidx, p.vals)
         rng = np.random.default_rng(7)
         B_nk = rng.standard_normal((N, p.K)).astype(np.float16)
         nb = len(bci)
@@ -144,12 +148,68 @@ def multiply_fixtures():
         print("multiply", name, p.M, p.K, N, "nnzb", nb)
 
 
+def reader_cases():
+    """(name, Matrix-Market text) of the reader / blocked-format fixtures: every banner variant the reader accepts,
+    shapes that are not multiples of 16, duplicate entries, unsorted columns, explicit zeros, and each benchmark
+    configuration at a small scale."""
+    rng = np.random.default_rng(31)
+    cases = []
+
+    def coo_text(banner, M, K, rows, cols, vals=None):
+        lines = [f"%%MatrixMarket matrix coordinate {banner}", "% fixture", f"{M} {K} {len(rows)}"]
+        for i in range(len(rows)):
+            lines.append(f"{rows[i] + 1} {cols[i] + 1}" + ("" if vals is None else f" {vals[i]}"))
+        return "\n".join(lines) + "\n"
+
+    M, K = 253, 251
+    keys = np.unique(rng.integers(0, M * K, 3000))
+    rng.shuffle(keys)  # file order is kept inside the rows: columns end up unsorted
+    cases.append(("general_real_shuffled", coo_text("real general", M, K, keys // K, keys % K,
+                                                    [repr(float(v)) for v in rng.standard_normal(keys.size)])))
+    n = 100
+    keys = np.unique(rng.integers(0, n * n, 600))
+    r, c = keys // n, keys % n
+    low = r >= c
+    cases.append(("symmetric_real", coo_text("real symmetric", n, n, r[low], c[low],
+                                             [repr(float(v)) for v in rng.standard_normal(int(low.sum()))])))
+    keys = np.unique(rng.integers(0, 70 * 90, 400))
+    cases.append(("pattern_general", coo_text("pattern general", 70, 90, keys // 90, keys % 90)))
+    keys = rng.integers(0, 40 * 48, 500)  # with repeats: duplicate (row, col) entries, the last one wins in a block
+    cases.append(("integer_duplicates", coo_text("integer general", 40, 48, keys // 48, keys % 48,
+                                                 [str(int(v)) for v in rng.integers(-9, 10, keys.size)])))
+    keys = np.unique(rng.integers(0, 64 * 64, 300))
+    vals = rng.standard_normal(keys.size)
+    vals[::3] = 0.0  # stored zeros still make their block "nonzero"
+    cases.append(("explicit_zeros", coo_text("real general", 64, 64, keys // 64, keys % 64, [repr(float(v)) for v in vals])))
+    cases.append(("single_entry_last_corner", coo_text("real general", 33, 17, [32], [16], ["-2.5"])))
+    for name, sc in (("band", 0.03), ("uniform", 0.01), ("powerlaw", 0.004), ("clustered", 0.0005), ("llm", 0.012)):
+        p = gen.make_config(name, scale=sc)
+        rows = np.repeat(np.arange(p.M), np.diff(p.rowptr))
+        cases.append((f"cfg_{name}", coo_text("real general", p.M, p.K, rows, p.colidx,
+                                              [repr(float(v)) for v in p.vals.astype(np.float32)])))
+    return cases
+
+
+def reader_fixtures():
+    """Outputs of the reference's own mmio_allinone + SparseMatrix::csrToBcsr (compiled unmodified into
+    oracle/_ref/libsmat_ref_gpu.so; both are host code and run without a GPU) on reader_cases()."""
+    for name, text in reader_cases():
+        with tempfile.TemporaryDirectory() as d:
+            path = os.path.join(d, name + ".mtx")
+            with open(path, "w") as f:
+                f.write(text)
+            M, K, crp, cci, cv, brp, bci, bv = oracle.ref_sparse_matrix(path, host_only=True)
+        np.savez_compressed(os.path.join(HERE, f"reader_{name}.npz"), mtx=np.frombuffer(text.encode(), np.uint8), M=M, K=K,
+                            csr_rowptr=crp, csr_colidx=cci, csr_vals=cv, bcsr_rowptr=brp, bcsr_colidx=bci, bcsr_vals=bv)
+        print("reader", name, M, K, "nnz", len(cci), "nnzb", len(bci))
+
+
 def formats_fixtures():
     """Runs the reference's own Python glue (src/reorder.py, imported from the reference tree) and its
     Matrix_Blocking program on a small pattern matrix: text converters, row pass, column pass."""
     import shutil
     import types
-    ref_src = os.path.join(os.environ.get("SMAT_REFERENCE", "/root/reference"), "src")
+    ref_src = os.path.join(os.environ["SMAT_REFERENCE"], "src")  # root of the reference tree
     sys.modules.setdefault("utils", types.ModuleType("utils"))  # plotting helpers, not needed (matplotlib absent)
     sys.path.insert(0, ref_src)
     import reorder as ref_reorder  # the reference module
@@ -191,4 +251,5 @@ if __name__ == "__main__":
     similarities()
     reorder_fixtures()
     multiply_fixtures()
+    reader_fixtures()
     formats_fixtures()

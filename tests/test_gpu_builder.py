@@ -1,5 +1,9 @@
-"""Device-side BCSR builder (through the C ABI) against the oracle's restatement of csrToBcsr:
-row pointers, column indices and values must be bit-identical."""
+"""Device-side BCSR builder (through the C ABI) against the reference's csrToBcsr -- fixtures made by running the
+unmodified reference, the reference itself where it was built, and the oracle's restatement for the larger cases: row
+pointers, column indices and values must be bit-identical."""
+import glob
+import os
+
 import numpy as np
 import pytest
 
@@ -24,6 +28,35 @@ def test_builder_matches_oracle_on_configs(name, scale):
     p = gen.make_config(name, scale=scale)
     A = S.SparseMatrix.from_csr(p.M, p.K, p.rowptr, p.colidx, p.vals)
     _same(A, *oracle.csr_to_bcsr(p.M, p.K, p.rowptr, p.colidx, p.vals))
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "reader_*.npz"))),
+                         ids=lambda p: os.path.basename(p)[7:-4])
+def test_file_to_bcsr_matches_reference_run(path, tmp_path):
+    """The product's whole front end -- smat_read_mtx, upload, smat_bcsr_count / smat_bcsr_fill on the device -- against
+    what the reference's own SparseMatrix(file) (mmio_allinone + csrToBcsr) produced for the same Matrix-Market text."""
+    z = np.load(path)
+    mtx = str(tmp_path / "m.mtx")
+    with open(mtx, "wb") as f:
+        f.write(z["mtx"].tobytes())
+    A = S.SparseMatrix.from_file(mtx)
+    assert (A.M, A.K) == (int(z["M"]), int(z["K"]))
+    _same(A, z["bcsr_rowptr"], z["bcsr_colidx"], z["bcsr_vals"])
+
+
+def test_file_to_bcsr_matches_live_reference_constructor(tmp_path):
+    """Where the reference's SparseMatrix was compiled for this GPU (oracle/_ref/libsmat_ref_gpu.so): run its real
+    constructor -- reader, csrToBcsr, uploads -- on a fresh file and compare the product's device-built arrays with it."""
+    G = oracle.ref_gpu()
+    if G is None or not hasattr(G, "ref_sparse_matrix_load"):
+        pytest.skip("oracle/_ref/libsmat_ref_gpu.so is not built here")
+    p = gen.make_config("uniform", scale=0.02)
+    path = str(tmp_path / "u.mtx")
+    gen.write_mtx(path, p.M, p.K, p.rowptr, p.colidx, p.vals)
+    M, K, crp, cci, cv, brp, bci, bv = oracle.ref_sparse_matrix(path, host_only=False)
+    A = S.SparseMatrix.from_file(path)
+    assert (A.M, A.K) == (M, K)
+    _same(A, brp, bci, bv)
 
 
 def test_builder_unsorted_columns_duplicates_and_explicit_zeros():

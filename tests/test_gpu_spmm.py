@@ -46,7 +46,7 @@ def _run(brp, bci, bv, B_nk, M, N, K, variant="call"):
     A = S.SparseMatrix.from_bcsr(M, K, brp, bci, bv)
     B = S.Matrix.from_host(B_nk)
     C = S.Matrix(M, N, fill=float("nan"))
-    kernel = {"smem": 1, "tmem": 2, "wide": 3}.get(variant, 0)  # force one kernel variant, else automatic choice
+    kernel = {"smem": 1, "tmem": 2, "wide": 3, "tall": 4}.get(variant, 0)  # force one kernel variant, else automatic choice
     S.set_variant(kernel)
     try:
         if variant == "call":
@@ -70,7 +70,7 @@ def _problem(name, scale, N=None):
     return p, brp, bci, bv
 
 
-@pytest.mark.parametrize("variant", ["call", "plan", "smem", "tmem", "wide"])
+@pytest.mark.parametrize("variant", ["call", "plan", "smem", "tmem", "wide", "tall"])
 @pytest.mark.parametrize("name,scale,N", [("band", 1.0, 64), ("band", 0.1, 8), ("uniform", 0.02, 256),
                                           ("uniform", 0.01, 136), ("powerlaw", 0.01, 128), ("clustered", 0.004, 512),
                                           ("llm", 0.0625, 256), ("llm", 0.04, 24)])
@@ -147,13 +147,13 @@ def test_ragged_rows_and_long_block_row():
     bci = np.concatenate([np.sort(rng.choice(Kb, c, replace=False)) for c in counts]).astype(np.int32) * 16
     bv = rng.standard_normal(brp[-1] * 256).astype(np.float16)
     B = rng.standard_normal((N, Kb * 16)).astype(np.float16)
-    for variant in ("call", "smem", "tmem", "wide"):
+    for variant in ("call", "smem", "tmem", "wide", "tall"):
         C = _run(brp, bci, bv, B, Mb * 16, N, Kb * 16, variant)
         Cref, Cabs = _oracle_c(bv, brp, bci, B, Mb * 16, N, Kb * 16)
         assert _rel_err(C, Cref, Cabs) <= TOL
 
 
-@pytest.mark.parametrize("variant", ["call", "smem", "tmem", "wide"])
+@pytest.mark.parametrize("variant", ["call", "smem", "tmem", "wide", "tall"])
 @pytest.mark.parametrize("Mb,Kb,N,fill", [(3, 4096, 128, 0.5), (16, 2048, 264, 0.3), (40, 1024, 512, 0.15), (1, 9000, 8, 1.0)])
 def test_items_cut_across_ctas(Mb, Kb, N, fill, variant):
     """Few block-rows, many block-columns: far fewer work items than SMs, so every item is computed in parts by
@@ -300,3 +300,65 @@ def test_full_size_sampled_block_rows(name):
     for br in empty[:4]:
         assert torch.all(C.data[br * 16:br * 16 + 16] == 0)
     assert not torch.isnan(C.data).any()
+
+
+def test_tall_plan_dense_and_odd_shapes():
+    """The tall kernel (24-row work items, panels read from tensor memory) on shapes that exercise its plan: quads
+    with more blocks than a step holds (dense block-rows: steps are cut and the panel is fetched again), a group
+    height that does not divide the matrix, an odd number of steps per CTA, N below and beyond one tile."""
+    rng = np.random.default_rng(21)
+    for Mb, Kb, N, fill in [(50, 96, 200, 1.0), (24, 333, 136, 0.6), (7, 5, 8, 1.0), (100, 64, 520, 0.2)]:
+        mask = rng.random((Mb, Kb)) < fill
+        mask[:, 0] |= ~mask.any(axis=1)
+        counts = mask.sum(axis=1)
+        brp = np.zeros(Mb + 1, np.int32)
+        brp[1:] = np.cumsum(counts)
+        bci = (np.nonzero(mask)[1] * 16).astype(np.int32)
+        bv = (rng.standard_normal(brp[-1] * 256) * 0.25).astype(np.float16)
+        B = rng.standard_normal((N, Kb * 16)).astype(np.float16)
+        C = _run(brp, bci, bv, B, Mb * 16, N, Kb * 16, "tall")
+        Cref, Cabs = _oracle_c(bv, brp, bci, B, Mb * 16, N, Kb * 16)
+        assert _rel_err(C, Cref, Cabs) <= TOL
+        again = _run(brp, bci, bv, B, Mb * 16, N, Kb * 16, "tall")
+        assert np.array_equal(C.view(np.uint16), again.view(np.uint16))
+
+
+def test_bounded_wait_timeout_is_reported():
+    """The error path of the kernels' bounded waits, driven from the host: a one-thread kernel waits on a barrier that
+    nothing completes, gives up after ~0.2 ms and sets the device status word; smat_device_status reports
+    SMAT_ERR_DEVICE_WAIT once, clears the word, and the context keeps working."""
+    torch = _torch()
+    L = S.lib()
+    assert L.smat_device_status(None) == 0
+    assert L.smat_selftest_wait_timeout(torch.cuda.current_stream().cuda_stream) == 0
+    rc = L.smat_device_status(torch.cuda.current_stream().cuda_stream)
+    assert rc == -3 and b"site code 90" in L.smat_last_error_string()
+    assert L.smat_device_status(None) == 0
+    p, brp, bci, bv = _problem("band", 0.1, 8)
+    C = _run(brp, bci, bv, p.B_nk, p.M, 8, p.K)
+    Cref, Cabs = _oracle_c(bv, brp, bci, p.B_nk, p.M, 8, p.K)
+    assert _rel_err(C, Cref, Cabs) <= TOL
+
+
+def test_inconsistent_row_pointers_are_reported_not_written_past():
+    """nonzeroBlocks smaller than what the row pointers claim: the plan buffers are sized from nonzeroBlocks, so the
+    plan kernels refuse the range (empty plan, status word) and smat_device_status returns SMAT_ERR_RANGE."""
+    torch = _torch()
+    p, brp, bci, bv = _problem("band", 0.1, 8)
+    A = S.SparseMatrix.from_bcsr(p.M, p.K, brp, bci, bv)
+    B = S.Matrix.from_host(p.B_nk)
+    C = S.Matrix(p.M, 8, fill=0.0)
+    L = S.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    for entry in ("plain", "static"):
+        lie = A.nnzb - 5  # fewer blocks than bcsrRowPtr[M / 16]
+        if entry == "plain":
+            rc = L.smat_spmm_bcsr_f16(A.getBcsrValues(), A.getBcsrRowPtr(), A.getBcsrColIdx(), B.data.data_ptr(), C.data.data_ptr(),
+                                      p.M, 8, p.K, lie, None, None, stream)
+        else:
+            rc = L.smat_spmm_bcsr_f16_static(A.getBcsrValues(), A.getBcsrRowPtr(), A.getBcsrColIdx(), B.data.data_ptr(),
+                                             C.data.data_ptr(), p.M, 8, p.K, lie, stream)
+        assert rc == 0
+        rc = L.smat_device_status(stream)
+        assert rc == -6 and b"bcsrRowPtr" in L.smat_last_error_string(), entry
+        assert L.smat_device_status(stream) == 0

@@ -47,6 +47,40 @@ def test_bad_arguments_are_reported():
         S.read_mtx("/nonexistent/file.mtx")
 
 
+def test_reader_refuses_malformed_files(tmp_path):
+    """Errors are returned, never undefined behaviour: a 'symmetric' file that is not square (the mirror step would
+    write past the row arrays), a truncated entry list, an index outside the stated size."""
+    bad = {
+        "nonsquare_symmetric.mtx": "%%MatrixMarket matrix coordinate real symmetric\n3 40 2\n1 1 1.0\n2 40 2.0\n",
+        "truncated.mtx": "%%MatrixMarket matrix coordinate real general\n3 3 4\n1 1 1.0\n2 2 2.0\n",
+        "out_of_range.mtx": "%%MatrixMarket matrix coordinate real general\n3 3 1\n4 1 1.0\n",
+        "no_banner.mtx": "3 3 1\n1 1 1.0\n",
+    }
+    for name, text in bad.items():
+        path = str(tmp_path / name)
+        with open(path, "w") as f:
+            f.write(text)
+        with pytest.raises(S.SmatError) as e:
+            S.read_mtx(path)
+        assert e.value.code in (-4, -6), name
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(ROOT, "tests", "golden", "reader_*.npz"))),
+                         ids=lambda p: os.path.basename(p)[7:-4])
+def test_reader_matches_reference_run(path, tmp_path):
+    """smat_read_mtx against the arrays the reference's own mmio_allinone produced for the same file (fixtures made by
+    running the unmodified reference, tests/golden/make_golden.py): dimensions, row pointers, columns in file order,
+    fp16 value bits."""
+    z = np.load(path)
+    mtx = str(tmp_path / "m.mtx")
+    with open(mtx, "wb") as f:
+        f.write(z["mtx"].tobytes())
+    M, K, rp, ci, v, _ = S.read_mtx(mtx)
+    assert (M, K) == (int(z["M"]), int(z["K"]))
+    assert np.array_equal(rp, z["csr_rowptr"]) and np.array_equal(ci, z["csr_colidx"])
+    assert np.array_equal(v.view(np.uint16), z["csr_vals"].view(np.uint16))
+
+
 def test_reader_matches_oracle(tmp_path):
     rng = np.random.default_rng(2)
     M, K, n = 253, 251, 3000  # not multiples of 16: both readers pad to 256 x 256

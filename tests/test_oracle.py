@@ -53,6 +53,56 @@ def test_multiply_matches_reference_vbr(golden_dir, name):
     assert np.array_equal(C.view(np.uint32), z["C_f32"].view(np.uint32))
 
 
+READER_FIXTURES = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "reader_*.npz")))
+
+
+@pytest.mark.parametrize("path", READER_FIXTURES, ids=lambda p: os.path.basename(p)[7:-4])
+def test_reader_and_blocking_match_reference_run(path, tmp_path):
+    """The reference's own mmio_allinone + SparseMatrix::csrToBcsr were run on these Matrix-Market texts (fixtures made
+    by tests/golden/make_golden.py): the oracle's reader and blocked-format builder must give the same arrays, bit for bit."""
+    z = np.load(path)
+    mtx = str(tmp_path / "m.mtx")
+    with open(mtx, "wb") as f:
+        f.write(z["mtx"].tobytes())
+    M, K, rp, ci, v, _ = oracle.read_mtx(mtx)
+    assert (M, K) == (int(z["M"]), int(z["K"]))
+    assert np.array_equal(rp, z["csr_rowptr"]) and np.array_equal(ci, z["csr_colidx"])
+    assert np.array_equal(v.view(np.uint16), z["csr_vals"].view(np.uint16))
+    brp, bci, bv = oracle.csr_to_bcsr(M, K, rp, ci, v)
+    assert np.array_equal(brp, z["bcsr_rowptr"]) and np.array_equal(bci, z["bcsr_colidx"])
+    assert np.array_equal(bv.view(np.uint16), z["bcsr_vals"].view(np.uint16))
+    if oracle.have_ref() and hasattr(oracle.ref(), "ref_vbr_from_csr"):
+        # a second, independent piece of the reference: its CPU blocking code (VBR::fill_from_CSR_inplace)
+        vrp, vci, vv = oracle.ref_bcsr_via_vbr(M, K, rp, ci, v)
+        assert np.array_equal(vrp, brp) and np.array_equal(vci, bci)
+        if len(np.unique(np.stack([np.repeat(np.arange(M), np.diff(rp)), ci]), axis=1).T) == len(ci):  # no duplicate entries
+            assert np.array_equal(vv.view(np.uint16), bv.view(np.uint16))
+
+
+def test_reader_and_blocking_match_live_reference(tmp_path):
+    """Where oracle/_ref holds the reference's reader and builder (compiled from its sources): fuzz against them."""
+    G = oracle.ref_gpu()
+    if G is None or not hasattr(G, "ref_sparse_matrix_load"):
+        pytest.skip("oracle/_ref/libsmat_ref_gpu.so is not built here")
+    rng = np.random.default_rng(5)
+    for case in range(6):
+        M, K = int(rng.integers(1, 200)), int(rng.integers(1, 200))
+        n = int(rng.integers(1, 800))
+        rows, cols = rng.integers(0, M, n), rng.integers(0, K, n)
+        rows[-1], cols[-1] = M - 1, K - 1
+        path = str(tmp_path / f"f{case}.mtx")
+        with open(path, "w") as f:
+            f.write(f"%%MatrixMarket matrix coordinate real general\n{M} {K} {n}\n")
+            f.write("".join(f"{r + 1} {c + 1} {v!r}\n" for r, c, v in zip(rows.tolist(), cols.tolist(), rng.standard_normal(n).tolist())))
+        ref = oracle.ref_sparse_matrix(path, host_only=True)
+        Mo, Ko, rp, ci, v, _ = oracle.read_mtx(path)
+        assert (Mo, Ko) == ref[:2] and np.array_equal(rp, ref[2]) and np.array_equal(ci, ref[3])
+        assert np.array_equal(v.view(np.uint16), ref[4].view(np.uint16))
+        brp, bci, bv = oracle.csr_to_bcsr(Mo, Ko, rp, ci, v)
+        assert np.array_equal(brp, ref[5]) and np.array_equal(bci, ref[6])
+        assert np.array_equal(bv.view(np.uint16), ref[7].view(np.uint16))
+
+
 def _dense_bcsr(M, K, rowptr, colidx, vals):
     """Independent numpy construction of the BCSR arrays from a dense scatter."""
     D = np.zeros((M, K), np.float16)

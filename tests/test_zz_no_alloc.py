@@ -16,6 +16,28 @@ from smat_b200 import generators as gen
 pytestmark = pytest.mark.gpu
 
 
+def _device_memory_in_use():
+    """(bytes in use on the device as the driver sees it, bytes handed out by the device's default stream-ordered
+    pool): neither may move across a call that claims to allocate nothing."""
+    import torch
+    free, total = torch.cuda.mem_get_info()
+    rt = None
+    for name in ("libcudart.so.12", "libcudart.so"):
+        try:
+            rt = ctypes.CDLL(name)
+            break
+        except OSError:
+            continue
+    used_pool = -1
+    if rt is not None:
+        pool = ctypes.c_void_p()
+        if rt.cudaDeviceGetDefaultMemPool(ctypes.byref(pool), torch.cuda.current_device()) == 0:
+            val = ctypes.c_uint64(0)
+            if rt.cudaMemPoolGetAttribute(pool, 7, ctypes.byref(val)) == 0:  # cudaMemPoolAttrUsedMemCurrent
+                used_pool = int(val.value)
+    return total - free, used_pool
+
+
 def _both(p, brp, bci, bv, B_nk):
     import torch
     A = S.SparseMatrix.from_bcsr(p.M, p.K, brp, bci, bv)
@@ -25,10 +47,21 @@ def _both(p, brp, bci, bv, B_nk):
     S.spmm(A, B, want, check=True)
     got = S.Matrix(p.M, N, fill=float("nan"))
     L = S.lib()
-    rc = L.smat_spmm_bcsr_f16_static(A.getBcsrValues(), A.getBcsrRowPtr(), A.getBcsrColIdx(), B.data.data_ptr(),
-                                     got.data.data_ptr(), p.M, N, p.K, A.nnzb, torch.cuda.current_stream().cuda_stream)
+    args = (A.getBcsrValues(), A.getBcsrRowPtr(), A.getBcsrColIdx(), B.data.data_ptr(), got.data.data_ptr(), p.M, N, p.K,
+            A.nnzb, torch.cuda.current_stream().cuda_stream)
+    rc = L.smat_spmm_bcsr_f16_static(*args)  # the first call on a device also looks up the array's address
     assert rc == 0, L.smat_last_error_string()
     torch.cuda.synchronize()
+    # a further call with everything set up: device memory in use must not move, neither during nor after it
+    before = _device_memory_in_use()
+    rc = L.smat_spmm_bcsr_f16_static(*args)
+    assert rc == 0, L.smat_last_error_string()
+    during = _device_memory_in_use()
+    torch.cuda.synchronize()
+    after = _device_memory_in_use()
+    assert before == during == after, (before, during, after)
+    # device-side errors of the static entry point are visible through smat_device_status
+    assert L.smat_device_status(torch.cuda.current_stream().cuda_stream) == 0, L.smat_last_error_string()
     return want.data.cpu().numpy(), got.data.cpu().numpy()
 
 

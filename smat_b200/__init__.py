@@ -15,12 +15,15 @@ from .api import (  # noqa: F401
     SparseMatrix,
     Tester,
     all_gather_rows,
+    apply_col_permutation,
     apply_row_permutation,
     jaccard_group,
     launch_count,
     lib,
     partition_block_rows,
+    permute_rows_of_B,
     read_mtx,
+    reorder_cols,
     reorder_rows,
     set_variant,
     spmm,

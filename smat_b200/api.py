@@ -132,6 +132,39 @@ def apply_row_permutation(rowptr, colidx, vals, perm):
     return new_rp.astype(np.int32), np.asarray(colidx)[idx], np.asarray(vals)[idx]
 
 
+def apply_col_permutation(rowptr, colidx, vals, perm):
+    """CSR with columns permuted, values carried: new column c = old column perm[c], i.e. an entry in old column j
+    moves to column inv(perm)[j]; columns are re-sorted inside every row.  This is what the reference's column pass
+    amounts to (src/reorder.py:143-182: transpose, reorder the rows of the transpose, which it leaves transposed and
+    without values).  With A' = this matrix and B' = permute_rows_of_B(B, perm):  A' x B' == A x B."""
+    rowptr = np.asarray(rowptr, dtype=np.int64)
+    perm = np.asarray(perm, dtype=np.int64)
+    inv = np.empty_like(perm)
+    inv[perm] = np.arange(perm.size, dtype=np.int64)
+    rows = np.repeat(np.arange(rowptr.size - 1, dtype=np.int64), np.diff(rowptr))
+    new_cols = inv[np.asarray(colidx, dtype=np.int64)]
+    order = np.lexsort((new_cols, rows))
+    return rowptr.astype(np.int32), new_cols[order].astype(np.int32), np.asarray(vals)[order]
+
+
+def permute_rows_of_B(B_nk, perm):
+    """The dense operand that goes with apply_col_permutation: row k of the new B is row perm[k] of the old one.
+    B_nk is the [N][K] array of the boundary (k contiguous), so the permutation acts on its second axis."""
+    return np.ascontiguousarray(np.asarray(B_nk)[:, np.asarray(perm, dtype=np.int64)])
+
+
+def reorder_cols(rowptr, colidx, K, tau=0.5, col_block=16, row_block=16, threads=0):
+    """Column permutation by the reference's recipe (src/reorder.py:143-182, 206-219): the similarity reorder applied
+    to the rows of the transpose.  Returns (grouping, perm) over the K columns."""
+    rowptr = np.asarray(rowptr, dtype=np.int64)
+    colidx = np.asarray(colidx, dtype=np.int64)
+    rows = np.repeat(np.arange(rowptr.size - 1, dtype=np.int64), np.diff(rowptr))
+    order = np.lexsort((rows, colidx))
+    t_rp = np.zeros(K + 1, np.int64)
+    np.cumsum(np.bincount(colidx, minlength=K), out=t_rp[1:])
+    return reorder_rows(t_rp, rows[order].astype(np.int32), tau=tau, col_block=col_block, row_block=row_block, threads=threads)
+
+
 def partition_block_rows(bcsr_rowptr_host, parts):
     """nnzb-balanced contiguous block-row ranges -> bounds int64[parts+1]."""
     rp = np.ascontiguousarray(bcsr_rowptr_host, dtype=np.int32)

@@ -198,8 +198,21 @@ def reader_fixtures():
             path = os.path.join(d, name + ".mtx")
             with open(path, "w") as f:
                 f.write(text)
-            M, K, crp, cci, cv, brp, bci, bv = oracle.ref_sparse_matrix(path, host_only=True)
+            # small cases also get the reference's export for the Magicube baseline (SparseMatrix::outputCsr writes
+            # ./data/magicube_cop20k_A.mtx relative to the current directory)
+            magicube = b""
+            export = len(text) < 20000
+            cwd = os.getcwd()
+            os.makedirs(os.path.join(d, "data"))
+            os.chdir(d)
+            try:
+                M, K, crp, cci, cv, brp, bci, bv = oracle.ref_sparse_matrix(path, host_only=True, export_magicube=export)
+                if export:
+                    magicube = open(os.path.join(d, "data", "magicube_cop20k_A.mtx"), "rb").read()
+            finally:
+                os.chdir(cwd)
         np.savez_compressed(os.path.join(HERE, f"reader_{name}.npz"), mtx=np.frombuffer(text.encode(), np.uint8), M=M, K=K,
+                            magicube=np.frombuffer(magicube, np.uint8),
                             csr_rowptr=crp, csr_colidx=cci, csr_vals=cv, bcsr_rowptr=brp, bcsr_colidx=bci, bcsr_vals=bv)
         print("reader", name, M, K, "nnz", len(cci), "nnzb", len(bci))
 

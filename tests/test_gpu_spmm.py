@@ -362,3 +362,27 @@ def test_inconsistent_row_pointers_are_reported_not_written_past():
         rc = L.smat_device_status(stream)
         assert rc == -6 and b"bcsrRowPtr" in L.smat_last_error_string(), entry
         assert L.smat_device_status(stream) == 0
+
+
+@pytest.mark.parametrize("name,scale", [("uniform", 0.03), ("powerlaw", 0.01)])
+def test_row_and_column_reorder_keep_the_product(name, scale):
+    """The reference's full preprocessing -- similarity reorder of the rows, then of the columns through the transpose
+    (src/reorder.py:107-182) -- with values carried and the rows of B permuted to match:
+    spmm(P A Q^T, Q B) must equal P spmm(A, B)."""
+    p = gen.make_config(name, scale=scale)
+    _, perm = S.reorder_rows(p.rowptr, p.colidx)
+    rp, ci, v = S.apply_row_permutation(p.rowptr, p.colidx, p.vals, perm)
+    _, cperm = S.reorder_cols(rp, ci, p.K)
+    rp2, ci2, v2 = S.apply_col_permutation(rp, ci, v, cperm)
+    B2 = S.permute_rows_of_B(p.B_nk, cperm)
+    brp0, bci0, bv0 = oracle.csr_to_bcsr(p.M, p.K, p.rowptr, p.colidx, p.vals)
+    brp2, bci2, bv2 = oracle.csr_to_bcsr(p.M, p.K, rp2, ci2, v2)
+    C0 = _run(brp0, bci0, bv0, p.B_nk, p.M, p.N, p.K)
+    C2 = _run(brp2, bci2, bv2, B2, p.M, p.N, p.K)
+    Cref, Cabs = _oracle_c(bv2, brp2, bci2, B2, p.M, p.N, p.K)
+    assert _rel_err(C2, Cref, Cabs) <= TOL
+    # against the unpermuted product: the same sums in another order of addition
+    d = np.abs(C2.astype(np.float32) - C0[perm].astype(np.float32))
+    Cabs0 = oracle.bcsr_spmm(np.abs(bv0), brp0, bci0, np.abs(p.B_nk), p.M, p.N, p.K, 0, p.M // 16, threads=8)[perm]
+    assert float(np.max(d / (np.maximum(np.abs(C0[perm].astype(np.float32)), 1e-2 * Cabs0) + 1e-30))) <= TOL
+    assert len(bci2) <= len(bci0)  # the point of the exercise: fewer nonzero blocks

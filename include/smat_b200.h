@@ -151,6 +151,19 @@ int smat_bcsr_count(const int* csr_rowptr, const int* csr_colidx, size_t M, size
 int smat_bcsr_fill(const int* csr_rowptr, const int* csr_colidx, const void* csr_vals, size_t M, size_t K, size_t nnz,
                    const int* bcsr_rowptr, int* bcsr_colidx, void* bcsr_vals, size_t nnzb, void* stream);
 
+/* Gap-skipping blocking (host, block-rows in parallel).  Replaces SparseMatrix::csrToBcsrKnapsacking
+ * (src/cuda_hgemm/src/common/matrix.h:504-671), the alternative to csrToBcsr that the reference keeps without calling it
+ * (matrix.h:174): blocks are 16 rows x 16 columns but may START AT ANY COLUMN, a new block being opened at the first
+ * stored column the current one does not cover.  Input: host CSR (fp16 bit patterns), M a multiple of 16.  Output
+ * arrays are malloc'ed (release with smat_free_host): bcsr_rowptr int32[M/16+1], bcsr_colidx int32[nnzb] = start
+ * column of every block, bcsr_vals row-major 16x16 blocks.  threads <= 0 uses every hardware thread.
+ * The SpMM entry points above take 16-aligned block columns only; smat_knapsack_to_csr converts back (entries that
+ * are zero inside a block are dropped). */
+int smat_bcsr_knapsack(const int* csr_rowptr, const int* csr_colidx, const uint16_t* csr_vals, size_t M, size_t K, int threads,
+                       size_t* nnzb, int** bcsr_rowptr, int** bcsr_colidx, uint16_t** bcsr_vals);
+int smat_knapsack_to_csr(const int* bcsr_rowptr, const int* bcsr_colidx, const uint16_t* bcsr_vals, size_t M, size_t K,
+                         size_t* nnz, int** csr_rowptr, int** csr_colidx, uint16_t** csr_vals);
+
 /* Matrix-Market reader (host).  Replaces mmio_allinone
  * (src/cuda_hgemm/src/common/mmio_highlevel.h:619-786): dimensions padded up to multiples of 16,
  * 0-based CSR in file order inside each row, symmetric/hermitian files mirrored, pattern files get

@@ -239,10 +239,11 @@ def ref_bcsr_via_vbr(M, K, rowptr, colidx, vals):
     return brp, bci, out.reshape(-1).astype(np.float16)
 
 
-def ref_sparse_matrix(path, host_only=True, export_magicube=False):
+def ref_sparse_matrix(path, host_only=True, export_magicube=False, knapsack=False):
     """Runs the reference's own reader and blocked-format builder, unmodified: mmio_allinone
     (src/cuda_hgemm/src/common/mmio_highlevel.h:619-786) + SparseMatrix::csrToBcsr (matrix.h:376-502).  host_only: just
     those two host steps (no GPU needed); else the class's full constructor, which also uploads (needs a GPU).
+    knapsack (host_only): csrToBcsrKnapsacking (matrix.h:504-671) in place of csrToBcsr -- blocks start at any column.
     Returns (M, K, csr_rowptr, csr_colidx, csr_vals f16, bcsr_rowptr, bcsr_colidx, bcsr_vals f16)."""
     G = ref_gpu()
     if G is None or not hasattr(G, "ref_sparse_matrix_load"):
@@ -251,7 +252,7 @@ def ref_sparse_matrix(path, host_only=True, export_magicube=False):
     M, K, nnz, nnzb = sz(), sz(), sz(), sz()
     ip, up = C.POINTER(C.c_int), C.POINTER(C.c_uint16)
     crp, cci, cv, brp, bci, bv = ip(), ip(), up(), ip(), ip(), up()
-    rc = G.ref_sparse_matrix_load(path.encode(), 1 if host_only else 0, 1 if export_magicube else 0, C.byref(M), C.byref(K), C.byref(nnz), C.byref(nnzb),
+    rc = G.ref_sparse_matrix_load(path.encode(), (2 if knapsack else 1) if host_only else 0, 1 if export_magicube else 0, C.byref(M), C.byref(K), C.byref(nnz), C.byref(nnzb),
                                   C.byref(crp), C.byref(cci), C.byref(cv), C.byref(brp), C.byref(bci), C.byref(bv))
     if rc != 0:
         raise RuntimeError(f"ref_sparse_matrix_load -> {rc}")
@@ -263,3 +264,54 @@ def ref_sparse_matrix(path, host_only=True, export_magicube=False):
     out = (M.value, K.value, take(crp, M.value + 1, None), take(cci, nnz.value, None), take(cv, nnz.value, np.float16),
            take(brp, M.value // 16 + 1, None), take(bci, nnzb.value, None), take(bv, nnzb.value * 256, np.float16))
     return out
+
+
+def csr_to_bcsr_knapsack(M, K, rowptr, colidx, vals):
+    """Restatement of SparseMatrix::csrToBcsrKnapsacking (src/cuda_hgemm/src/common/matrix.h:504-671), the reference's
+    gap-skipping blocking: inside a block-row the stored columns are walked in ascending order and a new 16-wide block
+    is opened at the first column the current one does not cover (:583-606), so blocks start at ANY column; the start
+    of a block is moved left when the columns still to come would otherwise leave a ragged last block (:551-570,
+    :586-600).  Returns (rowptr int32[M/16+1], colidx int32 = start column of every block, vals float16[nnzb*256]).
+    Plain Python loops: for fixtures and small cases."""
+    rowptr = np.asarray(rowptr, dtype=np.int64)
+    colidx = np.asarray(colidx, dtype=np.int64)
+    v16 = np.asarray(vals, dtype=np.float16)
+    brp = np.zeros(M // 16 + 1, np.int32)
+    starts, blocks = [], []
+    nb = 0
+    for br in range(M // 16):
+        brp[br] = nb
+        lo, hi = rowptr[br * 16], rowptr[br * 16 + 16]
+        if hi == lo:
+            continue
+        cols = colidx[lo:hi]
+        rows = np.repeat(np.arange(br * 16, br * 16 + 16), np.diff(rowptr[br * 16:br * 16 + 17]))
+        order = np.argsort(cols, kind="stable")
+        cols, rows, vv = cols[order], rows[order], v16[lo:hi][order]
+        first, last = int(cols[0]), int(cols[-1])
+        add_right = K - last - 1
+
+        def place(col, add_left):
+            span = last - col + 1
+            to_add = 16 - span % 16
+            if span % 16 == 0 or add_right >= to_add:
+                return col
+            if add_left >= to_add:
+                return col - to_add
+            return col - add_left
+        start = place(first, first)
+        starts.append(start)
+        blocks.append(np.zeros((16, 16), np.float16))
+        end = start + 16
+        for c, r, x in zip(cols.tolist(), rows.tolist(), vv):
+            if c >= end:
+                start = place(c, c - end)
+                starts.append(start)
+                blocks.append(np.zeros((16, 16), np.float16))
+                end = start + 16
+                nb += 1
+            blocks[nb][r % 16, c - start] = x
+        nb += 1
+    brp[M // 16] = nb
+    bv = np.stack(blocks).reshape(-1) if blocks else np.zeros(0, np.float16)
+    return brp, np.asarray(starts, np.int32), bv

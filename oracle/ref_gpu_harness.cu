@@ -114,7 +114,10 @@ int ref_sparse_matrix_load(const char* mtx_path, int host_only, int export_magic
         sm = static_cast<SparseMatrix*>(calloc(1, sizeof(SparseMatrix)));
         sm->filename = const_cast<char*>(mtx_path);
         sm->readCsr();
-        sm->csrToBcsr();
+        // host_only == 2: the alternative, gap-skipping blocking the reference keeps beside csrToBcsr
+        // (csrToBcsrKnapsacking, matrix.h:504-671; its call in the constructor is commented out, matrix.h:174)
+        if (host_only == 2) sm->csrToBcsrKnapsacking();
+        else sm->csrToBcsr();
     } else {
         sm = new SparseMatrix("A", const_cast<char*>(mtx_path));
     }

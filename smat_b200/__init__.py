@@ -17,7 +17,9 @@ from .api import (  # noqa: F401
     all_gather_rows,
     apply_col_permutation,
     apply_row_permutation,
+    bcsr_knapsack,
     jaccard_group,
+    knapsack_to_csr,
     launch_count,
     lib,
     partition_block_rows,

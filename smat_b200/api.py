@@ -165,6 +165,45 @@ def reorder_cols(rowptr, colidx, K, tau=0.5, col_block=16, row_block=16, threads
     return reorder_rows(t_rp, rows[order].astype(np.int32), tau=tau, col_block=col_block, row_block=row_block, threads=threads)
 
 
+def _take(ptr, n, ctype, dtype):
+    a = np.ctypeslib.as_array(ptr, shape=(max(n, 1),))[:n].copy()
+    lib().smat_free_host(C.cast(ptr, C.c_void_p))
+    return a.view(dtype)
+
+
+def bcsr_knapsack(M, K, rowptr, colidx, vals, threads=0):
+    """Gap-skipping blocking (csrToBcsrKnapsacking, src/cuda_hgemm/src/common/matrix.h:504-671): 16x16 blocks that may
+    start at any column.  Returns (bcsr_rowptr int32, start column per block int32, bcsr_vals float16)."""
+    rp = np.ascontiguousarray(rowptr, dtype=np.int32)
+    ci = np.ascontiguousarray(colidx, dtype=np.int32)
+    v = np.ascontiguousarray(vals, dtype=np.float16).view(np.uint16)
+    nnzb = C.c_size_t()
+    prp, pci, pv = C.POINTER(C.c_int)(), C.POINTER(C.c_int)(), C.POINTER(C.c_uint16)()
+    L = lib()
+    L.smat_bcsr_knapsack.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_int, C.POINTER(C.c_size_t),
+                                     C.POINTER(C.POINTER(C.c_int)), C.POINTER(C.POINTER(C.c_int)), C.POINTER(C.POINTER(C.c_uint16))]
+    _check(L.smat_bcsr_knapsack(rp.ctypes.data, ci.ctypes.data if ci.size else None, v.ctypes.data if v.size else None, M, K,
+                                threads, C.byref(nnzb), C.byref(prp), C.byref(pci), C.byref(pv)))
+    return (_take(prp, M // 16 + 1, C.c_int, np.int32), _take(pci, nnzb.value, C.c_int, np.int32),
+            _take(pv, nnzb.value * 256, C.c_uint16, np.float16))
+
+
+def knapsack_to_csr(M, K, bcsr_rowptr, bcsr_colidx, bcsr_vals):
+    """Back from the gap-skipping blocking to CSR (columns ascending; zero entries of a block are dropped)."""
+    rp = np.ascontiguousarray(bcsr_rowptr, dtype=np.int32)
+    ci = np.ascontiguousarray(bcsr_colidx, dtype=np.int32)
+    v = np.ascontiguousarray(bcsr_vals, dtype=np.float16).view(np.uint16)
+    nnz = C.c_size_t()
+    prp, pci, pv = C.POINTER(C.c_int)(), C.POINTER(C.c_int)(), C.POINTER(C.c_uint16)()
+    L = lib()
+    L.smat_knapsack_to_csr.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.POINTER(C.c_size_t),
+                                       C.POINTER(C.POINTER(C.c_int)), C.POINTER(C.POINTER(C.c_int)), C.POINTER(C.POINTER(C.c_uint16))]
+    _check(L.smat_knapsack_to_csr(rp.ctypes.data, ci.ctypes.data if ci.size else None, v.ctypes.data if v.size else None, M, K,
+                                  C.byref(nnz), C.byref(prp), C.byref(pci), C.byref(pv)))
+    return (_take(prp, M + 1, C.c_int, np.int32), _take(pci, nnz.value, C.c_int, np.int32),
+            _take(pv, nnz.value, C.c_uint16, np.float16))
+
+
 def partition_block_rows(bcsr_rowptr_host, parts):
     """nnzb-balanced contiguous block-row ranges -> bounds int64[parts+1]."""
     rp = np.ascontiguousarray(bcsr_rowptr_host, dtype=np.int32)

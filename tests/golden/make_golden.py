@@ -17,7 +17,8 @@ Outputs:
   multiply_<name>.npz   BCSR arrays (blocked by the reference's VBR::fill_from_CSR_inplace) + B + fp32 C of the
                         reference's VBR::multiply
   reader_<name>.npz     a Matrix-Market text + the CSR and BCSR arrays that the reference's mmio_allinone and
-                        SparseMatrix::csrToBcsr make of it (needs `make -C oracle ref_gpu REF=...` too)
+                        SparseMatrix::csrToBcsr make of it, the arrays of its csrToBcsrKnapsacking, and for small cases
+                        the bytes of its outputCsr export (needs `make -C oracle ref_gpu REF=...` too)
   formats/*             outputs of the reference's Python glue (src/reorder.py: mtx2el, el2mtx, row pass,
                         transpose, column pass) on a small pattern matrix
 """
@@ -209,10 +210,13 @@ def reader_fixtures():
                 M, K, crp, cci, cv, brp, bci, bv = oracle.ref_sparse_matrix(path, host_only=True, export_magicube=export)
                 if export:
                     magicube = open(os.path.join(d, "data", "magicube_cop20k_A.mtx"), "rb").read()
+                # and the reference's alternative, gap-skipping blocking (csrToBcsrKnapsacking)
+                knap = oracle.ref_sparse_matrix(path, host_only=True, knapsack=True)
             finally:
                 os.chdir(cwd)
         np.savez_compressed(os.path.join(HERE, f"reader_{name}.npz"), mtx=np.frombuffer(text.encode(), np.uint8), M=M, K=K,
-                            magicube=np.frombuffer(magicube, np.uint8),
+                            magicube=np.frombuffer(magicube, np.uint8), knap_rowptr=knap[5], knap_colidx=knap[6],
+                            knap_vals=knap[7],
                             csr_rowptr=crp, csr_colidx=cci, csr_vals=cv, bcsr_rowptr=brp, bcsr_colidx=bci, bcsr_vals=bv)
         print("reader", name, M, K, "nnz", len(cci), "nnzb", len(bci))
 

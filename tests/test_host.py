@@ -81,6 +81,32 @@ def test_reader_matches_reference_run(path, tmp_path):
     assert np.array_equal(v.view(np.uint16), z["csr_vals"].view(np.uint16))
 
 
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(ROOT, "tests", "golden", "reader_*.npz"))),
+                         ids=lambda p: os.path.basename(p)[7:-4])
+def test_knapsack_blocking_matches_reference_run(path):
+    """smat_bcsr_knapsack and the oracle's restatement against the arrays the reference's own csrToBcsrKnapsacking
+    produced (fixtures): row pointers and start columns always; values wherever no (row, column) is stored twice (the
+    reference's unstable sort picks the survivor there).  Converting back gives the matrix again."""
+    z = np.load(path)
+    M, K = int(z["M"]), int(z["K"])
+    rp, ci, v = z["csr_rowptr"], z["csr_colidx"], z["csr_vals"]
+    rows = np.repeat(np.arange(M), np.diff(rp))
+    no_dups = len(np.unique(rows.astype(np.int64) * K + ci)) == len(ci)
+    for got in (S.bcsr_knapsack(M, K, rp, ci, v, threads=3), S.bcsr_knapsack(M, K, rp, ci, v, threads=1),
+                oracle.csr_to_bcsr_knapsack(M, K, rp, ci, v)):
+        assert np.array_equal(got[0], z["knap_rowptr"]) and np.array_equal(got[1], z["knap_colidx"])
+        if no_dups:
+            assert np.array_equal(got[2].view(np.uint16), z["knap_vals"].view(np.uint16))
+    assert len(z["knap_colidx"]) <= len(z["bcsr_colidx"])  # never more blocks than the aligned blocking
+    if no_dups:
+        brp, bci, bv = S.bcsr_knapsack(M, K, rp, ci, v)
+        rp2, ci2, v2 = S.knapsack_to_csr(M, K, brp, bci, bv)
+        keep = (v.view(np.uint16) & 0x7fff) != 0  # stored zeros cannot be told from padding
+        order = np.lexsort((ci[keep], rows[keep]))
+        assert np.array_equal(ci2, ci[keep][order]) and np.array_equal(v2.view(np.uint16), v[keep][order].view(np.uint16))
+        assert np.array_equal(np.diff(rp2), np.bincount(rows[keep], minlength=M))
+
+
 def test_reader_matches_oracle(tmp_path):
     rng = np.random.default_rng(2)
     M, K, n = 253, 251, 3000  # not multiples of 16: both readers pad to 256 x 256

@@ -3,18 +3,25 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--config NAME] [--impl ours|reference]
 
-One "step" is one multiplication of the whole matrix by a fresh-in-HBM B.  Default workload: the
-second BASELINE configuration ("uniform": n = 65536, 0.1 % density, similarity row reorder, 16x16
-blocking, N = 256).  Prints ONE JSON line.
+One "step" is one multiplication of the whole matrix by a B that is resident in HBM.  Default workload: the
+block-sparse weight layer ("llm": 8192 x 28672, 20 % of the 16x16 blocks kept, 4096 activation columns) -- the
+workload both stated targets are defined on (fraction of the roofline at >= 20 % block fill; scaling over 1/2/4/8 GPUs).
+Prints ONE JSON line.
 
-  value      effective TFLOP/s = 2*16*16*N*nnzb / t with A (blocked + plan), B and C resident in HBM
-  e2e        same metric through the library's plan call with HOST B and C: each step copies B
-             host->device from pinned memory, multiplies, and copies C device->host
+  value      effective TFLOP/s = 2*16*16*N*nnzb / t with A (blocked + plan), B and C resident in HBM; t = median over
+             --repeats timed regions of --steps launches each, maximum over ranks
+  e2e        same metric through the library's host-buffer call: each step copies B host->device from pinned memory,
+             multiplies, and copies C device->host (N > 1: every rank uploads 1/N of B, the slices are exchanged over
+             NVLink with one NCCL all-gather)
   roofline   algorithmic bytes (or FLOPs) per launch / measured launch time, against the measured peak
+  all_configs   (1 GPU) the same measurement, one region, for the other four configurations
+  gpu_baselines (1 GPU) the reference's own kernels compiled unmodified for sm_100a, and cuSPARSE CSR SpMM, on the same
+                GPU and matrix
   cpu_baseline  the reference's own CPU blocked multiply (VBR::multiply) on a bounded sample
-With --impl reference the reference's CPU blocked multiply is the thing timed (all host cores, each on
-its own block-row range).  For N > 1 (torchrun) block-rows are partitioned by block count, B is
-replicated, C stays sharded, and there is no collective in the timed region.
+  parity_max_rel_err  sampled block-rows of every measured C against the CPU oracle (the oracle is the checker only)
+With --impl reference the reference's CPU blocked multiply is the thing timed (all host cores, each on its own
+block-row range).  For N > 1 (torchrun) block-rows are partitioned by block count, B is replicated, C stays sharded, and
+there is no collective in the timed region of `value`.
 """
 import argparse
 import json
@@ -40,6 +47,8 @@ NCU_TRAFFIC_BYTES = {
     ("uniform", 1.0, 1): int(117.86e6 * 3548444 / 204859),
     ("uniform", 0.25, 1): int(117.86e6),
 }
+SEEDS = {"band": 0, "uniform": 1, "powerlaw": 2, "clustered": 3, "llm": 4}
+ALL_CONFIGS = ["band", "uniform", "powerlaw", "clustered", "llm"]
 
 
 def load_peaks():
@@ -95,21 +104,27 @@ def build_problem(name, scale, log):
     import smat_b200 as S
     from smat_b200 import generators as gen
     t = time.time()
-    p = gen.make_config(name, scale=scale)
+    if name == "clustered_literal":  # the off-cluster density read literally: 0.001 % of n^2 positions
+        p = gen.make_config("clustered", scale=scale, literal_offcluster=True)
+    else:
+        p = gen.make_config(name, scale=scale)
     log(f"generated {p.desc} in {time.time() - t:.1f}s")
     return p
 
 
-def reorder_if_needed(p, log, perm=None):
+def reorder_if_needed(p, log, perm=None, name=None, scale=1.0):
+    """Row reorder of the configurations that ask for one.  The permutation comes from the on-disk cache when the file
+    for (configuration, seed, scale, tau, block) exists and fits the matrix, else it is computed and stored."""
     import smat_b200 as S
+    from smat_b200 import formats
     if not p.reorder:
         return p.rowptr, p.colidx, p.vals, 0.0, None
-    t = time.time()
+    secs, hit = 0.0, False
     if perm is None:
-        _, perm = S.reorder_rows(p.rowptr, p.colidx, tau=0.5, col_block=16, row_block=16, threads=0)
-    secs = time.time() - t
+        key = formats.cache_key(name or p.name, SEEDS.get(name or p.name, -1), scale, 0.5, 16)
+        perm, secs, hit = formats.cached_permutation(key, p.rowptr, p.colidx, tau=0.5, col_block=16, row_block=16, threads=0, log=log)
     rp, ci, v = S.apply_row_permutation(p.rowptr, p.colidx, p.vals, perm)
-    log(f"row reorder (tau 0.5, 16x16, Keeper) in {secs:.1f}s")
+    log(f"row reorder (tau 0.5, 16x16, Keeper): " + ("from the cache" if hit else f"{secs:.1f}s"))
     return rp, ci, v, secs, perm
 
 
@@ -209,18 +224,124 @@ def sample_ranges(brp, Mb, target_blocks, parts):
     return out
 
 
+def parity_check(C_rows, b0, brp_h, bci_h, bv_h, B_nk, M, N, K, n_samples=4):
+    """Outside every timed region: `n_samples` block-rows of this rank's C (the heaviest one among them) against the CPU
+    oracle, with the error measure of the test-suite: |c - ref| / max(|ref|, 1e-2 * sum |a||b|).  C_rows maps a
+    block-row of the shard to its 16 x N fp16 rows (numpy)."""
+    import oracle
+    b1 = b0 + C_rows.n_brows
+    if b1 <= b0:
+        return 0.0
+    counts = np.diff(brp_h[b0:b1 + 1])
+    picks = sorted({b0 + int(np.argmax(counts)), b0, b1 - 1, b0 + (b1 - b0) // 2, b0 + (b1 - b0) // 3}, key=lambda x: x)[:max(1, n_samples + 1)]
+    worst = 0.0
+    for br in picks:
+        ref = oracle.bcsr_spmm(bv_h, brp_h, bci_h, B_nk, M, N, K, br, br + 1)
+        mag = oracle.bcsr_spmm(np.abs(bv_h), brp_h, bci_h, np.abs(B_nk), M, N, K, br, br + 1)
+        ref16 = ref.astype(np.float16).astype(np.float32)
+        got = C_rows(br - b0).astype(np.float32)
+        worst = max(worst, float(np.max(np.abs(got - ref16) / (np.maximum(np.abs(ref16), 1e-2 * mag) + 1e-30))))
+    return worst
+
+
+class _Rows:
+    """Block-rows of a C held as a torch tensor (device or pinned host) for parity_check."""
+
+    def __init__(self, C):
+        self.C, self.n_brows = C, C.shape[0] // 16
+
+    def __call__(self, i):
+        return self.C[i * 16:(i + 1) * 16].cpu().numpy().view(np.float16)
+
+
+def roofline_of(peaks, bytes_alg, flops, kernel_ms, traffic):
+    t_hbm = bytes_alg / (peaks["hbm_gbs"] * 1e9)
+    t_tensor = flops / (peaks["tflops"] * 1e12)
+    secs = kernel_ms * 1e-3
+    if t_hbm >= t_tensor:
+        ach = bytes_alg / secs / 1e9
+        roof = {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": round(ach / peaks["hbm_gbs"], 4), "traffic": traffic}
+    else:
+        ach = flops / secs / 1e12
+        roof = {"bound": "tensor", "achieved": round(ach, 1), "peak": peaks["tflops"], "unit": "TFLOP/s",
+                "frac": round(ach / peaks["tflops"], 4), "traffic": traffic}
+    roof.update({"peak_source": peaks["source"], "algorithmic_bytes": int(bytes_alg), "flops": flops,
+                 "t_hbm_ms": round(t_hbm * 1e3, 4), "t_tensor_ms": round(t_tensor * 1e3, 4),
+                 "kernel": "spmm_bcsr_tc_kernel", "kernel_ms": round(kernel_ms, 4)})
+    return roof
+
+
+def prepare(name, scale, rank, world, dist, log, keep_csr=False):
+    """Generates a configuration, reorders it if it asks for that, builds the blocked matrix on the device, the block-row
+    range of this rank and its plan.  Returns a dict of everything the measurements need."""
+    import torch
+    import smat_b200 as S
+    p = build_problem(name, scale, log)
+    perm = None
+    if p.reorder and world > 1:  # rank 0 obtains the permutation; the others receive it
+        t = torch.empty(p.M, dtype=torch.int64, device="cuda")
+        if rank == 0:
+            _, _, _, _, perm0 = reorder_if_needed(p, log, None, name, scale)
+            t.copy_(torch.from_numpy(np.asarray(perm0, dtype=np.int64)))
+        dist.broadcast(t, 0)
+        perm = t.cpu().numpy()
+    rp, ci, v, reorder_s, perm = reorder_if_needed(p, log, perm, name, scale)
+    t0 = time.time()
+    A = S.SparseMatrix.from_csr(p.M, p.K, rp, ci, v, keep_csr=keep_csr)
+    build_s = time.time() - t0
+    brp_h, bci_h, bv_h = A.host_arrays()
+    bounds = S.partition_block_rows(brp_h, world)
+    b0, b1 = int(bounds[rank]), int(bounds[rank + 1])
+    t0 = time.time()
+    plan = S.Plan(A, b0, b1, n_hint=p.N)
+    torch.cuda.synchronize()
+    plan_s = time.time() - t0
+    log(f"{name}: M={p.M} K={p.K} N={p.N} nnzb={A.nnzb} (device BCSR build {build_s:.2f}s, plan {plan_s:.2f}s); "
+        f"rank {rank}: block-rows [{b0},{b1}) = {int(brp_h[b1] - brp_h[b0])} blocks")
+    B = S.Matrix.from_host(p.B_nk)
+    Cd = torch.empty(((b1 - b0) * 16, p.N), dtype=torch.float16, device="cuda")
+    return {"p": p, "A": A, "plan": plan, "B": B, "Cd": Cd, "b0": b0, "b1": b1, "bounds": bounds, "host": (brp_h, bci_h, bv_h),
+            "nnz": len(ci), "setup_s": {"reorder": round(reorder_s, 2), "bcsr_build": round(build_s, 3), "plan": round(plan_s, 3)}}
+
+
+def time_regions(ctx, steps, warmup, repeats, barrier, sampler=None):
+    """`warmup` untimed launches, then `repeats` regions of `steps` launches, each between two CUDA events on the launch
+    stream with a barrier + synchronize on both sides.  Returns the per-step milliseconds of every region (this rank)."""
+    import torch
+    import smat_b200 as S
+    plan, B, Cd = ctx["plan"], ctx["B"], ctx["Cd"]
+    for _ in range(warmup):
+        plan.spmm(B, Cd)
+    S.api._check(S.lib().smat_device_status(None))
+    out = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(repeats):
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            plan.spmm(B, Cd)
+        e1.record()
+        barrier()
+        out.append(e0.elapsed_time(e1) / steps)
+    S.api._check(S.lib().smat_device_status(None))
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps launches; the median is reported")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="uniform", choices=["band", "uniform", "powerlaw", "clustered", "llm"])
+    ap.add_argument("--config", default="llm", choices=ALL_CONFIGS)
     ap.add_argument("--scale", type=float, default=1.0)
     ap.add_argument("--cpu-sample-seconds", type=float, default=15.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--gpu-baselines", action="store_true",
-                    help="also time the reference's own kernels (compiled for sm_100a) and cuSPARSE CSR SpMM on this GPU")
+    ap.add_argument("--no-gpu-baselines", action="store_true",
+                    help="skip the reference's own kernels (compiled for sm_100a) and cuSPARSE CSR SpMM on this GPU")
+    ap.add_argument("--no-all-configs", action="store_true", help="skip the one-region measurement of the other configurations")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -246,111 +367,84 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    p = build_problem(args.config, args.scale, log)
-    perm = None
-    if p.reorder and world > 1:
-        # rank 0 computes the permutation once; the others receive it
-        t = torch.empty(p.M, dtype=torch.int64, device="cuda")
-        if rank == 0:
-            _, perm0 = S.reorder_rows(p.rowptr, p.colidx, tau=0.5, col_block=16, row_block=16, threads=0)
-            t.copy_(torch.from_numpy(perm0))
-        dist.broadcast(t, 0)
-        perm = t.cpu().numpy()
-    rp, ci, v, reorder_s, perm = reorder_if_needed(p, log, perm)
-
-    t0 = time.time()
-    A = S.SparseMatrix.from_csr(p.M, p.K, rp, ci, v, keep_csr=args.gpu_baselines)
-    build_s = time.time() - t0
-    brp_h, bci_h, bv_h = A.host_arrays()
-    Mb = p.M // 16
-    bounds = S.partition_block_rows(brp_h, world)
-    b0, b1 = int(bounds[rank]), int(bounds[rank + 1])
-    my_blocks = int(brp_h[b1] - brp_h[b0])
-    t0 = time.time()
-    plan = S.Plan(A, b0, b1, n_hint=p.N)
-    torch.cuda.synchronize()
-    plan_s = time.time() - t0
-    log(f"M={p.M} K={p.K} N={p.N} nnzb={A.nnzb} (device BCSR build {build_s:.2f}s, plan {plan_s:.2f}s); "
-        f"rank {rank}: block-rows [{b0},{b1}) = {my_blocks} blocks")
-
-    B = S.Matrix.from_host(p.B_nk)
-    Cd = torch.empty(((b1 - b0) * 16, p.N), dtype=torch.float16, device="cuda")
-    N = p.N
-
     def barrier():
         torch.cuda.synchronize()
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---------------- resident timing: W warm-ups, K steps between two events ----------------
-    for _ in range(args.warmup):
-        plan.spmm(B, Cd)
-    S.api._check(S.lib().smat_device_status(None))
-    barrier()
+    def max_over_ranks(x):
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    want_gpu_baselines = world == 1 and not args.no_gpu_baselines
+    ctx = prepare(args.config, args.scale, rank, world, dist, log, keep_csr=want_gpu_baselines)
+    p, A, plan, B, Cd, b0, b1 = ctx["p"], ctx["A"], ctx["plan"], ctx["B"], ctx["Cd"], ctx["b0"], ctx["b1"]
+    brp_h, bci_h, bv_h = ctx["host"]
+    N, Mb = p.N, p.M // 16
+    my_blocks = int(brp_h[b1] - brp_h[b0])
+    flops_total = 2.0 * 256.0 * N * A.nnzb
+
+    # ---------------- resident timing ----------------
     launches0 = S.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
-        e0.record()
-        for _ in range(args.steps):
-            plan.spmm(B, Cd)
-        e1.record()
-        barrier()
-        ms_total = e0.elapsed_time(e1)
+        regions = time_regions(ctx, args.steps, args.warmup, args.repeats, barrier)
         launches = S.launch_count() - launches0
         # keep sampling under load for at least ~1.5 s so that the clock record is meaningful
-        t_end = time.time() + max(0.0, 1.5 - ms_total / 1e3)
+        t_end = time.time() + max(0.0, 1.5 - sum(regions) * args.steps / 1e3)
         while time.time() < t_end:
             plan.spmm(B, Cd)
         torch.cuda.synchronize()
-    S.api._check(S.lib().smat_device_status(None))
-    ms_step_local = ms_total / args.steps
-    t = torch.tensor([ms_step_local], dtype=torch.float64, device="cuda")
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t.item())
-    flops_total = 2.0 * 256.0 * N * A.nnzb
+    ms_step_local = statistics.median(regions)
+    ms_step = max_over_ranks(ms_step_local)
     value = flops_total / (ms_step * 1e-3) * 1e-12
+    parity = parity_check(_Rows(Cd), b0, brp_h, bci_h, bv_h, p.B_nk, p.M, N, p.K)
 
     # ---------------- end to end: host B in, host C out, every step ----------------
     B_host = torch.from_numpy(p.B_nk.view(np.int16)).pin_memory()
     C_host = torch.empty(((b1 - b0) * 16, N), dtype=torch.int16).pin_memory()
 
     def e2e_step():
-        # smat_plan_spmm_host: B copied in and C copied out in column chunks, pipelined with the multiplication
-        plan.spmm_host(B_host, C_host)
+        if dist is None:
+            # smat_plan_spmm_host: B copied in and C copied out in column chunks, pipelined with the multiplication
+            plan.spmm_host(B_host, C_host)
+        else:
+            # every rank uploads its 1/N of B; the slices are exchanged on the device (NCCL all-gather over NVLink)
+            plan.spmm_host_sharded(B_host, C_host)
 
     for _ in range(2):
         e2e_step()
     barrier()
-    e2e_steps = max(3, min(args.steps, 10))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(e2e_steps):
+    for _ in range(args.steps):
         e2e_step()
     e1.record()
     barrier()
-    t = torch.tensor([e0.elapsed_time(e1) / e2e_steps], dtype=torch.float64, device="cuda")
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item())
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
     e2e_value = flops_total / (e2e_ms * 1e-3) * 1e-12
+    parity = max(parity, parity_check(_Rows(C_host.view(torch.float16)), b0, brp_h, bci_h, bv_h, p.B_nk, p.M, N, p.K))
+    parity = max_over_ranks(parity)
+    h2d = int(N * p.K * 2) if dist is None else int((S.b_slice_of_rank(N, world, rank)[1] - S.b_slice_of_rank(N, world, rank)[0]) * p.K * 2)
+    del B_host, C_host
 
     # ---------------- optional exchange step, reported beside the SpMM: all-gather of the C shards ----------------
     gather = None
     if dist is not None:
         C_full = torch.empty((p.M, N), dtype=torch.float16, device="cuda")
         for _ in range(2):
-            S.all_gather_rows(Cd, bounds, out=C_full)
+            S.all_gather_rows(Cd, ctx["bounds"], out=C_full)
         barrier()
         g_steps = 5
         e0.record()
         for _ in range(g_steps):
-            S.all_gather_rows(Cd, bounds, out=C_full)
+            S.all_gather_rows(Cd, ctx["bounds"], out=C_full)
         e1.record()
         barrier()
-        t = torch.tensor([e0.elapsed_time(e1) / g_steps], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        gather = {"ms": round(float(t.item()), 4), "bytes_received_per_rank": int(p.M * N * 2 - (b1 - b0) * 16 * N * 2),
+        gather = {"ms": round(max_over_ranks(e0.elapsed_time(e1) / g_steps), 4),
+                  "bytes_received_per_rank": int(p.M * N * 2 - (b1 - b0) * 16 * N * 2),
                   "note": "padded NCCL all_gather of the C shards + copy into place; not part of value or e2e"}
         del C_full
 
@@ -362,22 +456,8 @@ def main():
     # ---------------- roofline of the SpMM kernel (rank 0's launch) ----------------
     peaks = load_peaks()
     bytes_alg = algorithmic_bytes(brp_h[b0:b1 + 1] - brp_h[b0], bci_h[brp_h[b0]:brp_h[b1]], (b1 - b0) * 16, N)
-    flops_rank = 2.0 * 256.0 * N * my_blocks
-    t_hbm = bytes_alg / (peaks["hbm_gbs"] * 1e9)
-    t_tensor = flops_rank / (peaks["tflops"] * 1e12)
-    kernel_s = ms_step_local * 1e-3  # one SpMM launch per step
-    traffic = NCU_TRAFFIC_BYTES.get((args.config, args.scale, world))
-    if t_hbm >= t_tensor:
-        ach = bytes_alg / kernel_s / 1e9
-        roof = {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": round(ach / peaks["hbm_gbs"], 4), "traffic": traffic}
-    else:
-        ach = flops_rank / kernel_s / 1e12
-        roof = {"bound": "tensor", "achieved": round(ach, 1), "peak": peaks["tflops"], "unit": "TFLOP/s",
-                "frac": round(ach / peaks["tflops"], 4), "traffic": traffic}
-    roof.update({"peak_source": peaks["source"], "algorithmic_bytes": int(bytes_alg), "flops": flops_rank,
-                 "t_hbm_ms": round(t_hbm * 1e3, 4), "t_tensor_ms": round(t_tensor * 1e3, 4),
-                 "kernel": "spmm_bcsr_tc_kernel", "kernel_ms": round(ms_step_local, 4)})
+    roof = roofline_of(peaks, bytes_alg, 2.0 * 256.0 * N * my_blocks, ms_step_local,
+                       NCU_TRAFFIC_BYTES.get((args.config, args.scale, world)))
 
     # ---------------- CPU baseline: the reference's blocked multiply on a bounded sample ----------------
     cpu = None
@@ -393,24 +473,32 @@ def main():
                "sample": f"block-rows [{rng[0][0]},{rng[0][1]}) = {nb} of {A.nnzb} blocks ({100.0 * nb / A.nnzb:.2f}%), "
                          f"{secs:.1f}s, VBR::multiply fp32 single thread"}
 
-    other = None
-    if world == 1 and args.gpu_baselines:
-        other = gpu_baselines(A, B, p, N, log)
+    other = gpu_baselines(A, B, p, N, log) if want_gpu_baselines else None
+
+    def l2_label(nnzb, K, n_cols, rows):
+        resident = nnzb * 512 + n_cols * K * 2 + rows * n_cols * 2  # A blocks + B + C touched by every step
+        return ("inputs larger than L2 (A blocks, B and C of a step: %.0f MB; every step streams them from HBM)" % (resident / 1e6)
+                if resident > 126e6 else "inputs fit L2 (%.0f MB); no flush between steps" % (resident / 1e6))
 
     out = {
         "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
         "config": {"workload": f"{args.config}: {p.desc}; 16x16 blocking" + ("; similarity row reorder" if p.reorder else ""),
-                   "M": p.M, "K": p.K, "N": N, "nnzb": A.nnzb, "block_fill": round(len(ci) / (A.nnzb * 256.0), 5),
+                   "M": p.M, "K": p.K, "N": N, "nnzb": A.nnzb, "block_fill": round(ctx["nnz"] / (A.nnzb * 256.0), 5),
                    "parallelism": f"block-rows split by block count over {world} GPU(s), B replicated, C sharded",
-                   "l2": "inputs larger than L2 (A blocks stream from HBM every step)" if A.nnzb * 512 > 130e6
-                   else "inputs fit L2; no flush between steps",
-                   "setup_s": {"reorder": round(reorder_s, 2), "bcsr_build": round(build_s, 3), "plan": round(plan_s, 3)}},
-        "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": int(N * p.K * 2),
-                "d2h_bytes_per_step": int((b1 - b0) * 16 * N * 2), "ms_per_step": round(e2e_ms, 4),
-                "note": "smat_plan_spmm_host per step: B host->device (pinned) and C device->host in column chunks pipelined with the multiplication; A (blocked) resident"},
+                   "l2": l2_label(my_blocks, p.K, N, (b1 - b0) * 16),
+                   "timing": f"median of {args.repeats} regions of {args.steps} launches (CUDA events on the launch stream), max over ranks",
+                   "setup_s": ctx["setup_s"]},
+        "regions_ms_per_step": [round(x, 5) for x in regions],
+        "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": int((b1 - b0) * 16 * N * 2), "ms_per_step": round(e2e_ms, 4), "steps": args.steps,
+                "note": ("smat_plan_spmm_host per step: B host->device (pinned) and C device->host in column chunks pipelined with the "
+                         "multiplication; A (blocked) resident") if world == 1 else
+                        ("per step and rank: 1/N of B host->device (pinned), NCCL all-gather of the slices over NVLink, multiply, "
+                         "C shard device->host; h2d/d2h bytes are rank 0's")},
         "gpu_launches": int(launches),
+        "parity_max_rel_err": float(f"{parity:.3e}"),
         "clocks": clocks.summary(),
         "roofline": roof,
         "cpu_baseline": cpu,
@@ -419,6 +507,32 @@ def main():
         out["gpu_baselines"] = other
     if gather is not None:
         out["c_allgather"] = gather
+
+    # ---------------- the other configurations, one region each (1 GPU) ----------------
+    if world == 1 and not args.no_all_configs:
+        rows = [{"config": args.config, "ms": round(ms_step, 5), "tflops": round(value, 2), "bound": roof["bound"], "frac": roof["frac"],
+                 "nnzb": A.nnzb, "parity_max_rel_err": float(f"{parity:.3e}")}]
+        plan.close()
+        del ctx, plan, A, B, Cd
+        torch.cuda.empty_cache()
+        for name in [n for n in ALL_CONFIGS + ["clustered_literal"] if n != args.config]:
+            try:
+                c2 = prepare(name, args.scale, 0, 1, None, log)
+                reg = time_regions(c2, max(args.steps, 20), 3, 1, barrier)
+                p2, h2 = c2["p"], c2["host"]
+                ms2 = reg[0]
+                r2 = roofline_of(peaks, algorithmic_bytes(h2[0], h2[1], p2.M, p2.N), 2.0 * 256.0 * p2.N * c2["A"].nnzb, ms2, None)
+                par2 = parity_check(_Rows(c2["Cd"]), 0, h2[0], h2[1], h2[2], p2.B_nk, p2.M, p2.N, p2.K)
+                rows.append({"config": name, "ms": round(ms2, 5), "tflops": round(2.0 * 256.0 * p2.N * c2["A"].nnzb / (ms2 * 1e-3) * 1e-12, 2),
+                             "bound": r2["bound"], "frac": r2["frac"], "nnzb": c2["A"].nnzb,
+                             "block_fill": round(c2["nnz"] / (c2["A"].nnzb * 256.0), 5), "parity_max_rel_err": float(f"{par2:.3e}"),
+                             "setup_s": c2["setup_s"]})
+                c2["plan"].close()
+                del c2
+                torch.cuda.empty_cache()
+            except Exception as e:  # one configuration failing must not lose the headline line
+                rows.append({"config": name, "error": f"{type(e).__name__}: {e}"[:200]})
+        out["all_configs"] = rows
     print(json.dumps(out), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -432,7 +546,7 @@ def run_reference_arm(args, rank, world, log):
     import oracle
     import smat_b200 as S
     p = build_problem(args.config, args.scale, log)
-    rp, ci, v, reorder_s, _ = reorder_if_needed(p, log)
+    rp, ci, v, reorder_s, _ = reorder_if_needed(p, log, None, args.config, args.scale)
     brp, bci, bv = oracle.csr_to_bcsr(p.M, p.K, rp, ci, v)
     nnzb, Mb, N = len(bci), p.M // 16, p.N
     cores = os.cpu_count() or 1

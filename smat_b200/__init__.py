@@ -17,6 +17,8 @@ from .api import (  # noqa: F401
     all_gather_rows,
     apply_col_permutation,
     apply_row_permutation,
+    b_slice_of_rank,
+    gather_b_slices,
     bcsr_knapsack,
     jaccard_group,
     knapsack_to_csr,

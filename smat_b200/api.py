@@ -204,6 +204,39 @@ def knapsack_to_csr(M, K, bcsr_rowptr, bcsr_colidx, bcsr_vals):
             _take(pv, nnz.value, C.c_uint16, np.float16))
 
 
+def b_slice_of_rank(N, world, rank):
+    """Which rows of the [N][K] array B (= columns of the logical K x N matrix) a rank uploads in the sharded
+    host-buffer product: (first, last + 1, rows per rank before the last one = the padded slice height).  Slices are
+    multiples of 8 rows wide, like N itself."""
+    per = ((N + world - 1) // world + 7) // 8 * 8
+    lo = min(N, rank * per)
+    hi = min(N, lo + per)
+    return lo, hi, per
+
+
+def gather_b_slices(B_host, staging, group=None):
+    """Every rank copies its slice of B_host ([N][K], see b_slice_of_rank) into its part of ``staging``
+    ([world * slice height][K], on the device the collective runs on), one all_gather fills the rest, and the [N][K]
+    matrix is returned (a view of ``staging`` when the slices need no padding)."""
+    import torch
+    import torch.distributed as dist
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    N = B_host.shape[0]
+    lo, hi, pad = b_slice_of_rank(N, world, rank)
+    mine = staging[rank * pad:(rank + 1) * pad]
+    mine[:hi - lo].copy_(B_host[lo:hi], non_blocking=True)
+    # NCCL gathers in place (the rank's slice already sits where it belongs); other backends want a separate input
+    # (as bytes: not every backend knows 16-bit element types)
+    dist.all_gather_into_tensor(staging.view(torch.uint8), (mine if staging.is_cuda else mine.clone()).view(torch.uint8), group=group)
+    if world * pad == N:
+        return staging
+    parts = []
+    for r in range(world):
+        a, b, _ = b_slice_of_rank(N, world, r)
+        parts.append(staging[r * pad:r * pad + (b - a)])
+    return torch.cat(parts)
+
+
 def partition_block_rows(bcsr_rowptr_host, parts):
     """nnzb-balanced contiguous block-row ranges -> bounds int64[parts+1]."""
     rp = np.ascontiguousarray(bcsr_rowptr_host, dtype=np.int32)
@@ -413,6 +446,29 @@ class Plan:
         assert B_host.is_contiguous() and C_host.is_contiguous() and not B_host.is_cuda and not C_host.is_cuda
         assert B_host.element_size() == 2 and C_host.element_size() == 2
         _check(lib().smat_plan_spmm_host(self._h, B_host.data_ptr(), C_host.data_ptr(), N, _stream()))
+
+    def spmm_host_sharded(self, B_host, C_host, group=None):
+        """The host-buffer product for a plan that is one rank's shard of a multi-GPU run.  B is replicated on the
+        device side, but every rank taking all of it over PCIe each step makes G ranks pull G copies through the host;
+        here a rank uploads only its 1/G of B's columns (a contiguous row range of the [N][K] array, see
+        ``b_slice_of_rank``), the slices are exchanged on the device with one all_gather (NCCL over NVLink for CUDA
+        tensors; every kernel still reads local memory only), then the shard is multiplied and its rows of C copied out.
+        B_host / C_host as in ``spmm_host``; every rank passes the same B_host."""
+        import torch
+        import torch.distributed as dist
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        N, K = B_host.shape
+        rows = (self.brow_end - self.brow_begin) * 16
+        assert K == self.A.K and tuple(C_host.shape) == (rows, N) and B_host.element_size() == 2
+        dev = torch.device("cuda", torch.cuda.current_device())
+        _, _, pad = b_slice_of_rank(N, world, rank)
+        if getattr(self, "_sh", None) is None or self._sh[0].shape != (world * pad, K) or self._sh[0].dtype != B_host.dtype:
+            self._sh = (torch.empty((world * pad, K), dtype=B_host.dtype, device=dev),
+                        torch.empty((rows, N), dtype=C_host.dtype, device=dev))
+        Bd, Cd = self._sh
+        B_full = gather_b_slices(B_host, Bd, group)
+        _check(lib().smat_plan_spmm(self._h, B_full.data_ptr(), Cd.data_ptr(), N, _stream()))
+        C_host.copy_(Cd, non_blocking=True)
 
     def close(self):
         if self._h is not None:

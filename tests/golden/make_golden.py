@@ -260,6 +260,14 @@ def formats_fixtures():
                         os.path.join(out, "ref_reordered_transposed_reordered.el"))
         finally:
             os.chdir(cwd)
+    # the reference's band-matrix generator (src/generate_matrices.py:5-35), imported from the reference tree
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("ref_generate_matrices", os.path.join(ref_src, "generate_matrices.py"))
+    ref_gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref_gen)
+    with tempfile.TemporaryDirectory() as d:
+        ref_gen.generate_band_mtx_matrix(37, 5, d, "band.mtx")
+        shutil.copy(os.path.join(d, "band.mtx"), os.path.join(out, "ref_band_37_5.mtx"))
     print("formats fixtures:", sorted(os.listdir(out)))
 
 

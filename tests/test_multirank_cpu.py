@@ -45,6 +45,13 @@ def _worker(rank, world, port, out_dir):
         np.save(os.path.join(out_dir, "ranges.npy"), torch.stack(allr).numpy())
         np.save(os.path.join(out_dir, "total.npy"), np.array([len(bci), p.M // 16]))
     np.save(os.path.join(out_dir, f"shard{rank}.npy"), shard)
+    # the host-buffer product of a shard: every rank contributes its slice of B, one all_gather rebuilds the whole
+    for n_cols in (p.N, 40):  # slices that tile B exactly / a last slice that is shorter
+        B_host = torch.from_numpy(p.B_nk[:n_cols].view(np.int16).copy())
+        _, _, pad = S.b_slice_of_rank(n_cols, world, rank)
+        staging = torch.full((world * pad, p.K), -1, dtype=torch.int16)
+        B_full = S.gather_b_slices(B_host if rank == 0 else B_host.clone(), staging)
+        assert torch.equal(B_full, B_host)
     # the optional exchange step: every rank assembles the whole C from the shards of unequal height
     gathered = S.all_gather_rows(torch.from_numpy(shard), bounds)
     np.save(os.path.join(out_dir, f"gathered{rank}.npy"), gathered.numpy())
@@ -65,3 +72,14 @@ def test_two_ranks_partition_and_tile_the_result(tmp_path):
     assert np.array_equal(tiled.view(np.uint32), full.view(np.uint32))
     for r in range(world):
         assert np.array_equal(np.load(tmp_path / f"gathered{r}.npy").view(np.uint32), full.view(np.uint32))
+
+
+def test_b_slices_tile_the_columns():
+    for N in (8, 40, 256, 4096, 4104):
+        for world in (1, 2, 3, 4, 8):
+            at = 0
+            for r in range(world):
+                lo, hi, pad = S.b_slice_of_rank(N, world, r)
+                assert lo == at and lo <= hi <= N and (hi - lo) % 8 == 0 and hi - lo <= pad and pad % 8 == 0
+                at = hi
+            assert at == N

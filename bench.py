@@ -341,6 +341,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gpu-baselines", action="store_true",
                     help="skip the reference's own kernels (compiled for sm_100a) and cuSPARSE CSR SpMM on this GPU")
+    ap.add_argument("--variant", type=int, default=0, choices=[0, 1, 2, 3, 4],
+                    help="kernel variant for every plan of this run (smat_spmm_set_variant; 0 = chosen per matrix)")
     ap.add_argument("--no-all-configs", action="store_true", help="skip the one-region measurement of the other configurations")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -379,6 +381,7 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    S.set_variant(args.variant)
     want_gpu_baselines = world == 1 and not args.no_gpu_baselines
     ctx = prepare(args.config, args.scale, rank, world, dist, log, keep_csr=want_gpu_baselines)
     p, A, plan, B, Cd, b0, b1 = ctx["p"], ctx["A"], ctx["plan"], ctx["B"], ctx["Cd"], ctx["b0"], ctx["b1"]
@@ -488,6 +491,7 @@ def main():
                    "M": p.M, "K": p.K, "N": N, "nnzb": A.nnzb, "block_fill": round(ctx["nnz"] / (A.nnzb * 256.0), 5),
                    "parallelism": f"block-rows split by block count over {world} GPU(s), B replicated, C sharded",
                    "l2": l2_label(my_blocks, p.K, N, (b1 - b0) * 16),
+                   "kernel_variant": args.variant,
                    "timing": f"median of {args.repeats} regions of {args.steps} launches (CUDA events on the launch stream), max over ranks",
                    "setup_s": ctx["setup_s"]},
         "regions_ms_per_step": [round(x, 5) for x in regions],

@@ -630,10 +630,20 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
         if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
         if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan build failed: %s", cudaGetErrorString(e));
     }
-    // Densely filled quads (config 4: every quad of a cluster holds all 64 blocks) are cut into pieces of at most 24
+    // blocks of THIS range (nonzeroBlocks counts the whole arrays): what the choices below and at launch go by
+    size_t range_blocks = nnzb;
+    if (rc == SMAT_OK && nnzb) {
+        int ends[2] = {0, 0};
+        e = cudaMemcpyAsync(&ends[0], bcsrRowPtrA + brow_begin, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(&ends[1], bcsrRowPtrA + brow_end, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+        if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan build failed: %s", cudaGetErrorString(e));
+        else if (ends[1] >= ends[0] && (size_t)(ends[1] - ends[0]) <= nnzb) range_blocks = (size_t)(ends[1] - ends[0]);
+    }
+    // Densely filled quads (dense clusters: every quad of a cluster holds all 64 blocks) are cut into pieces of at most 24
     // blocks that each fetch the B panel again; when the steps are that full on average, recount with 32 per step.
     size_t cap = kPlanBlocksPerStep;
-    if (rc == SMAT_OK && total_and_max[0] > 0 && nnzb >= 18 * (size_t)total_and_max[0]) {
+    if (rc == SMAT_OK && total_and_max[0] > 0 && range_blocks >= 18 * (size_t)total_and_max[0]) {
         cap = kPlanBlocksPerStepDense;
         rc = plan_count_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, rg, gsp, (cudaStream_t)stream, nullptr, cap);
         if (rc == SMAT_OK) {
@@ -757,7 +767,7 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
     p->v.blk = reinterpret_cast<int*>(b + sz.steps_bytes);
     p->v.packed = b + sz.steps_bytes + sz.blk_bytes;
     p->v.K = K;
-    p->v.nnzb = nnzb;
+    p->v.nnzb = range_blocks;  // blocks of the plan's range
     p->v.brow_begin = brow_begin;
     p->v.brow_end = brow_end;
     p->v.n_groups = sz.n_groups;

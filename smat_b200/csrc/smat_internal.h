@@ -118,6 +118,7 @@ struct PlanView {
     const void* steps = nullptr;
     const int* blk = nullptr;
     const void* packed = nullptr;
+    // nnzb: blocks of block-rows [brow_begin, brow_end) when known (plans), else of the whole arrays; steers heuristics only
     size_t K = 0, nnzb = 0, brow_begin = 0, brow_end = 0, n_groups = 0, rg = kPlanRowsPerGroup;
     size_t total_steps = 0;  // number of steps of the range when the host knows it, else 0
     size_t cap = kPlanBlocksPerStep;  // most blocks of a step: kPlanBlocksPerStep or kPlanBlocksPerStepDense

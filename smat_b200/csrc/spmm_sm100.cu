@@ -69,12 +69,10 @@ constexpr int NL = 4;                  // loader warps
 #ifndef SMAT_TMA_EPILOGUE
 #define SMAT_TMA_EPILOGUE 1
 #endif
-// L2 prefetches of the panel and the blocks a few steps ahead of their copies.  Off: measured on the final kernel they
-// change nothing where the copies are not the limit (uniform, block-sparse layer, power-law) and cost a third of the
-// time where they are (dense clusters: 0.335 -> 0.230 ms), because a prefetch occupies the copy engine like a copy.
-#ifndef SMAT_L2_PREFETCH
-#define SMAT_L2_PREFETCH 0
-#endif
+// L2 prefetches of the panel and the blocks a few steps ahead of their copies (kernel argument `pf`) are off unless the
+// environment variable SMAT_L2_PREFETCH=1 asks for them.  Measured on the final kernel they change nothing where the copies
+// are not the limit (uniform, block-sparse layer and its shards, power-law) and cost a third of the time where they are
+// (dense clusters: 0.335 -> 0.230 ms without), because a prefetch occupies the copy engine like a copy.
 constexpr int NM = kPlanOwners;        // MMA-issuing warps; warp m owns accumulators [m * RG / NM, (m + 1) * RG / NM)
 constexpr int NC = 4;                  // panel-copier warps (used by the tensor-memory-operand variant)
 constexpr int kThreads = (NL + NC + NM + 4) * 32;
@@ -133,7 +131,7 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_const
                     const int* __restrict__ rowptr, __half* __restrict__ C, int brow_begin, int brow_end, int rg, int N,
                     int n_tiles, int n_items, int n_groups, int tail_parts, uint32_t panel_bytes,
                     float* __restrict__ fix_scratch, int* status, size_t ldc, const int* __restrict__ sched_off,
-                    const int* __restrict__ sched_list, int nm) {
+                    const int* __restrict__ sched_list, int nm, int pf) {
     static_assert(!(TS && NH == 2), "the panel ring and 32 accumulators do not fit tensor memory together");
     // The schedule is a template parameter: measured, the code generated for the MMA issue loop changed by up to 35 %
     // with the shape of the control flow around it, so each schedule gets a kernel with only its own loops.
@@ -344,15 +342,13 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_const
                     h_next += NL;
                 }
             };
-            // Optional (SMAT_L2_PREFETCH, off by default): the panel and the blocks of the step U/2 positions ahead
-            // (of this warp; NL * U/2 steps ahead overall) are prefetched into L2.
+            // When the launch asks for it (pf): the panel and the blocks of the step U/2 positions ahead (of this warp;
+            // NL * U/2 steps ahead overall) are prefetched into L2.
             auto prefetch = [&](const StepRec& r) {
-#if SMAT_L2_PREFETCH
-                if (r.live) {
+                if (pf && r.live) {
                     tma_prefetch_l2_2d(&mapB, (int)r.d.x, r.tile * NT);
                     bulk_prefetch_l2(packed + (size_t)r.d.y * 256, (uint32_t)(__popc(r.d.z) + __popc(r.d.w)) * ABLK_BYTES);
                 }
-#endif
             };
 #pragma unroll
             for (int a = 0; a < U; a++) gen(rec[a]);
@@ -719,13 +715,15 @@ int launch_spmm(const PlanView& whole, const void* B, void* C, size_t N, cudaStr
         const int v = std::atoi(ev);
         if (v == 1 || v == 2 || v == 4 || v == 8) nm = v;
     }
+    int pf = 0;  // L2 prefetch (see the top of the file)
+    if (const char* ev = std::getenv("SMAT_L2_PREFETCH")) pf = std::atoi(ev) != 0;  // tuning knob
     auto launch = [&](auto kernel, uint32_t smem_bytes) -> int {
         SMAT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
         kernel<<<grid, kThreads, smem_bytes, stream>>>(
             mapB, mapC, reinterpret_cast<const uint8_t*>(plan.packed), reinterpret_cast<const uint4*>(plan.steps), plan.gsp,
             plan.rowptr, reinterpret_cast<__half*>(C), (int)plan.brow_begin, (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles,
             (int)n_items, (int)plan.n_groups, parts, panel_rows * 128u, plan.fix_scratch, ctx->d_status, ldc,
-            listed ? plan.sched_off : nullptr, listed ? plan.sched_list : nullptr, nm);
+            listed ? plan.sched_off : nullptr, listed ? plan.sched_list : nullptr, nm, pf);
         count_launch();
         SMAT_CUDA_TRY(cudaGetLastError());
         return SMAT_OK;

@@ -30,6 +30,9 @@
 // Scheduling is the round-robin-with-cut-last-round scheme of spmm_sm100.cu (SegGen<0>).
 #include <cuda_fp16.h>
 #include <limits.h>
+#include <stdlib.h>
+
+#include <cstdlib>
 
 #include "ptx_sm100.cuh"
 #include "smat_internal.h"
@@ -82,7 +85,7 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
                       const uint4* __restrict__ steps, const uint4* __restrict__ winfo, const int* __restrict__ gsp,
                       const int* __restrict__ rowptr,
                       __half* __restrict__ C, size_t ldc, int brow_begin, int brow_end, int rg, int N, int n_tiles, int n_items,
-                      int tail_parts, uint32_t panel_bytes, float* __restrict__ fix_scratch, int* status) {
+                      int tail_parts, uint32_t panel_bytes, float* __restrict__ fix_scratch, int* status, int pf) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar0 = base + OFF_BAR;
@@ -149,11 +152,8 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
             Seg cs;
             bool have = sg.next(cs);
             uint32_t h_st0 = 0, h_next = (uint32_t)j;
-#ifndef SMAT_TALL_PF
-#define SMAT_TALL_PF 0
-#endif
             constexpr int U = 4;  // step records in flight per loader (their descriptors are requested U positions ahead)
-            constexpr int PF = SMAT_TALL_PF;  // records ahead (of this loader) whose data is prefetched into L2; 0 = none
+            constexpr int PF = 2;  // records ahead (of this loader) whose data is prefetched into L2 when the launch asks for it
             TallStep rec[U];
             auto gen = [&](TallStep& r) {
                 while (have && h_next >= h_st0 + (uint32_t)(cs.k1 - cs.k0)) {
@@ -170,7 +170,7 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
                 }
             };
             auto prefetch = [&](const TallStep& r) {  // HBM latency is hidden in L2: fetched PF records ahead of the copies
-                if (PF > 0 && r.live) {
+                if (pf && r.live) {
                     tma_prefetch_l2_2d(&mapB, (int)r.a.x, r.tile * 128);
                     bulk_prefetch_l2(packed + (size_t)r.a.y * 256, r.a.z * 512u);
                 }
@@ -409,12 +409,14 @@ int launch_spmm_tall(const PlanView& whole, const void* B, void* C, size_t N, cu
     const int parts = (int)tail_parts_for(n_items, sms, true, est_steps);
     const int grid = (int)((parts > 1 || n_items > sms) ? sms : n_items);
     const int n_full = (int)(n_items / (size_t)grid * (size_t)grid);
+    int pf = 0;  // L2 prefetch: measured to make no difference here, and it costs copy-engine time
+    if (const char* ev = std::getenv("SMAT_L2_PREFETCH")) pf = std::atoi(ev) != 0;  // tuning knob
     SMAT_CUDA_TRY(cudaFuncSetAttribute(spmm_bcsr_tall_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
     spmm_bcsr_tall_kernel<<<grid, kTallThreads, SMEM_BYTES, stream>>>(
         mapB, reinterpret_cast<const uint8_t*>(plan.packed), reinterpret_cast<const uint4*>(plan.steps),
         reinterpret_cast<const uint4*>(plan.winfo), plan.gsp, plan.rowptr,
         reinterpret_cast<__half*>(C), ldc, (int)plan.brow_begin, (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles, (int)n_items, parts, panel_rows * 128u,
-        plan.fix_scratch, ctx->d_status);
+        plan.fix_scratch, ctx->d_status, pf);
     count_launch();
     SMAT_CUDA_TRY(cudaGetLastError());
     if (parts == 1) return SMAT_OK;

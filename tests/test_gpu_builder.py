@@ -94,7 +94,7 @@ def test_builder_from_mtx_file(tmp_path):
 
 
 def test_builder_full_size_llm_structure():
-    """Config 5 at full size: exact block count and a checksum of the value array."""
+    """The block-sparse weight layer at full size: exact block count and a checksum of the value array."""
     p = gen.make_config("llm")
     A = S.SparseMatrix.from_csr(p.M, p.K, p.rowptr, p.colidx, p.vals)
     assert A.nnzb == 183501

@@ -135,7 +135,7 @@ def test_edge_cases():
 
 
 def test_ragged_rows_and_long_block_row():
-    """Block-rows with 0, 1 and hundreds of blocks side by side (load imbalance, as in config 3)."""
+    """Block-rows with 0, 1 and hundreds of blocks side by side (load imbalance, as in a power-law matrix)."""
     rng = np.random.default_rng(4)
     Mb, Kb, N = 40, 600, 72
     counts = rng.integers(0, 4, Mb)
@@ -279,24 +279,41 @@ def test_tester_harness_reports_throughput():
     assert np.max(np.abs(got - want)) <= 1e-2 * np.maximum(np.abs(want), 1).max()
 
 
-@pytest.mark.parametrize("name", ["llm", "clustered"])
+@pytest.mark.parametrize("name", ["llm", "clustered", "uniform", "powerlaw"])
 def test_full_size_sampled_block_rows(name):
-    """BASELINE-size configs: the GPU result of sampled block-rows against the oracle, plus the
-    size-independent property that block-rows without blocks are exactly zero."""
+    """The benchmark's matrices at full size, prepared the way bench.py prepares them (similarity reorder from the
+    permutation cache where the configuration asks for one, device-side blocking, a plan): sampled block-rows of the
+    GPU result against the oracle -- the first, the last, the one with the most blocks, one of the group with the most
+    blocks, and random ones -- plus the size-independent property that block-rows without blocks are exactly zero.
+    These sizes select code paths the small cases do not: 256-column work items over several rounds (uniform), the
+    listed schedule with thousands of steps per CTA (power-law), steps of 32 blocks (clustered)."""
+    from smat_b200 import formats
     torch = _torch()
     p = gen.make_config(name)
-    A = S.SparseMatrix.from_csr(p.M, p.K, p.rowptr, p.colidx, p.vals)
+    rp, ci, v = p.rowptr, p.colidx, p.vals
+    if p.reorder:
+        seed = {"uniform": 1, "powerlaw": 2}[name]
+        perm, _, _ = formats.cached_permutation(formats.cache_key(name, seed, 1.0, 0.5, 16), rp, ci)
+        rp, ci, v = S.apply_row_permutation(rp, ci, v, perm)
+    A = S.SparseMatrix.from_csr(p.M, p.K, rp, ci, v)
     B = S.Matrix.from_host(p.B_nk)
     C = S.Matrix(p.M, p.N, fill=float("nan"))
-    S.spmm(A, B, C, check=True)
+    plan = S.Plan(A, n_hint=p.N)
+    plan.spmm(B, C, check=True)
+    plan.close()
     brp, bci, bv = A.host_arrays()
     Mb = p.M // 16
     rng = np.random.default_rng(0)
-    for br in sorted(set([0, Mb - 1] + rng.integers(0, Mb, 6).tolist())):
+    counts = np.diff(brp)
+    heaviest = int(np.argmax(counts))
+    per_group = np.add.reduceat(counts, np.arange(0, Mb, 16))
+    in_heaviest_group = int(np.argmax(per_group)) * 16 + 7
+    picks = sorted(set([0, Mb - 1, heaviest, min(in_heaviest_group, Mb - 1)] + rng.integers(0, Mb, 6).tolist()))
+    for br in picks:
         Cref, Cabs = _oracle_c(bv, brp, bci, p.B_nk, p.M, p.N, p.K, rows=(br, br + 1))
         got = C.data[br * 16:br * 16 + 16].cpu().numpy()
         assert _rel_err(got, Cref, Cabs) <= TOL, br
-    empty = np.nonzero(np.diff(brp) == 0)[0]
+    empty = np.nonzero(counts == 0)[0]
     for br in empty[:4]:
         assert torch.all(C.data[br * 16:br * 16 + 16] == 0)
     assert not torch.isnan(C.data).any()

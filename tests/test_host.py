@@ -202,3 +202,33 @@ def test_partition_is_balanced_and_covers():
         if parts > 1:
             assert loads.max() <= rp[-1] / parts + 4000
     assert S.partition_block_rows(np.zeros(11, np.int32), 4).tolist() == [0, 2, 5, 7, 10]
+
+
+def test_integration_shim_compiles_against_the_reference_signature(tmp_path):
+    """The shim INTEGRATION.md tells a maintainer of the reference to add is taken from that file and compiled (nvcc -c)
+    against include/smat_b200.h, and a second translation unit declares it through the reference's own
+    HGEMM_FUNC_SPARSE2 macro (src/cuda_hgemm/src/main.cu:7, restated below) and hands it to a function that takes the
+    harness's function-pointer type (src/cuda_hgemm/src/common/tester.h:166): the boundary claim is checked by the
+    compiler, not only written."""
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc not found")
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    shim = re.search(r"```cpp\n(// src/cuda_hgemm/src/mma/smat_b200_shim.cu.*?)```", text, flags=re.S).group(1)
+    shim = "\n".join(l for l in shim.split("\n") if not l.startswith("// main.cu:"))
+    # stand-in for the reference's common.h: its logging macro and the CUDA half type (common.h:21-63)
+    (tmp_path / "common.h").write_text("#include <cuda_fp16.h>\n#include <stdio.h>\n#include <stdlib.h>\n"
+                                       "#define HLOG(fmt, ...) printf(fmt \"\\n\", ##__VA_ARGS__)\n")
+    (tmp_path / "shim.cu").write_text(shim)
+    (tmp_path / "use.cu").write_text(
+        "#include <cuda_fp16.h>\n#include <stddef.h>\n"
+        "#define HGEMM_FUNC_SPARSE2(name) void name(half *bcsrValuesA, int *bcsrRowPtrA, int *bcsrColIdxA, half *B, half *C, "
+        "size_t M, size_t N, size_t K, size_t nonzeroBlocks, int* blockInfo, int* relativeBlockIndexMapping)\n"
+        "HGEMM_FUNC_SPARSE2(smatB200Kernel);\n"
+        "typedef void (*sparse2_fn)(half *, int *, int *, half *, half *, size_t, size_t, size_t, size_t, int *, int *);\n"
+        "sparse2_fn pick() { return smatB200Kernel; }\n")
+    for src in ("shim.cu", "use.cu"):
+        subprocess.check_call([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-c", "-I", str(tmp_path),
+                               "-I", os.path.join(ROOT, "include"), "-o", str(tmp_path / (src + ".o")), str(tmp_path / src)])

@@ -137,7 +137,7 @@ def test_csr_to_bcsr_against_dense_construction():
 
 
 def test_band_config_block_count():
-    """Config 1: 9 blocks per block-row minus the 20 cut off at the two edges."""
+    """The band matrix (n = 4096, half-bandwidth 64): 9 blocks per block-row minus the 20 cut off at the two edges."""
     p = gen.make_config("band")
     brp, bci, _ = oracle.csr_to_bcsr(p.M, p.K, p.rowptr, p.colidx, p.vals)
     assert len(bci) == 2284 and brp[-1] == 2284

@@ -44,6 +44,10 @@ METRIC = "SpMM effective TFLOP/s (nonzero-block FLOPs)"
 NCU_TRAFFIC_BYTES = {
     # 117.86 MB (113.68 read + 4.17 written, mean of two launches) measured at scale 0.25 (nnzb 204859), scaled by nnzb to the
     # full-size matrix (3548444 blocks): every block is read once per launch and dominates the traffic
+    # block-sparse layer, full size: dram__bytes_read.sum + dram__bytes_write.sum of the SpMM kernel (1043.2 + 59.5 MB, mean of three
+    # launches, captured at full size: the two counters take one pass).  2.8x the algorithmic bytes: B (235 MB) does not fit L2 and
+    # is streamed from HBM once per round of work items (3.5 rounds)
+    ("llm", 1.0, 1): 1102730000,
     ("uniform", 1.0, 1): int(117.86e6 * 3548444 / 204859),
     ("uniform", 0.25, 1): int(117.86e6),
 }

@@ -18,6 +18,7 @@
 
 #include <new>
 
+#include <cstdio>
 #include <cstdlib>
 #include <vector>
 #include <utility>
@@ -324,7 +325,8 @@ plan_tall_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx,
                             }
                         }
                         const uint32_t pos = 2u * (uint32_t)(gfirst - rfirst + b);
-                        steps[gs + s] = make_uint4((uint32_t)(w0 + i0 + 4 * qd) << 4, pos, (uint32_t)taken, 0u);
+                        steps[gs + s] = make_uint4((uint32_t)(w0 + i0 + 4 * qd) << 4, pos, (uint32_t)taken,
+                                                    (part[0] ? 1u : 0u) | (part[1] ? 2u : 0u) | (part[2] ? 4u : 0u) | (part[3] ? 8u : 0u));
                         // what each MMA-issuing warp needs of the step: warp m owns block-rows 2m, 2m + 1
                         const uint32_t pre1 = (uint32_t)__popc(part[0]), pre2 = pre1 + (uint32_t)__popc(part[1]),
                                        pre3 = pre2 + (uint32_t)__popc(part[2]);
@@ -366,9 +368,50 @@ plan_tall_kernel(const int* __restrict__ rowptr, const int* __restrict__ colidx,
             steps_done += tot_s;
             __syncthreads();
         }
-        if (!FILL && threadIdx.x == 0) gsp[g + 1] = steps_done;
+        // The kernel hands steps to its MMA warps two at a time: a group with an odd number of steps gets one more
+        // without blocks (no panel is fetched for it).
+        if (!FILL && threadIdx.x == 0) gsp[g + 1] = (steps_done + 1) & ~1;
+        if (FILL && threadIdx.x == 0 && (steps_done & 1)) {
+            steps[gs + steps_done] = make_uint4(0u, 2u * (uint32_t)(gfirst - rfirst + blocks_done), 0u, 0u);
+            uint4* wdst = winfo + 4 * (size_t)(gs + steps_done);
+            for (int v = 0; v < 4; v++) wdst[v] = make_uint4(0u, 0u, 0u, 0u);
+        }
     }
     if (!FILL && blockIdx.x == 0 && threadIdx.x == 0) gsp[0] = 0;
+}
+
+// Tall plans, last pass: the kernel hands its MMA warps the steps two at a time, so what each warp has to issue for a
+// pair is listed here once, ready to use.  One thread per (pair, warp m): from the two steps' words (bits 2s, 2s + 1
+// = rows 2m, 2m + 1 have a block in sub-column s; bits [8 + 5s, 13 + 5s) = position of the first of them among the
+// step's blocks) to four words holding up to eight 16-bit entries, one per MMA, in (step, sub-column) order:
+//   bits [0, 6)  block position in the pair's two block slots (24 * step + position in the step)
+//   bits [6, 9)  panel sub-column, 4 * step + s            bit 9  accumulator of row 2m + 1 (else 2m)
+//   bit 10       both rows (one MMA of 32 accumulator columns)
+// and the number of entries in bits [28, 32) of word 0 (the spare bits of its second entry).
+__global__ void __launch_bounds__(256) tall_pair_kernel(const uint32_t* __restrict__ wstep, uint4* __restrict__ winfo,
+                                                       const int* __restrict__ gsp, int n_groups) {
+    const int pairs = __ldg(gsp + n_groups) >> 1;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < pairs * 16; i += gridDim.x * blockDim.x) {
+        const int pr = i >> 4, m = i & 15;
+        uint32_t out[4] = {0u, 0u, 0u, 0u};
+        if (m < kTallRows / 2) {
+            uint32_t n = 0;
+            for (uint32_t st = 0; st < 2; st++) {
+                const uint32_t x = __ldg(wstep + ((size_t)(2 * pr) + st) * 16 + m);
+                for (uint32_t sub = 0; sub < 4; sub++) {
+                    const uint32_t own = (x >> (2 * sub)) & 3u;
+                    if (!own) continue;
+                    const uint32_t q = (x >> (8 + 5 * sub)) & 31u;
+                    const uint32_t e = (st * (uint32_t)kTallBlocksPerStep + q) | ((4 * st + sub) << 6) | ((own == 2u ? 1u : 0u) << 9) |
+                                       ((own == 3u ? 1u : 0u) << 10);
+                    out[n >> 1] |= e << (16 * (n & 1));
+                    n++;
+                }
+            }
+            out[0] |= n << 28;
+        }
+        winfo[(size_t)pr * 16 + m] = make_uint4(out[0], out[1], out[2], out[3]);
+    }
 }
 
 // One warp per step of a tall plan: copies the step's value blocks to their place in the packed stream (32-byte swizzle).
@@ -530,7 +573,8 @@ int plan_count_tall_async(const int* rowptr, const int* colidx, size_t K, size_t
 }
 
 int plan_fill_tall_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
-                         size_t rg, const int* gsp, void* steps, void* winfo, int* blk, cudaStream_t stream, const DeviceCtx* ctx_in) {
+                         size_t rg, const int* gsp, void* steps, void* wstep, void* winfo, int* blk, cudaStream_t stream,
+                         const DeviceCtx* ctx_in) {
     const DeviceCtx* ctx = nullptr;
     if (int rc = plan_launch_setup(ctx_in, &ctx)) return rc;
     const size_t n_groups = (brow_end - brow_begin + rg - 1) / rg;
@@ -541,7 +585,10 @@ int plan_fill_tall_async(const int* rowptr, const int* colidx, size_t K, size_t 
     plan_tall_kernel<true><<<grid, kTallPlanThreads, smem_fill, stream>>>(rowptr, colidx, (int)brow_begin, (int)brow_end, (int)rg,
                                                                          kTallBlocksPerStep, (int)(K / 16), (int)n_groups,
                                                                          const_cast<int*>(gsp), reinterpret_cast<uint4*>(steps),
-                                                                         reinterpret_cast<uint4*>(winfo), blk, (int)nnzb, ctx->d_status);
+                                                                         reinterpret_cast<uint4*>(wstep), blk, (int)nnzb, ctx->d_status);
+    count_launch();
+    tall_pair_kernel<<<ctx->sm_count * 4, 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(wstep), reinterpret_cast<uint4*>(winfo), gsp,
+                                                            (int)n_groups);
     count_launch();
     SMAT_CUDA_TRY(cudaGetLastError());
     return SMAT_OK;
@@ -700,48 +747,88 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
             }
         }
     }
-    // Tall plan: when a group's quads hold several blocks each but are far from full, and a work item is long, the
-    // tensor-memory-operand kernel with taller groups (fewer panel fetches per block, no panel traffic through the
-    // shared-memory operand port) is the faster one.  smat_spmm_set_variant(4) forces it, 1..3 exclude it.
+    // Tall plan: groups of up to 24 block-rows for the kernel that reads the B panels from tensor memory.  Its steps
+    // cost a little more than those of the 16-row kernels (measured ~600 against ~540 cycles, the latter growing with
+    // the blocks of the step: ~42 cycles each, the shared-memory operand port), so it pays where taller groups mean
+    // fewer steps: matrices whose quads mostly hold a block (a block-sparse layer, a reordered random matrix: three
+    // quarters of the steps), not scattered ones (as many steps as before) and not dense clusters (steps of 32 blocks
+    // already).  Both plans are counted and the estimates compared; smat_spmm_set_variant(4) forces a tall plan,
+    // 1..3 exclude it.
     bool tall = false;
     size_t rg_used = rg;
-    if (rc == SMAT_OK && !balanced && !p->v.sched_list && total_steps > 0) {
-        // (measured so far the 16-row kernels are still the faster ones on every configuration of the benchmark, so
-        // a tall plan is only made on request)
-        tall = g_spmm_variant == 4 && brow_end > brow_begin;
-    }
-    if (tall) {
-        const size_t rows = brow_end - brow_begin, tiles = ((N_hint ? N_hint : 128) + 127) / 128;
+    const size_t rows = brow_end - brow_begin, tiles = ((N_hint ? N_hint : 128) + 127) / 128;
+    const bool tall_forced = g_spmm_variant == 4;
+    const bool tall_possible = rc == SMAT_OK && !balanced && !p->v.sched_list && total_steps > 0 && rows > 0 &&
+                               (tall_forced || (g_spmm_variant == 0 && cap == (size_t)kPlanBlocksPerStep && rows >= 16 && N_hint >= 128 &&
+                                                (size_t)total_steps * tiles >= 64 * (size_t)ctx->sm_count));
+    if (tall_possible) {
+        // Height of the groups: what a launch costs is about (rounds of work items) x (steps of an item) x (bytes a
+        // step moves from L2: a 16 KB panel and its blocks).  The steps of an item hardly change with the height as
+        // long as most quads hold a block, so compare rounds x bytes per step.
+        size_t rg_tall = kTallRows;
         double best = 0.0;
-        for (size_t r = kTallRows; r >= 16; r--) {
+        const double steps_per_group = (double)total_steps / (double)sz.n_groups;
+        for (size_t r = kTallRows; r >= 16; r -= 2) {
             const size_t groups = (rows + r - 1) / r;
-            const double cost = rounds_for(groups * tiles, (size_t)ctx->sm_count, true, (size_t)total_steps / sz.n_groups, false);
+            // (blocks per step of a full group: the heaviest item sets the time of a round)
+            const double blocks_per_step =
+                (double)range_blocks / (double)rows * (double)(r < rows ? r : rows) / (steps_per_group > 1.0 ? steps_per_group : 1.0);
+            const double cost = rounds_for(groups * tiles, (size_t)ctx->sm_count, true, (size_t)steps_per_group, false) *
+                                (16384.0 + 512.0 * blocks_per_step);
             if (r == (size_t)kTallRows || cost < best * 0.97) {
                 best = cost;
-                rg_used = r;
+                rg_tall = r;
             }
         }
-        if (const char* ev = std::getenv("SMAT_TALL_ROWS")) {
+        if (const char* ev = std::getenv("SMAT_TALL_ROWS")) {  // tuning knob
             const int v = std::atoi(ev);
-            if (v >= 1 && v <= kTallRows) rg_used = (size_t)v;
+            if (v >= 1 && v <= kTallRows) rg_tall = (size_t)v;
         }
-        // the group count changes with the height: count again into a buffer of the right size
-        cudaFree(p->gsp_buffer);
-        p->gsp_buffer = nullptr;
-        sz = plan_sizes(nnzb, brow_begin, brow_end, rg_used);
-        e = cudaMalloc(&p->gsp_buffer, sz.gsp_bytes);
+        // the group count changes with the height: count into a buffer of its own, kept if the tall plan is taken
+        const PlanSizes sz_tall = plan_sizes(nnzb, brow_begin, brow_end, rg_tall);
+        void* gsp_tall = nullptr;
+        int tall_total_and_max[2] = {0, 0};
+        e = cudaMalloc(&gsp_tall, sz_tall.gsp_bytes);
         if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan allocation failed: %s", cudaGetErrorString(e));
-        gsp = static_cast<int*>(p->gsp_buffer);
         if (rc == SMAT_OK)
-            rc = plan_count_tall_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, rg_used, gsp, (cudaStream_t)stream);
+            rc = plan_count_tall_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, rg_tall, static_cast<int*>(gsp_tall),
+                                       (cudaStream_t)stream);
         if (rc == SMAT_OK) {
-            e = cudaMemcpyAsync(total_and_max, gsp + sz.n_groups, 2 * sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+            e = cudaMemcpyAsync(tall_total_and_max, static_cast<int*>(gsp_tall) + sz_tall.n_groups, 2 * sizeof(int), cudaMemcpyDeviceToHost,
+                                (cudaStream_t)stream);
             if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
             if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan build failed: %s", cudaGetErrorString(e));
         }
-        cap = kTallBlocksPerStep;
+        if (rc == SMAT_OK) {
+            const double per_step = (double)range_blocks / (double)total_steps;
+            const double est16 = rounds_for(sz.n_groups * tiles, (size_t)ctx->sm_count, true, (size_t)steps_per_group, false) * steps_per_group *
+                                 (per_step * 42.0 > 540.0 ? per_step * 42.0 : 540.0);
+            const double steps_per_tall = (double)tall_total_and_max[0] / (double)sz_tall.n_groups;
+            const double est_tall =
+                rounds_for(sz_tall.n_groups * tiles, (size_t)ctx->sm_count, true, (size_t)steps_per_tall, false) * steps_per_tall * 600.0;
+            tall = tall_forced || est_tall < 0.95 * est16;
+            if (std::getenv("SMAT_PLAN_DEBUG"))
+                fprintf(stderr, "[smat plan] estimates: 16-row %.0f cycles, tall (rg %zu, %d steps) %.0f cycles -> %s\n", est16, rg_tall,
+                        tall_total_and_max[0], est_tall, tall ? "tall" : "16-row");
+        }
+        if (rc == SMAT_OK && tall) {
+            cudaFree(p->gsp_buffer);
+            p->gsp_buffer = gsp_tall;
+            gsp = static_cast<int*>(gsp_tall);
+            sz = sz_tall;
+            rg_used = rg_tall;
+            total_and_max[0] = tall_total_and_max[0];
+            total_and_max[1] = tall_total_and_max[1];
+            cap = kTallBlocksPerStep;
+        } else {
+            cudaFree(gsp_tall);
+        }
     }
     const int steps_final = total_and_max[0];
+    if (std::getenv("SMAT_PLAN_DEBUG"))
+        fprintf(stderr, "[smat plan] rows %zu blocks %zu: 16-row plan rg %zu steps %d cap %zu balanced %d listed %d; tall %d rg %zu steps %d max/group %d\n",
+                brow_end - brow_begin, range_blocks, rg, total_steps, cap, (int)balanced, p->v.sched_list != nullptr, (int)tall, rg_used,
+                steps_final, total_and_max[1]);
     if (rc == SMAT_OK && balanced) {  // two partial tiles per CTA
         cudaFree(p->fix_buffer);
         p->fix_buffer = nullptr;
@@ -749,7 +836,7 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
         if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan allocation failed: %s", cudaGetErrorString(e));
     }
     if (rc == SMAT_OK) {
-        sz = plan_sizes(nnzb, brow_begin, brow_end, rg_used, (size_t)(steps_final > 0 ? steps_final : 1) * (tall ? 5 : 1));
+        sz = plan_sizes(nnzb, brow_begin, brow_end, rg_used, (size_t)(steps_final > 0 ? steps_final : 1) * (tall ? 13 : 1));  // tall: + 64 bytes of per-step words + 128 bytes of the per-pair lists
         e = cudaMalloc(&p->buffer, sz.steps_bytes + sz.blk_bytes + sz.packed_bytes);
         if (e != cudaSuccess) rc = fail(SMAT_ERR_CUDA, "plan allocation failed: %s", cudaGetErrorString(e));
     }
@@ -778,8 +865,10 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
     p->v.cap = cap;
     p->v.tall = tall;
     if (tall) {
-        p->v.winfo = b + (size_t)(steps_final > 0 ? steps_final : 1) * 16;  // behind the step records, in the same region
-        rc = plan_fill_tall_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, rg_used, gsp, const_cast<void*>(p->v.steps),
+        // behind the step records, in the same region: the per-step words (only read while the plan is built), then the per-pair lists
+        char* wstep = b + (size_t)(steps_final > 0 ? steps_final : 1) * 16;
+        p->v.winfo = wstep + (size_t)(steps_final > 0 ? steps_final : 1) * 64;
+        rc = plan_fill_tall_async(bcsrRowPtrA, bcsrColIdxA, K, nnzb, brow_begin, brow_end, rg_used, gsp, const_cast<void*>(p->v.steps), wstep,
                                   const_cast<void*>(p->v.winfo), const_cast<int*>(p->v.blk), (cudaStream_t)stream);
         if (rc == SMAT_OK)
             rc = pack_values_tall_async(bcsrRowPtrA, bcsrValuesA, gsp, p->v.steps, p->v.blk, const_cast<void*>(p->v.packed),

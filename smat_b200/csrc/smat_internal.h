@@ -122,11 +122,11 @@ struct PlanView {
     size_t K = 0, nnzb = 0, brow_begin = 0, brow_end = 0, n_groups = 0, rg = kPlanRowsPerGroup;
     size_t total_steps = 0;  // number of steps of the range when the host knows it, else 0
     size_t cap = kPlanBlocksPerStep;  // most blocks of a step: kPlanBlocksPerStep or kPlanBlocksPerStepDense
-    // Tall plan: groups of rg <= kTallRows block-rows, at most kTallBlocksPerStep blocks per step.  A step record is
-    // {element column of the quad, position of the first block in the packed stream in 256-byte units, number of
-    // blocks, 0}; winfo holds 16 words per step: word m < 12 tells the warp that owns block-rows 2m, 2m + 1 what to
-    // multiply (bits 2s, 2s + 1: its rows that have a block in sub-column s; bits [8 + 5s, 13 + 5s): position in the
-    // step's block sequence of the first of them), word 12 the non-empty sub-columns (bit s).
+    // Tall plan: groups of rg <= kTallRows block-rows with an even number of steps, at most kTallBlocksPerStep blocks
+    // per step.  A step record is {element column of the quad, position of the first block in the packed stream in
+    // 256-byte units, number of blocks (0: a step that only pads its group), non-empty sub-columns (bit s)}; winfo
+    // holds 16 x 16 bytes per PAIR of steps: entry m < 12 lists the MMAs of the warp that owns block-rows 2m, 2m + 1
+    // (layout: tall_pair_kernel in plan.cu).
     bool tall = false;
     const void* winfo = nullptr;
     // The heaviest group has many times the average number of steps: deal out equal step ranges instead of items
@@ -162,7 +162,7 @@ int pack_values_async(const int* rowptr, const void* vals, const int* gsp, const
 int plan_count_tall_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
                           size_t rg, int* gsp, cudaStream_t stream, const DeviceCtx* ctx = nullptr);
 int plan_fill_tall_async(const int* rowptr, const int* colidx, size_t K, size_t nnzb, size_t brow_begin, size_t brow_end,
-                         size_t rg, const int* gsp, void* steps, void* winfo, int* blk, cudaStream_t stream,
+                         size_t rg, const int* gsp, void* steps, void* wstep, void* winfo, int* blk, cudaStream_t stream,
                          const DeviceCtx* ctx = nullptr);
 int pack_values_tall_async(const int* rowptr, const void* vals, const int* gsp, const void* steps, const int* blk, void* packed,
                            size_t brow_begin, size_t brow_end, size_t rg, size_t nnzb, cudaStream_t stream,

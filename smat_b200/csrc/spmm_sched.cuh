@@ -19,6 +19,11 @@ __device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
     return v;
 }
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
 __device__ __forceinline__ void st_shared_u16(uint32_t addr, unsigned short v) {
     asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(v) : "memory");
 }
@@ -28,7 +33,7 @@ __device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
 
 
 #ifdef SMAT_PROFILE
-// Development aid (compiled out by default): cycles spent and number of waits that did not pass at once, per wait site.
+// Development aid (compiled out by default): cycles spent in waits per wait site, summed by the kernels at their end.
 static __device__ unsigned long long g_wait_prof[64];
 #endif
 
@@ -38,9 +43,6 @@ __device__ __forceinline__ void wait_bar(uint32_t bar, uint32_t parity, uint32_t
     if (mbar_try_wait(bar, parity)) return;
     if (ld_shared_u32(abort_addr)) return;
     const long long t0 = clock64();
-#ifdef SMAT_PROFILE
-    struct Acc { long long t0; int code; __device__ ~Acc() { atomicAdd(&g_wait_prof[code], (unsigned long long)(clock64() - t0)); atomicAdd(&g_wait_prof[32 + code], 1ull); } } acc_{t0, code};
-#endif
     // suspended waits: the warp sleeps in hardware until the phase completes or ~2 us pass
     while (!mbar_try_wait_suspend(bar, parity, 2000u)) {
         if (ld_shared_u32(abort_addr)) return;
@@ -98,6 +100,7 @@ template <int SCHED>
 struct SegGen {
     const int* gsp;
     int n_tiles, n_items, n_ctas, cta, item, n_full, P;
+    int quantum = 1;  // round-robin schedule: cut items at multiples of this many steps
     bool tail_done;
     Flat flat;
     long long p, p_begin, p_end;
@@ -143,8 +146,9 @@ struct SegGen {
         const int gg = (n_full + i) / n_tiles;
         const int gs = __ldg(gsp + gg), ns = __ldg(gsp + gg + 1) - gs;
         s.item = n_full + i; s.gs = gs; s.ns = ns; s.cut = P > 1; s.slot = cta;
-        s.k0 = (int)((unsigned)ns * (unsigned)j / (unsigned)P);  // P <= kMaxTailParts: the products fit 32 bits
-        s.k1 = (int)((unsigned)ns * (unsigned)(j + 1) / (unsigned)P);
+        const unsigned nq = (unsigned)(ns / quantum);  // P <= kMaxTailParts: the products fit 32 bits
+        s.k0 = (int)(nq * (unsigned)j / (unsigned)P) * quantum;
+        s.k1 = (j + 1 == P) ? ns : (int)(nq * (unsigned)(j + 1) / (unsigned)P) * quantum;
         return true;
     }
 };

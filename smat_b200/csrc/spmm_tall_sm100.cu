@@ -11,23 +11,31 @@
 //   * Streaming the panels L2 -> shared memory sustains ~70 bytes/cycle/SM (19-20 TB/s over the chip).  The panel
 //     traffic of a launch is (block-rows / rows per group) x K x N x 2 bytes, so taller groups cut it in proportion;
 //     tensor memory (512 columns) holds 24 accumulators of 16 columns plus a ring of four panels.
-//   * A thread can issue a tcgen05.mma only every ~70-190 cycles, different warps issue concurrently, and
-//     tcgen05.commit costs the tensor pipe nothing measurable.  So 12 warps issue, each owning two accumulator rows
-//     (all MMAs into one accumulator come from one thread, in order: results do not depend on warp timing), and
-//     each computes the operands of a step's (at most four) MMAs first and then issues them back to back.
+//   * Issuing a tcgen05.mma costs a thread ~15 cycles when its operand registers are left alone, ~90 more when one
+//     of them is written again right away, and each branch or register operation around it a few cycles more; with
+//     12 warps issuing at once the tensor pipe (9 cycles per MMA) is what each of them waits for.  tcgen05.commit and
+//     a barrier wait cost the issuing thread ~100-200 cycles each, the tensor pipe nothing.  So 12 warps issue, each
+//     owning two accumulator rows (all MMAs into one accumulator come from one thread, in order: results do not
+//     depend on warp timing), the steps are handed over two at a time, and the plan lists each warp's MMAs of a pair
+//     of steps so that the warp works the list off in straight-line code.
 //
 // Pipeline per step (four block-columns of a group), all hand-overs by mbarriers, every wait bounded:
-//   loader warps (4, one thread each, every 4th step): TMA box {64 k, 128 n} -> panel slot (4 slots), bulk copy of the
-//     step's packed A blocks -> block slot (8 slots), the step's row masks -> a meta slot;
-//   copier warps (4, one thread each, warp j owns panel slot j): wait panel + blocks, tcgen05.cp the non-empty
-//     sub-columns shared -> tensor memory ring (slot j), commit -> cp_done of the step's pair.  That frees the shared panel
-//     slot for the loader and tells the MMA warps that panel AND blocks of the step are in place;
-//   MMA warps (12): per PAIR of steps wait cp_done once, read the masks, issue, commit -> step_done (a plain arrive
-//     when the warp had no block in the pair); step_done frees the block slots (loader) and the tensor-memory panel
-//     slots (copier) of the pair;
+//   loader warps (4, one thread each, every 4th step): TMA box {64 k, 128 n} -> panel slot (6 slots), bulk copy of the
+//     step's packed A blocks -> block slot (10 slots) and, with the first step of a pair, of the pair's MMA lists;
+//   copier warps (4, one thread each, every 4th step): wait panel + blocks, tcgen05.cp the non-empty sub-columns
+//     shared -> tensor memory ring, commit -> cp_done of the step's pair.  That frees the shared panel slot for the
+//     loader and tells the MMA warps that panels AND blocks of the pair are in place;
+//   MMA warps (one per two accumulator rows): per PAIR of steps wait cp_done once, read their list, issue, commit ->
+//     step_done (a plain arrive when the warp had no block in the pair); step_done frees the block slots (loader)
+//     and the tensor-memory panel slots (copier) of the pair;
 //   epilogue warps (8 = two per tensor-memory lane quarter, alternating block-rows): tcgen05.ld -> zero the
-//     accumulator -> fp16 -> shared-memory tile -> one TMA store per block-row; cut items write fp32 partial tiles.
-// Scheduling is the round-robin-with-cut-last-round scheme of spmm_sm100.cu (SegGen<0>).
+//     accumulator -> fp16 -> 4-byte stores to C; cut items write fp32 partial tiles.
+// Groups of at most 16 or 20 block-rows use fewer accumulators and a longer tensor-memory panel ring (8 or 6 slots
+// instead of 4).  Scheduling is the round-robin-with-cut-last-round scheme of spmm_sm100.cu (SegGen<0>); the plan
+// pads every group to an even number of steps and items are cut at even positions, so a pair never spans two items.
+// What bounds the kernel on the block-sparse layer it was written for: every step moves 16 KB of panel and ~10 KB of
+// blocks from L2 to the SM, and 148 SMs doing that every ~600 cycles is ~12 TB/s, two thirds of what L2 delivered
+// to a pure streaming kernel (19-20 TB/s); the rest is latency of the chain copy -> MMAs -> slot release.
 #include <cuda_fp16.h>
 #include <limits.h>
 #include <stdlib.h>
@@ -44,33 +52,47 @@ using namespace ptx;
 
 namespace {
 
-constexpr int TRG = kTallRows;   // block-rows per work item (accumulators)
 constexpr int NLW = 4;           // loader warps
-constexpr int NCW = 4;           // copier warps = panel slots
-constexpr int NMW = TRG / 2;     // MMA warps, two accumulator rows each
+constexpr int NCW = 4;           // copier warps
 constexpr int NEW = 8;           // epilogue warps
-constexpr int kTallThreads = (NLW + NCW + NMW + NEW) * 32;
-constexpr uint32_t PS = 8;                                   // panel slots in shared memory
-constexpr uint32_t TS_ = 4;                                  // panel slots in tensor memory
-constexpr uint32_t BS = 8;                                   // block slots
+constexpr uint32_t PS = 6;                                   // panel slots in shared memory (a slot is free once copied to tensor memory)
+constexpr uint32_t BS = 10;                                  // block slots (held until the step's MMAs have completed)
 constexpr uint32_t PANEL_BYTES = 128 * 64 * 2;               // 128 n x 64 k fp16
 constexpr uint32_t BLK_SLOT_BYTES = kTallBlocksPerStep * 512;
 constexpr uint32_t OFF_PANEL = 0;
 constexpr uint32_t OFF_BLK = OFF_PANEL + PS * PANEL_BYTES;
-constexpr uint32_t META_BYTES = 64;                           // per step: 12 per-warp words + the non-empty sub-columns
+constexpr uint32_t META_BYTES = 256;                          // per pair of steps: the MMA lists of the 12 issuing warps
 constexpr uint32_t OFF_META = OFF_BLK + BS * BLK_SLOT_BYTES;
-constexpr uint32_t OFF_BAR = OFF_META + BS * META_BYTES;
-constexpr uint32_t NPAIR = BS / 2;                            // pairs of steps whose blocks are in flight
-constexpr uint32_t N_BARS = PS + BS + NPAIR + NPAIR + 2;
+constexpr uint32_t OFF_SUBS = OFF_META + (BS / 2) * META_BYTES;  // per step: its non-empty sub-columns (written by the loader)
+constexpr uint32_t OFF_BAR = OFF_SUBS + BS * 8;
+// A thread that waits on an mbarrier by parity must see every phase of it.  Loader j and copier j handle the steps
+// st = j (mod 4), so a "full" barrier ring is as long as lcm(slots, 4): barrier st % ring then always belongs to
+// the same loader and the same copier.  The per-pair rings (8 barriers) are visited by a loader or copier at every
+// other pair, i.e. each barrier of its parity class once per 8 pairs: once per phase.
+constexpr uint32_t FP = 12;                                   // full_p ring: lcm(PS, 4)
+constexpr uint32_t FB = 20;                                   // full_b ring: lcm(BS, 4)
+constexpr uint32_t NPAIR = 8;                                 // cp_done / step_done rings (pairs of steps)
+constexpr uint32_t N_BARS = FP + FB + NPAIR + NPAIR + 2;
 constexpr uint32_t OFF_MISC = OFF_BAR + N_BARS * 8;
 constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;        // slack for the manual 1024-byte alignment
-constexpr uint32_t TMEM_ACC = 0;                             // accumulators: TRG x 16 columns
-constexpr uint32_t TMEM_PANELS = TRG * 16;                   // panel ring: TS_ x 32 columns
+constexpr uint32_t TMEM_ACC = 0;                             // accumulators: one per block-row, 16 columns each
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
-static_assert(TMEM_PANELS + TS_ * 32 <= 512, "tensor-memory budget");
-static_assert(PS % NCW == 0 && BS % NCW == 0 && PS % NLW == 0 && BS % NLW == 0 && PS == BS && TS_ == 4 && NCW == 4,
-              "the barrier phase arithmetic below assumes these (a thread must see every phase of a barrier it waits on)");
-static_assert(TRG * 16 * 128 <= kFixSlotFloats, "a partial tile must fit a scratch slot");
+static_assert(NLW == 4 && NCW == 4 && FP % PS == 0 && FP % 4 == 0 && FB % BS == 0 && FB % 4 == 0 && PS % 2 == 0 && BS % 2 == 0 &&
+                  NPAIR % 2 == 0 && NPAIR > BS / 2,
+              "the barrier phase arithmetic below assumes these");
+static_assert(kTallRows * 16 * 128 <= kFixSlotFloats, "a partial tile must fit a scratch slot");
+
+// Shape of a work item: TRG block-rows (accumulators), two of them per MMA-issuing warp.  What tensor memory the
+// accumulators leave holds the panel ring (32 columns a slot, at most 8 slots).
+template <int TRG>
+struct Shape {
+    static constexpr int NMW = TRG / 2;
+    static constexpr int kThreads = (NLW + NCW + NMW + NEW) * 32;
+    static constexpr uint32_t TMEM_PANELS = TRG * 16;
+    static constexpr uint32_t TS_ = (512 - TRG * 16) / 32 < 8 ? (512 - TRG * 16) / 32 : 8;
+    static_assert(TRG % 2 == 0 && TRG <= kTallRows && kThreads <= 1024, "shape");
+    static_assert(TS_ >= 4 && TS_ % 2 == 0 && TS_ / 2 < NPAIR && TMEM_PANELS + TS_ * 32 <= 512, "tensor-memory budget: whole pairs of panel slots");
+};
 
 struct TallStep {
     int live;
@@ -80,36 +102,57 @@ struct TallStep {
     uint4 a;      // {element column, packed position (256-byte units), blocks, 0}
 };
 
-__global__ void __launch_bounds__(kTallThreads, 1)
+template <int TRG>
+__global__ void __launch_bounds__((Shape<TRG>::kThreads), 1)
 spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* __restrict__ packed,
                       const uint4* __restrict__ steps, const uint4* __restrict__ winfo, const int* __restrict__ gsp,
                       const int* __restrict__ rowptr,
                       __half* __restrict__ C, size_t ldc, int brow_begin, int brow_end, int rg, int N, int n_tiles, int n_items,
                       int tail_parts, uint32_t panel_bytes, float* __restrict__ fix_scratch, int* status, int pf) {
+    constexpr int NMW = Shape<TRG>::NMW;
+    constexpr uint32_t TS_ = Shape<TRG>::TS_, TMEM_PANELS = Shape<TRG>::TMEM_PANELS;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar0 = base + OFF_BAR;
     auto full_p = [&](uint32_t s) { return bar0 + 8 * s; };
-    auto full_b = [&](uint32_t s) { return bar0 + 8 * (PS + s); };
+    auto full_b = [&](uint32_t s) { return bar0 + 8 * (FP + s); };
     // The MMA warps are handed the steps two at a time (pair p = steps 2p, 2p + 1 of the CTA's sequence, whatever
     // work items they belong to): measured, a barrier wait or a commit costs the issuing thread about as much as an
     // MMA (~100 cycles), so one of each per step and warp would hold the whole pipeline back.
-    auto cp_done = [&](uint32_t p) { return bar0 + 8 * (PS + BS + p); };            // both panels of pair p (mod NPAIR) copied
-    auto step_done = [&](uint32_t p) { return bar0 + 8 * (PS + BS + NPAIR + p); };  // all MMAs of pair p (mod NPAIR) completed
-    const uint32_t acc_full = bar0 + 8 * (PS + BS + 2 * NPAIR), acc_empty = acc_full + 8;
+    auto cp_done = [&](uint32_t p) { return bar0 + 8 * (FP + FB + p); };            // both panels of pair p (mod NPAIR) copied
+    auto step_done = [&](uint32_t p) { return bar0 + 8 * (FP + FB + NPAIR + p); };  // all MMAs of pair p (mod NPAIR) completed
+    const uint32_t acc_full = bar0 + 8 * (FP + FB + 2 * NPAIR), acc_empty = acc_full + 8;
     const uint32_t tmem_slot = base + OFF_MISC;
     const uint32_t abort_addr = base + OFF_MISC + 4;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-#ifdef SMAT_PROFILE
+#ifdef SMAT_PROFILE  // development aid: cycles this thread spends in each kind of wait (mbarrier.try_wait may itself suspend it)
     const long long t_kernel0 = clock64();
+    unsigned int prof_c[12] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    long long prof_t = 0;
+#define PROF_MARK(code)                                          \
+    do {                                                         \
+        const long long t_ = clock64();                          \
+        if (code) prof_c[code] += (unsigned int)(t_ - prof_t);   \
+        prof_t = t_;                                             \
+    } while (0)
+#define TWAIT(bar, par, code)                                    \
+    do {                                                         \
+        const long long t_ = clock64();                          \
+        wait_bar(bar, par, abort_addr, status, code);            \
+        prof_c[code] += (unsigned int)(clock64() - t_);          \
+    } while (0)
+#else
+#define TWAIT(bar, par, code) wait_bar(bar, par, abort_addr, status, code)
+#define PROF_MARK(code)
 #endif
     const int n_full = n_items / (int)gridDim.x * (int)gridDim.x;  // items of the complete rounds
     auto make_gen = [&]() {
         SegGen<0> sg;
         sg.gsp = gsp; sg.n_tiles = n_tiles; sg.n_items = n_items; sg.n_ctas = (int)gridDim.x; sg.cta = (int)blockIdx.x;
         sg.item = (int)blockIdx.x; sg.n_full = n_full; sg.P = tail_parts; sg.tail_done = false;
+        sg.quantum = 2;  // groups hold an even number of steps (the plan pads them) and are cut at even positions
         sg.flat.gsp = gsp; sg.flat.n_tiles = n_tiles; sg.flat.n_groups = 0; sg.flat.total = 0; sg.g = 0;
         sg.p = sg.p_begin = sg.p_end = 0;
         sg.list = nullptr; sg.li = sg.li_end = 0; sg.lt = 0;
@@ -117,8 +160,8 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
     };
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < PS; s++) mbar_init(full_p(s), 1);
-        for (uint32_t s = 0; s < BS; s++) mbar_init(full_b(s), 1);
+        for (uint32_t s = 0; s < FP; s++) mbar_init(full_p(s), 1);
+        for (uint32_t s = 0; s < FB; s++) mbar_init(full_b(s), 1);
         for (uint32_t s = 0; s < NPAIR; s++) { mbar_init(cp_done(s), 2); mbar_init(step_done(s), NMW); }
         mbar_init(acc_full, NMW);
         mbar_init(acc_empty, NEW);
@@ -186,18 +229,25 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
                     TallStep& r = rec[a];
                     if (!r.live) { more = false; break; }
                     const uint32_t ps = r.st % PS, bs = r.st % BS, pi = r.st >> 1;
-                    // Blocks first: their slot (and the meta slot) is free once the MMAs of the step BS positions back
-                    // (pair pi - NPAIR) have completed; it rarely has to be waited for.
-                    if (pi >= NPAIR) wait_bar(step_done(pi % NPAIR), ((pi - NPAIR) / NPAIR) & 1, abort_addr, status, 2);
-                    const uint32_t a_bytes = r.a.z * 512u;
-                    mbar_arrive_expect_tx(full_b(bs), a_bytes + META_BYTES);
-                    bulk_load(base + OFF_META + bs * META_BYTES, winfo + 4 * (size_t)r.idx, META_BYTES, full_b(bs));
-                    bulk_load(base + OFF_BLK + bs * BLK_SLOT_BYTES, packed + (size_t)r.a.y * 256, a_bytes, full_b(bs));
-                    // Then the panel, whose slot is what the pipeline usually waits for: it is free once the copy of the
-                    // step PS positions back (pair pi - PS / 2) has left it; nothing but the copy itself follows the wait.
-                    if (pi >= PS / 2) wait_bar(cp_done((pi - PS / 2) % NPAIR), ((pi - PS / 2) / NPAIR) & 1, abort_addr, status, 1);
-                    mbar_arrive_expect_tx(full_p(ps), panel_bytes);
-                    tma_load_2d(base + OFF_PANEL + ps * PANEL_BYTES, &mapB, (int)r.a.x, r.tile * 128, full_p(ps));
+                    const uint32_t a_bytes = r.a.z * 512u;  // 0: a step that only pads its group to an even count
+                    // The panel first (the copier needs it before the MMAs need the blocks): its slot is free once the
+                    // copy of the step PS positions back (pair pi - PS / 2) has left it.
+                    if (r.st >= PS) TWAIT(cp_done((pi - PS / 2) % NPAIR), ((pi - PS / 2) / NPAIR) & 1, 1);
+                    if (a_bytes) {
+                        mbar_arrive_expect_tx(full_p(r.st % FP), panel_bytes);
+                        tma_load_2d(base + OFF_PANEL + ps * PANEL_BYTES, &mapB, (int)r.a.x, r.tile * 128, full_p(r.st % FP));
+                    } else {
+                        mbar_arrive(full_p(r.st % FP));  // no panel: the phase completes at once
+                    }
+                    // Then the blocks and the masks: their slot is free once the MMAs of the step BS positions back
+                    // (pair pi - BS / 2) have completed.
+                    if (r.st >= BS) TWAIT(step_done((pi - BS / 2) % NPAIR), ((pi - BS / 2) / NPAIR) & 1, 2);
+                    st_shared_u32(base + OFF_SUBS + bs * 8, r.a.w);  // for the copier; ordered before its wait by the arrive below
+                    const uint32_t m_bytes = (r.st & 1u) ? 0u : META_BYTES;  // the pair's lists travel with its first step
+                    if (a_bytes + m_bytes) mbar_arrive_expect_tx(full_b(r.st % FB), a_bytes + m_bytes);
+                    else mbar_arrive(full_b(r.st % FB));
+                    if (m_bytes) bulk_load(base + OFF_META + (bs >> 1) * META_BYTES, winfo + 16 * (size_t)(r.idx >> 1), META_BYTES, full_b(r.st % FB));
+                    if (a_bytes) bulk_load(base + OFF_BLK + bs * BLK_SLOT_BYTES, packed + (size_t)r.a.y * 256, a_bytes, full_b(r.st % FB));
                     prefetch(rec[(a + PF) % U]);
                     gen(r);
                 }
@@ -217,13 +267,13 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
             for (uint32_t st = j; st < total; st += NCW) {
                 const uint32_t ps = st % PS, bs = st % BS, pi = st >> 1;
                 // everything that is usually there already first, so that only the copies follow the panel's arrival
-                wait_bar(full_b(bs), (st / BS) & 1, abort_addr, status, 4);
+                TWAIT(full_b(st % FB), (st / FB) & 1, 4);
                 // the tensor-memory slot is free once the MMAs of the step TS_ positions back (pair pi - 2) have completed
-                if (pi >= TS_ / 2) wait_bar(step_done((pi - TS_ / 2) % NPAIR), ((pi - TS_ / 2) / NPAIR) & 1, abort_addr, status, 5);
-                const uint32_t subs = ld_shared_u32(base + OFF_META + bs * META_BYTES + 48);  // non-empty sub-columns
+                if (pi >= TS_ / 2) TWAIT(step_done((pi - TS_ / 2) % NPAIR), ((pi - TS_ / 2) / NPAIR) & 1, 5);
+                const uint32_t subs = ld_shared_u32(base + OFF_SUBS + bs * 8);  // non-empty sub-columns
                 const uint64_t pdesc = smem_desc_k_sw128(base + OFF_PANEL + ps * PANEL_BYTES);
                 const uint32_t tdst = tmem_base + TMEM_PANELS + (st % TS_) * 32;
-                wait_bar(full_p(ps), (st / PS) & 1, abort_addr, status, 3);
+                TWAIT(full_p(st % FP), (st / FP) & 1, 3);
                 tc_fence_after();
 #ifndef SMAT_TALL_NOCP
                 if (subs & 1u) tc_cp_128x256b(tdst, pdesc);
@@ -233,9 +283,6 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
 #endif
                 tc_commit(cp_done(pi % NPAIR));
             }
-            // an odd number of steps leaves the last pair with one step: the copier whose turn the missing step would
-            // have been stands in for its arrival
-            if ((total & 1u) && total % NCW == j) mbar_arrive(cp_done((total >> 1) % NPAIR));
         }
         __syncwarp();
     } else if (warp < NLW + NCW + NMW) {
@@ -253,45 +300,60 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
             constexpr uint32_t IDESC16 = idesc_f16_f32(128, 16), IDESC32 = idesc_f16_f32(128, 32);
             const uint32_t acc_m = tmem_base + TMEM_ACC + 2u * m * 16u;  // this warp's two accumulators
             uint32_t st = 0, it = 0;
-            bool any = false;  // this warp issued an MMA in the current pair
             SegGen<0> sg = make_gen();
             Seg cs;
             while (sg.next(cs)) {
-                wait_bar(acc_empty, (it & 1) ^ 1, abort_addr, status, 6);
+                TWAIT(acc_empty, (it & 1) ^ 1, 6);
                 tc_fence_after();
-                for (int k = cs.k0; k < cs.k1; k++, st++) {
-                    const uint32_t ps = st % TS_, bs = st % BS, pi = st >> 1;
-                    if ((st & 1u) == 0u) {
-                        wait_bar(cp_done(pi % NPAIR), (pi / NPAIR) & 1, abort_addr, status, 7);
-                        tc_fence_after();
-                    }
-                    // this warp's word of the step: bits 2s, 2s + 1 = its rows with a block in sub-column s, bits
-                    // [8 + 5s, 13 + 5s) = position of the first of them among the step's blocks.  (Measured: working the
-                    // four sub-columns out on four lanes and broadcasting the operands by shuffles was 20 % slower --
-                    // a shuffled value is not warp-uniform to the compiler.)
-                    const uint32_t xl = ld_shared_u32(base + OFF_META + bs * META_BYTES + m * 4u);
-                    const uint32_t x = __ballot_sync(0xffffffffu, (xl >> lane) & 1u);
-                    const uint32_t tpanel = tmem_base + TMEM_PANELS + ps * 32;
+                // segments hold an even number of steps and start at an even position: a pair never spans two of them
+                for (int k = cs.k0; k < cs.k1; k += 2, st += 2) {
+                    const uint32_t pi = st >> 1, bs = st % BS;
+                    PROF_MARK(0);
+                    TWAIT(cp_done(pi % NPAIR), (pi / NPAIR) & 1, 7);
+                    tc_fence_after();
+                    // This warp's list for the pair: up to eight 16-bit entries, one per MMA (layout: tall_pair_kernel
+                    // in plan.cu), their number in the top bits of the first word.  Measured: the branches and the
+                    // register arithmetic around a tcgen05.mma cost the issuing thread far more than the instruction
+                    // (~15 cycles), and writing an operand register of an MMA just issued stalls it ~90 cycles.  So
+                    // the plan lists the MMAs, and the list is worked off in straight-line code entered at its length.
+                    const uint4 l = ld_shared_v4(base + OFF_META + (bs >> 1) * META_BYTES + m * 16u);
+                    uint32_t w[4];
+                    w[0] = __ballot_sync(0xffffffffu, (l.x >> lane) & 1u);
+                    w[1] = __ballot_sync(0xffffffffu, (l.y >> lane) & 1u);
+                    w[2] = __ballot_sync(0xffffffffu, (l.z >> lane) & 1u);
+                    w[3] = __ballot_sync(0xffffffffu, (l.w >> lane) & 1u);
+                    const uint32_t tpanel = tmem_base + TMEM_PANELS + (st % TS_) * 32;
                     const uint32_t b_lo = b_lo0 + bs * (BLK_SLOT_BYTES >> 4);
-                    uint32_t subs = (x | (x >> 1)) & 0x55u;  // bit 2s: sub-column s holds a block of this warp
-                    while (subs) {
-                        const uint32_t s2 = (uint32_t)__ffs((int)subs) - 1u;  // 2 * sub-column
-                        subs &= subs - 1u;
-                        const uint32_t own = (x >> s2) & 3u;
-                        const uint32_t q = (x >> (8u + (s2 >> 1) * 5u)) & 31u;
-                        const uint32_t d = acc_m + (own == 2u ? 16u : 0u);
+                    const uint32_t count = w[0] >> 28;
+                    PROF_MARK(9);
 #ifndef SMAT_TALL_NOMMA
-                        if (leader) mma_f16_ts_lohi(d, tpanel + s2 * 4u, b_lo + q * 32u, B_HI, own == 3u ? IDESC32 : IDESC16, 1u);
+#define SMAT_TALL_MMA(i)                                                                                               \
+    {                                                                                                                  \
+        const uint32_t e = ((i) & 1) ? (w[(i) >> 1] >> 16) : w[(i) >> 1];                                              \
+        if (leader)                                                                                                    \
+            mma_f16_ts_lohi(acc_m + ((e >> 5) & 16u), tpanel + ((e >> 3) & 56u), b_lo + (e & 63u) * 32u, B_HI,         \
+                            IDESC16 + ((e << 8) & (1u << 18)), 1u);                                                    \
+    }
+                    static_assert(IDESC32 == IDESC16 + (1u << 18), "the 32-column descriptor is the 16-column one plus bit 18");
+                    switch (count) {
+                        case 8: SMAT_TALL_MMA(7) [[fallthrough]];
+                        case 7: SMAT_TALL_MMA(6) [[fallthrough]];
+                        case 6: SMAT_TALL_MMA(5) [[fallthrough]];
+                        case 5: SMAT_TALL_MMA(4) [[fallthrough]];
+                        case 4: SMAT_TALL_MMA(3) [[fallthrough]];
+                        case 3: SMAT_TALL_MMA(2) [[fallthrough]];
+                        case 2: SMAT_TALL_MMA(1) [[fallthrough]];
+                        case 1: SMAT_TALL_MMA(0) [[fallthrough]];
+                        default: break;
+                    }
+#undef SMAT_TALL_MMA
 #endif
-                        any = true;
+                    PROF_MARK(10);
+                    if (leader) {
+                        if (count) tc_commit(step_done(pi % NPAIR));
+                        else mbar_arrive(step_done(pi % NPAIR));
                     }
-                    if (st & 1u) {
-                        if (leader) {
-                            if (any) tc_commit(step_done(pi % NPAIR));
-                            else mbar_arrive(step_done(pi % NPAIR));
-                        }
-                        any = false;
-                    }
+                    PROF_MARK(11);
                 }
                 if (leader) tc_commit(acc_full);
                 ++it;
@@ -304,7 +366,6 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
         const int quarter = warp & 3;  // a warp may only read tensor-memory lanes [32 * (warp % 4), +32)
         const int grp = e >> 2;        // two groups of four warps; group g takes block-rows g, g + 2, ...
         const int et = quarter * 32 + lane;
-        static_assert((NLW + NCW + NMW) % 4 == 0, "epilogue warp e must sit on lane quarter e % 4");
         uint32_t it = 0;
         SegGen<0> sg = make_gen();
         Seg cs;
@@ -317,7 +378,7 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
             const uint32_t nonempty = __ballot_sync(0xffffffffu, hi > lo);
             const bool partial = cs.cut;
             float* part_dst = fix_scratch + (size_t)cs.slot * (size_t)kFixSlotFloats;
-            if (lane == 0) wait_bar(acc_full, it & 1, abort_addr, status, 8);
+            if (lane == 0) TWAIT(acc_full, it & 1, 8);
             __syncwarp();
             tc_fence_after();
             int last_r = -1;  // last block-row this warp's group handles
@@ -365,6 +426,11 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
         }
     }
 
+#ifdef SMAT_PROFILE
+    if (lane == 0)
+        for (int c = 1; c < 12; c++)
+            if (prof_c[c]) atomicAdd(&g_wait_prof[c], (unsigned long long)prof_c[c]);
+#endif
     tc_fence_before();
     __syncthreads();
 #ifdef SMAT_PROFILE
@@ -411,12 +477,22 @@ int launch_spmm_tall(const PlanView& whole, const void* B, void* C, size_t N, cu
     const int n_full = (int)(n_items / (size_t)grid * (size_t)grid);
     int pf = 0;  // L2 prefetch: measured to make no difference here, and it costs copy-engine time
     if (const char* ev = std::getenv("SMAT_L2_PREFETCH")) pf = std::atoi(ev) != 0;  // tuning knob
-    SMAT_CUDA_TRY(cudaFuncSetAttribute(spmm_bcsr_tall_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
-    spmm_bcsr_tall_kernel<<<grid, kTallThreads, SMEM_BYTES, stream>>>(
-        mapB, reinterpret_cast<const uint8_t*>(plan.packed), reinterpret_cast<const uint4*>(plan.steps),
-        reinterpret_cast<const uint4*>(plan.winfo), plan.gsp, plan.rowptr,
-        reinterpret_cast<__half*>(C), ldc, (int)plan.brow_begin, (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles, (int)n_items, parts, panel_rows * 128u,
-        plan.fix_scratch, ctx->d_status, pf);
+    auto launch = [&](auto kernel, int threads) -> int {
+        SMAT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+        kernel<<<grid, threads, SMEM_BYTES, stream>>>(
+            mapB, reinterpret_cast<const uint8_t*>(plan.packed), reinterpret_cast<const uint4*>(plan.steps),
+            reinterpret_cast<const uint4*>(plan.winfo), plan.gsp, plan.rowptr, reinterpret_cast<__half*>(C), ldc, (int)plan.brow_begin,
+            (int)plan.brow_end, (int)plan.rg, (int)N, n_tiles, (int)n_items, parts, panel_rows * 128u, plan.fix_scratch, ctx->d_status, pf);
+        return SMAT_OK;
+    };
+    // the smallest shape that holds the plan's groups: fewer accumulators leave tensor memory for more panel slots
+    if (plan.rg <= 16) {
+        if (int rc = launch(spmm_bcsr_tall_kernel<16>, Shape<16>::kThreads)) return rc;
+    } else if (plan.rg <= 20) {
+        if (int rc = launch(spmm_bcsr_tall_kernel<20>, Shape<20>::kThreads)) return rc;
+    } else {
+        if (int rc = launch(spmm_bcsr_tall_kernel<24>, Shape<24>::kThreads)) return rc;
+    }
     count_launch();
     SMAT_CUDA_TRY(cudaGetLastError());
     if (parts == 1) return SMAT_OK;

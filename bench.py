@@ -41,15 +41,15 @@ METRIC = "SpMM effective TFLOP/s (nonzero-block FLOPs)"
 
 # DRAM bytes (read + write) per launch of the SpMM kernel from an ncu capture of the same workload
 # (see profiles/): filled per workload, None where no capture exists.
-NCU_TRAFFIC_BYTES = {
-    # 117.86 MB (113.68 read + 4.17 written, mean of two launches) measured at scale 0.25 (nnzb 204859), scaled by nnzb to the
-    # full-size matrix (3548444 blocks): every block is read once per launch and dominates the traffic
-    # block-sparse layer, full size: dram__bytes_read.sum + dram__bytes_write.sum of the SpMM kernel (1043.2 + 59.5 MB, mean of three
-    # launches, captured at full size: the two counters take one pass).  2.8x the algorithmic bytes: B (235 MB) does not fit L2 and
-    # is streamed from HBM once per round of work items (3.5 rounds)
-    ("llm", 1.0, 1): 1102730000,
-    ("uniform", 1.0, 1): int(117.86e6 * 3548444 / 204859),
-    ("uniform", 0.25, 1): int(117.86e6),
+NCU_TRAFFIC_BYTES = {  # (config, scale, GPUs, kernel) -> bytes per launch
+    # uniform: 117.86 MB (113.68 read + 4.17 written, mean of two launches) measured at scale 0.25 (nnzb 204859) with the 16-row
+    # kernel, scaled by nnzb to the full-size matrix (3548444 blocks): every block is read once per launch and dominates the traffic
+    ("uniform", 0.25, 1, "spmm_bcsr_tc_kernel"): int(117.86e6),
+    # block-sparse layer, full size: dram__bytes_read.sum + dram__bytes_write.sum of the SpMM kernel, mean of three launches,
+    # captured at full size (the two counters take one pass).  B (235 MB) does not fit L2 and is streamed from HBM once per
+    # round of work items
+    ("llm", 1.0, 1, "spmm_bcsr_tc_kernel"): 1102730000,   # 16-row kernel, 256-column items: 3.5 rounds
+    ("llm", 1.0, 1, "spmm_bcsr_tall_kernel"): 1358331000,  # 24-row kernel (the default plan): 4.8 rounds
 }
 SEEDS = {"band": 0, "uniform": 1, "powerlaw": 2, "clustered": 3, "llm": 4}
 ALL_CONFIGS = ["band", "uniform", "powerlaw", "clustered", "llm"]
@@ -258,7 +258,7 @@ class _Rows:
         return self.C[i * 16:(i + 1) * 16].cpu().numpy().view(np.float16)
 
 
-def roofline_of(peaks, bytes_alg, flops, kernel_ms, traffic):
+def roofline_of(peaks, bytes_alg, flops, kernel_ms, traffic, kernel):
     t_hbm = bytes_alg / (peaks["hbm_gbs"] * 1e9)
     t_tensor = flops / (peaks["tflops"] * 1e12)
     secs = kernel_ms * 1e-3
@@ -272,7 +272,7 @@ def roofline_of(peaks, bytes_alg, flops, kernel_ms, traffic):
                 "frac": round(ach / peaks["tflops"], 4), "traffic": traffic}
     roof.update({"peak_source": peaks["source"], "algorithmic_bytes": int(bytes_alg), "flops": flops,
                  "t_hbm_ms": round(t_hbm * 1e3, 4), "t_tensor_ms": round(t_tensor * 1e3, 4),
-                 "kernel": "spmm_bcsr_tc_kernel", "kernel_ms": round(kernel_ms, 4)})
+                 "kernel": kernel, "kernel_ms": round(kernel_ms, 4)})
     return roof
 
 
@@ -463,8 +463,10 @@ def main():
     # ---------------- roofline of the SpMM kernel (rank 0's launch) ----------------
     peaks = load_peaks()
     bytes_alg = algorithmic_bytes(brp_h[b0:b1 + 1] - brp_h[b0], bci_h[brp_h[b0]:brp_h[b1]], (b1 - b0) * 16, N)
+    kinfo = plan.info()
     roof = roofline_of(peaks, bytes_alg, 2.0 * 256.0 * N * my_blocks, ms_step_local,
-                       NCU_TRAFFIC_BYTES.get((args.config, args.scale, world)))
+                       NCU_TRAFFIC_BYTES.get((args.config, args.scale, world, kinfo["kernel"])), kinfo["kernel"])
+    roof["rows_per_item"] = kinfo["rows_per_item"]
 
     # ---------------- CPU baseline: the reference's blocked multiply on a bounded sample ----------------
     cpu = None
@@ -529,10 +531,11 @@ def main():
                 reg = time_regions(c2, max(args.steps, 20), 3, 1, barrier)
                 p2, h2 = c2["p"], c2["host"]
                 ms2 = reg[0]
-                r2 = roofline_of(peaks, algorithmic_bytes(h2[0], h2[1], p2.M, p2.N), 2.0 * 256.0 * p2.N * c2["A"].nnzb, ms2, None)
+                r2 = roofline_of(peaks, algorithmic_bytes(h2[0], h2[1], p2.M, p2.N), 2.0 * 256.0 * p2.N * c2["A"].nnzb, ms2, None,
+                                 c2["plan"].info()["kernel"])
                 par2 = parity_check(_Rows(c2["Cd"]), 0, h2[0], h2[1], h2[2], p2.B_nk, p2.M, p2.N, p2.K)
                 rows.append({"config": name, "ms": round(ms2, 5), "tflops": round(2.0 * 256.0 * p2.N * c2["A"].nnzb / (ms2 * 1e-3) * 1e-12, 2),
-                             "bound": r2["bound"], "frac": r2["frac"], "nnzb": c2["A"].nnzb,
+                             "bound": r2["bound"], "frac": r2["frac"], "kernel": r2["kernel"], "nnzb": c2["A"].nnzb,
                              "block_fill": round(c2["nnz"] / (c2["A"].nnzb * 256.0), 5), "parity_max_rel_err": float(f"{par2:.3e}"),
                              "setup_s": c2["setup_s"]})
                 c2["plan"].close()

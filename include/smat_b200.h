@@ -87,7 +87,8 @@ int smat_spmm_bcsr_f16_static(const void* bcsrValuesA, const int* bcsrRowPtrA, c
  * No counterpart in the reference (its kernel re-reads bcsrColIdx per tile, mmaCBT.cu:38-43). */
 typedef struct smat_plan smat_plan;
 /* N_hint: the number of columns of B the plan will mostly be used with (0 = unknown).  It only steers
- * how many block-rows form a work item (8 to 16), so that small matrices or shards still fill the SMs.
+ * how many block-rows form a work item (8 to 24) and which of the two kernels multiplies, so that small matrices or
+ * shards still fill the SMs.
  * A plan also owns scratch for work items that a launch computes in segments (38.8 MB on a 148-SM device, twice
  * that for matrices whose work is very unevenly spread over the block-rows) and may be used by one stream at a
  * time. */
@@ -108,6 +109,10 @@ int smat_plan_spmm(const smat_plan* plan, const void* B, void* C, size_t N, void
  * (src/cuda_hgemm/src/common/matrix.h:88-101). */
 int smat_plan_spmm_host(smat_plan* plan, const void* B_host, void* C_host, size_t N, void* stream);
 int smat_plan_destroy(smat_plan* plan);
+/* What a plan turned out to be (informational, no reference counterpart): *rows_per_item = block-rows of a work item
+ * (8..16: the kernel that reads both operands from shared memory; 16..24 with *tall = 1: the kernel that reads the
+ * B panels from tensor memory), *steps = steps of the walk order.  Any pointer may be NULL. */
+int smat_plan_info(const smat_plan* plan, int* tall, int* rows_per_item, size_t* steps);
 
 /* Kernel variant used by every multiplication of this process: 0 = chosen per matrix (default),
  * 1 = both MMA operands from shared memory (two accumulator buffers, epilogue overlapped),

@@ -38,6 +38,7 @@ def lib():
     L.smat_plan_spmm.argtypes = [vp, vp, vp, sz, vp]
     L.smat_plan_spmm_host.argtypes = [vp, vp, vp, sz, vp]
     L.smat_plan_destroy.argtypes = [vp]
+    L.smat_plan_info.argtypes = [vp, vp, vp, vp]
     L.smat_spmm_set_variant.argtypes = [C.c_int]
     L.smat_device_status.argtypes = [vp]
     L.smat_selftest_wait_timeout.argtypes = [vp]
@@ -428,6 +429,13 @@ class Plan:
     def set_values(self):
         """Re-reads A's value array after it changed (same structure)."""
         _check(lib().smat_plan_set_values(self._h, self.A.getBcsrValues(), _stream()))
+
+    def info(self):
+        """{'tall': bool, 'rows_per_item': int, 'steps': int, 'kernel': name of the CUDA kernel that multiplies}."""
+        t, r, n = C.c_int(0), C.c_int(0), C.c_size_t(0)
+        _check(lib().smat_plan_info(self._h, C.addressof(t), C.addressof(r), C.addressof(n)))
+        return {"tall": bool(t.value), "rows_per_item": r.value, "steps": n.value,
+                "kernel": "spmm_bcsr_tall_kernel" if t.value else "spmm_bcsr_tc_kernel"}
 
     def spmm(self, B, Cout, check=False):
         Bt = B.data if isinstance(B, Matrix) else B

@@ -1013,6 +1013,15 @@ int smat_plan_spmm_host(smat_plan* plan, const void* B_host, void* C_host, size_
     return SMAT_OK;
 }
 
+int smat_plan_info(const smat_plan* plan, int* tall, int* rows_per_item, size_t* steps) {
+    clear_error();
+    if (!plan) return fail(SMAT_ERR_BAD_ARG, "NULL plan");
+    if (tall) *tall = plan->v.tall ? 1 : 0;
+    if (rows_per_item) *rows_per_item = (int)plan->v.rg;
+    if (steps) *steps = plan->v.total_steps;
+    return SMAT_OK;
+}
+
 int smat_plan_destroy(smat_plan* plan) {
     clear_error();
     if (!plan) return SMAT_OK;

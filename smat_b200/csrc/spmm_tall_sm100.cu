@@ -52,7 +52,8 @@ using namespace ptx;
 
 namespace {
 
-constexpr int NLW = 4;           // loader warps
+constexpr int NLW = 4;           // panel-loader warps, and as many block-loader warps
+constexpr int LW = 2 * NLW;      // loader warps in all
 constexpr int NCW = 4;           // copier warps
 constexpr int NEW = 8;           // epilogue warps
 constexpr uint32_t PS = 6;                                   // panel slots in shared memory (a slot is free once copied to tensor memory)
@@ -87,7 +88,7 @@ static_assert(kTallRows * 16 * 128 <= kFixSlotFloats, "a partial tile must fit a
 template <int TRG>
 struct Shape {
     static constexpr int NMW = TRG / 2;
-    static constexpr int kThreads = (NLW + NCW + NMW + NEW) * 32;
+    static constexpr int kThreads = (LW + NCW + NMW + NEW) * 32;
     static constexpr uint32_t TMEM_PANELS = TRG * 16;
     static constexpr uint32_t TS_ = (512 - TRG * 16) / 32 < 8 ? (512 - TRG * 16) / 32 : 8;
     static_assert(TRG % 2 == 0 && TRG <= kTallRows && kThreads <= 1024, "shape");
@@ -170,7 +171,7 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
         fence_proxy_async();
         prefetch_tensormap(&mapB);
     }
-    if (warp == NLW) {
+    if (warp == LW) {
         tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
@@ -187,10 +188,12 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
     __syncthreads();
     tc_fence_after();
 
-    if (warp < NLW) {
-        // ------------------------------ loader warp j: steps j, j + NLW, ... ------------------------------
+    if (warp < LW) {
+        // ---------------- loader warps: panel loader j and block loader j take the steps j, j + NLW, ... ----------------
+        // (two threads per step, so that neither waits for the other's slot and each has half the work per step)
         if (lane == 0) {
-            const int j = warp;
+            const bool panels = warp < NLW;
+            const int j = warp % NLW;
             SegGen<0> sg = make_gen();
             Seg cs;
             bool have = sg.next(cs);
@@ -213,9 +216,9 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
                 }
             };
             auto prefetch = [&](const TallStep& r) {  // HBM latency is hidden in L2: fetched PF records ahead of the copies
-                if (pf && r.live) {
-                    tma_prefetch_l2_2d(&mapB, (int)r.a.x, r.tile * 128);
-                    bulk_prefetch_l2(packed + (size_t)r.a.y * 256, r.a.z * 512u);
+                if (pf && r.live && r.a.z) {
+                    if (panels) tma_prefetch_l2_2d(&mapB, (int)r.a.x, r.tile * 128);
+                    else bulk_prefetch_l2(packed + (size_t)r.a.y * 256, r.a.z * 512u);
                 }
             };
 #pragma unroll
@@ -230,34 +233,36 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
                     if (!r.live) { more = false; break; }
                     const uint32_t ps = r.st % PS, bs = r.st % BS, pi = r.st >> 1;
                     const uint32_t a_bytes = r.a.z * 512u;  // 0: a step that only pads its group to an even count
-                    // The panel first (the copier needs it before the MMAs need the blocks): its slot is free once the
-                    // copy of the step PS positions back (pair pi - PS / 2) has left it.
-                    if (r.st >= PS) TWAIT(cp_done((pi - PS / 2) % NPAIR), ((pi - PS / 2) / NPAIR) & 1, 1);
-                    if (a_bytes) {
-                        mbar_arrive_expect_tx(full_p(r.st % FP), panel_bytes);
-                        tma_load_2d(base + OFF_PANEL + ps * PANEL_BYTES, &mapB, (int)r.a.x, r.tile * 128, full_p(r.st % FP));
+                    if (panels) {
+                        // the panel's slot is free once the copy of the step PS positions back (pair pi - PS / 2) has left it
+                        if (r.st >= PS) TWAIT(cp_done((pi - PS / 2) % NPAIR), ((pi - PS / 2) / NPAIR) & 1, 1);
+                        if (a_bytes) {
+                            mbar_arrive_expect_tx(full_p(r.st % FP), panel_bytes);
+                            tma_load_2d(base + OFF_PANEL + ps * PANEL_BYTES, &mapB, (int)r.a.x, r.tile * 128, full_p(r.st % FP));
+                        } else {
+                            mbar_arrive(full_p(r.st % FP));  // no panel: the phase completes at once
+                        }
                     } else {
-                        mbar_arrive(full_p(r.st % FP));  // no panel: the phase completes at once
+                        // the slot of the blocks is free once the MMAs of the step BS positions back (pair pi - BS / 2) have completed
+                        if (r.st >= BS) TWAIT(step_done((pi - BS / 2) % NPAIR), ((pi - BS / 2) / NPAIR) & 1, 2);
+                        st_shared_u32(base + OFF_SUBS + bs * 8, r.a.w);  // for the copier; ordered before its wait by the arrive below
+                        const uint32_t m_bytes = (r.st & 1u) ? 0u : META_BYTES;  // the pair's lists travel with its first step
+                        if (a_bytes + m_bytes) mbar_arrive_expect_tx(full_b(r.st % FB), a_bytes + m_bytes);
+                        else mbar_arrive(full_b(r.st % FB));
+                        if (m_bytes)
+                            bulk_load(base + OFF_META + (bs >> 1) * META_BYTES, winfo + 16 * (size_t)(r.idx >> 1), META_BYTES, full_b(r.st % FB));
+                        if (a_bytes) bulk_load(base + OFF_BLK + bs * BLK_SLOT_BYTES, packed + (size_t)r.a.y * 256, a_bytes, full_b(r.st % FB));
                     }
-                    // Then the blocks and the masks: their slot is free once the MMAs of the step BS positions back
-                    // (pair pi - BS / 2) have completed.
-                    if (r.st >= BS) TWAIT(step_done((pi - BS / 2) % NPAIR), ((pi - BS / 2) / NPAIR) & 1, 2);
-                    st_shared_u32(base + OFF_SUBS + bs * 8, r.a.w);  // for the copier; ordered before its wait by the arrive below
-                    const uint32_t m_bytes = (r.st & 1u) ? 0u : META_BYTES;  // the pair's lists travel with its first step
-                    if (a_bytes + m_bytes) mbar_arrive_expect_tx(full_b(r.st % FB), a_bytes + m_bytes);
-                    else mbar_arrive(full_b(r.st % FB));
-                    if (m_bytes) bulk_load(base + OFF_META + (bs >> 1) * META_BYTES, winfo + 16 * (size_t)(r.idx >> 1), META_BYTES, full_b(r.st % FB));
-                    if (a_bytes) bulk_load(base + OFF_BLK + bs * BLK_SLOT_BYTES, packed + (size_t)r.a.y * 256, a_bytes, full_b(r.st % FB));
                     prefetch(rec[(a + PF) % U]);
                     gen(r);
                 }
             }
         }
         __syncwarp();
-    } else if (warp < NLW + NCW) {
-        // ------------------------------ copier j: panel slot j, steps j, j + NCW, ... ------------------------------
+    } else if (warp < LW + NCW) {
+        // ------------------------------ copier j: steps j, j + NCW, ... ------------------------------
         if (lane == 0) {
-            const uint32_t j = (uint32_t)(warp - NLW);
+            const uint32_t j = (uint32_t)(warp - LW);
             uint32_t total = 0;  // steps of this CTA
             {
                 SegGen<0> sg = make_gen();
@@ -266,26 +271,25 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
             }
             for (uint32_t st = j; st < total; st += NCW) {
                 const uint32_t ps = st % PS, bs = st % BS, pi = st >> 1;
-                // everything that is usually there already first, so that only the copies follow the panel's arrival
+                // what is usually there already first: blocks and panel wait in shared memory for a tensor-memory slot,
+                // which is free once the MMAs of the step TS_ positions back (pair pi - TS_ / 2) have completed; only
+                // the copies follow that
                 TWAIT(full_b(st % FB), (st / FB) & 1, 4);
-                // the tensor-memory slot is free once the MMAs of the step TS_ positions back (pair pi - 2) have completed
-                if (pi >= TS_ / 2) TWAIT(step_done((pi - TS_ / 2) % NPAIR), ((pi - TS_ / 2) / NPAIR) & 1, 5);
                 const uint32_t subs = ld_shared_u32(base + OFF_SUBS + bs * 8);  // non-empty sub-columns
                 const uint64_t pdesc = smem_desc_k_sw128(base + OFF_PANEL + ps * PANEL_BYTES);
                 const uint32_t tdst = tmem_base + TMEM_PANELS + (st % TS_) * 32;
                 TWAIT(full_p(st % FP), (st / FP) & 1, 3);
+                if (pi >= TS_ / 2) TWAIT(step_done((pi - TS_ / 2) % NPAIR), ((pi - TS_ / 2) / NPAIR) & 1, 5);
                 tc_fence_after();
-#ifndef SMAT_TALL_NOCP
                 if (subs & 1u) tc_cp_128x256b(tdst, pdesc);
                 if (subs & 2u) tc_cp_128x256b(tdst + 8, pdesc + 2);
                 if (subs & 4u) tc_cp_128x256b(tdst + 16, pdesc + 4);
                 if (subs & 8u) tc_cp_128x256b(tdst + 24, pdesc + 6);
-#endif
                 tc_commit(cp_done(pi % NPAIR));
             }
         }
         __syncwarp();
-    } else if (warp < NLW + NCW + NMW) {
+    } else if (warp < LW + NCW + NMW) {
         // ------------------------------ MMA warp m: accumulator rows 2m, 2m + 1 ------------------------------
         // The whole warp runs the loop converged and one elected lane issues.  Every operand of a tcgen05.mma must
         // be a value the compiler knows to be warp-uniform (the instruction reads uniform registers): measured, the
@@ -293,7 +297,7 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
         // of every ~80.  So the mask words, read from shared memory, are turned into ballots before anything is
         // derived from them.
         {
-            const uint32_t m = (uint32_t)__shfl_sync(0xffffffffu, warp - NLW - NCW, 0);
+            const uint32_t m = (uint32_t)__shfl_sync(0xffffffffu, warp - LW - NCW, 0);
             const bool leader = elect_one();
             const uint32_t B_HI = (uint32_t)(smem_desc_k_sw32(0) >> 32);
             const uint32_t b_lo0 = (uint32_t)smem_desc_k_sw32(base + OFF_BLK);
@@ -326,7 +330,6 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
                     const uint32_t b_lo = b_lo0 + bs * (BLK_SLOT_BYTES >> 4);
                     const uint32_t count = w[0] >> 28;
                     PROF_MARK(9);
-#ifndef SMAT_TALL_NOMMA
 #define SMAT_TALL_MMA(i)                                                                                               \
     {                                                                                                                  \
         const uint32_t e = ((i) & 1) ? (w[(i) >> 1] >> 16) : w[(i) >> 1];                                              \
@@ -347,7 +350,6 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
                         default: break;
                     }
 #undef SMAT_TALL_MMA
-#endif
                     PROF_MARK(10);
                     if (leader) {
                         if (count) tc_commit(step_done(pi % NPAIR));
@@ -362,7 +364,7 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
         __syncwarp();
     } else {
         // ------------------------------ epilogue: tensor memory -> fp16 -> C ------------------------------
-        const int e = warp - (NLW + NCW + NMW);
+        const int e = warp - (LW + NCW + NMW);
         const int quarter = warp & 3;  // a warp may only read tensor-memory lanes [32 * (warp % 4), +32)
         const int grp = e >> 2;        // two groups of four warps; group g takes block-rows g, g + 2, ...
         const int et = quarter * 32 + lane;
@@ -440,7 +442,7 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
         // a wait ran out somewhere: give copies still in flight time to land before the CTA retires
         for (int i = 0; i < 64; i++) __nanosleep(1000);
     }
-    if (warp == NLW) {
+    if (warp == LW) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }

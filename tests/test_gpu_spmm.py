@@ -340,6 +340,39 @@ def test_tall_plan_dense_and_odd_shapes():
         assert np.array_equal(C.view(np.uint16), again.view(np.uint16))
 
 
+def test_plan_chooses_tall_kernel_for_block_sparse_layer():
+    """Plan creation counts the steps of both walk orders and takes the 24-row one where its estimate wins: a
+    block-sparse layer with a fifth of its blocks kept and enough work to fill the device does, the same matrix with a
+    forced 16-row kernel does not; both give the oracle's result.  smat_plan_info reports the choice."""
+    torch = _torch()
+    rng = np.random.default_rng(33)
+    Mb, Kb, N = 192, 512, 2048
+    mask = rng.random((Mb, Kb)) < 0.2
+    brp = np.zeros(Mb + 1, np.int32)
+    brp[1:] = np.cumsum(mask.sum(axis=1))
+    bci = (np.nonzero(mask)[1] * 16).astype(np.int32)
+    bv = (rng.standard_normal(brp[-1] * 256) * 0.25).astype(np.float16)
+    B_nk = rng.standard_normal((N, Kb * 16)).astype(np.float16)
+    Cref, Cabs = _oracle_c(bv, brp, bci, B_nk, Mb * 16, N, Kb * 16)
+    A = S.SparseMatrix.from_bcsr(Mb * 16, Kb * 16, brp, bci, bv)
+    B = S.Matrix.from_host(B_nk)
+    for variant, want_tall in ((0, True), (1, False)):
+        S.set_variant(variant)
+        try:
+            plan = S.Plan(A, n_hint=N)
+        finally:
+            S.set_variant(0)
+        info = plan.info()
+        assert info["tall"] == want_tall, info
+        assert (16 <= info["rows_per_item"] <= 24) if want_tall else (info["rows_per_item"] <= 16)
+        assert info["steps"] > 0 and info["kernel"] == ("spmm_bcsr_tall_kernel" if want_tall else "spmm_bcsr_tc_kernel")
+        C = S.Matrix(Mb * 16, N, fill=float("nan"))
+        plan.spmm(B, C, check=True)
+        torch.cuda.synchronize()
+        assert _rel_err(C.data.cpu().numpy(), Cref, Cabs) <= TOL
+        plan.close()
+
+
 def test_bounded_wait_timeout_is_reported():
     """The error path of the kernels' bounded waits, driven from the host: a one-thread kernel waits on a barrier that
     nothing completes, gives up after ~0.2 ms and sets the device status word; smat_device_status reports

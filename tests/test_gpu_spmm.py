@@ -235,9 +235,10 @@ def test_block_row_range_entry_point():
         assert _close(shard.cpu().numpy(), full.data[b0 * 16:b1 * 16].cpu().numpy())
 
 
+@pytest.mark.parametrize("kernel", ["auto", "tall"])
 @pytest.mark.parametrize("ranges", ["", "3"])
 @pytest.mark.parametrize("N", [64, 264, 1024])
-def test_host_buffer_entry_point(N, ranges, monkeypatch):
+def test_host_buffer_entry_point(N, ranges, kernel, monkeypatch):
     """smat_plan_spmm_host: B and C in pinned host memory, copies pipelined in column chunks (1, 3 and 4 chunks
     here, the 264-column case with a ragged last chunk), called twice to cover the reuse of its staging; the last
     chunk multiplied and copied out in one range of block-rows (the automatic choice at this size) and in three."""
@@ -246,7 +247,12 @@ def test_host_buffer_entry_point(N, ranges, monkeypatch):
         monkeypatch.setenv("SMAT_HOST_RANGES", ranges)
     p, brp, bci, bv = _problem("uniform", 0.03, N)
     A = S.SparseMatrix.from_bcsr(p.M, p.K, brp, bci, bv)
-    plan = S.Plan(A, n_hint=N)
+    S.set_variant(4 if kernel == "tall" else 0)  # a tall plan (24-row work items) takes the same chunks and row ranges
+    try:
+        plan = S.Plan(A, n_hint=N)
+    finally:
+        S.set_variant(0)
+    assert plan.info()["tall"] == (kernel == "tall")
     B_host = torch.from_numpy(p.B_nk.view(np.int16)).pin_memory()
     C_host = torch.full((p.M, N), -1, dtype=torch.int16).pin_memory()
     Cref, Cabs = _oracle_c(bv, brp, bci, p.B_nk, p.M, N, p.K)

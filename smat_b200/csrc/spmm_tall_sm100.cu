@@ -130,7 +130,9 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
     const int lane = threadIdx.x & 31;
 #ifdef SMAT_PROFILE  // development aid: cycles this thread spends in each kind of wait (mbarrier.try_wait may itself suspend it)
     const long long t_kernel0 = clock64();
-    unsigned int prof_c[12] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    unsigned int prof_c[16] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    __shared__ unsigned int stamp_cp[8], stamp_mma[8];  // clock of the last commit of a pair's copies / MMAs
+    if (threadIdx.x < 8) stamp_cp[threadIdx.x] = stamp_mma[threadIdx.x] = (unsigned int)clock();
     long long prof_t = 0;
 #define PROF_MARK(code)                                          \
     do {                                                         \
@@ -261,31 +263,46 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
         __syncwarp();
     } else if (warp < LW + NCW) {
         // ------------------------------ copier j: steps j, j + NCW, ... ------------------------------
-        if (lane == 0) {
-            const uint32_t j = (uint32_t)(warp - LW);
+        // The whole warp runs the loop converged and one elected lane issues, like the MMA warps: operands a
+        // tcgen05 instruction gets from warp-uniform values cost its thread far less than ones from a lone lane.
+        {
+            const uint32_t j = (uint32_t)__shfl_sync(0xffffffffu, warp - LW, 0);
+            const bool leader = elect_one();
             uint32_t total = 0;  // steps of this CTA
             {
                 SegGen<0> sg = make_gen();
                 Seg cs;
                 while (sg.next(cs)) total += (uint32_t)(cs.k1 - cs.k0);
             }
+            total = (uint32_t)__shfl_sync(0xffffffffu, total, 0);
             for (uint32_t st = j; st < total; st += NCW) {
                 const uint32_t ps = st % PS, bs = st % BS, pi = st >> 1;
                 // what is usually there already first: blocks and panel wait in shared memory for a tensor-memory slot,
                 // which is free once the MMAs of the step TS_ positions back (pair pi - TS_ / 2) have completed; only
                 // the copies follow that
                 TWAIT(full_b(st % FB), (st / FB) & 1, 4);
-                const uint32_t subs = ld_shared_u32(base + OFF_SUBS + bs * 8);  // non-empty sub-columns
+                const uint32_t subs_l = ld_shared_u32(base + OFF_SUBS + bs * 8);  // non-empty sub-columns
+                const uint32_t subs = __ballot_sync(0xffffffffu, (subs_l >> lane) & 1u);
                 const uint64_t pdesc = smem_desc_k_sw128(base + OFF_PANEL + ps * PANEL_BYTES);
                 const uint32_t tdst = tmem_base + TMEM_PANELS + (st % TS_) * 32;
                 TWAIT(full_p(st % FP), (st / FP) & 1, 3);
                 if (pi >= TS_ / 2) TWAIT(step_done((pi - TS_ / 2) % NPAIR), ((pi - TS_ / 2) / NPAIR) & 1, 5);
+#ifdef SMAT_PROFILE
+                if (pi >= TS_ / 2) prof_c[13] += (unsigned int)clock() - *(volatile unsigned int*)&stamp_mma[(pi - TS_ / 2) % 8];
+                const unsigned int t_cp0 = (unsigned int)clock();
+#endif
                 tc_fence_after();
-                if (subs & 1u) tc_cp_128x256b(tdst, pdesc);
-                if (subs & 2u) tc_cp_128x256b(tdst + 8, pdesc + 2);
-                if (subs & 4u) tc_cp_128x256b(tdst + 16, pdesc + 4);
-                if (subs & 8u) tc_cp_128x256b(tdst + 24, pdesc + 6);
-                tc_commit(cp_done(pi % NPAIR));
+                if (leader) {
+                    if (subs & 1u) tc_cp_128x256b(tdst, pdesc);
+                    if (subs & 2u) tc_cp_128x256b(tdst + 8, pdesc + 2);
+                    if (subs & 4u) tc_cp_128x256b(tdst + 16, pdesc + 4);
+                    if (subs & 8u) tc_cp_128x256b(tdst + 24, pdesc + 6);
+                    tc_commit(cp_done(pi % NPAIR));
+                }
+#ifdef SMAT_PROFILE
+                if (leader) atomicMax(&stamp_cp[pi % 8], (unsigned int)clock());
+                prof_c[14] += (unsigned int)clock() - t_cp0;
+#endif
             }
         }
         __syncwarp();
@@ -314,6 +331,9 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
                     const uint32_t pi = st >> 1, bs = st % BS;
                     PROF_MARK(0);
                     TWAIT(cp_done(pi % NPAIR), (pi / NPAIR) & 1, 7);
+#ifdef SMAT_PROFILE
+                    prof_c[12] += (unsigned int)clock() - *(volatile unsigned int*)&stamp_cp[pi % 8];
+#endif
                     tc_fence_after();
                     // This warp's list for the pair: up to eight 16-bit entries, one per MMA (layout: tall_pair_kernel
                     // in plan.cu), their number in the top bits of the first word.  Measured: the branches and the
@@ -355,6 +375,9 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
                         if (count) tc_commit(step_done(pi % NPAIR));
                         else mbar_arrive(step_done(pi % NPAIR));
                     }
+#ifdef SMAT_PROFILE
+                    if (leader) atomicMax(&stamp_mma[pi % 8], (unsigned int)clock());
+#endif
                     PROF_MARK(11);
                 }
                 if (leader) tc_commit(acc_full);
@@ -430,7 +453,7 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
 
 #ifdef SMAT_PROFILE
     if (lane == 0)
-        for (int c = 1; c < 12; c++)
+        for (int c = 1; c < 16; c++)
             if (prof_c[c]) atomicAdd(&g_wait_prof[c], (unsigned long long)prof_c[c]);
 #endif
     tc_fence_before();

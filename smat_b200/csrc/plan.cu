@@ -249,7 +249,8 @@ __global__ void __launch_bounds__(256) pack_kernel(const uint4* __restrict__ val
 }
 
 
-// ---- tall plans: groups of up to 32 block-rows (the kernel uses at most kTallRows), 32-byte step records ----
+// ---- tall plans: groups of up to kTallRows block-rows (one warp of this kernel per block-row), 16-byte step records,
+// ---- 64 bytes of per-warp words per step (the input of tall_pair_kernel below), groups padded to an even step count ----
 constexpr int kTallPlanThreads = 1024;  // warp w owns block-row w of the group
 static_assert(kTallRows == 24 && kTallBlocksPerStep <= 32, "the per-warp step words below are laid out for 12 warps of two rows and 5-bit block positions");
 

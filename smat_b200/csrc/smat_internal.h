@@ -88,8 +88,9 @@ constexpr int kPlanBlocksPerStep = 24;
 // fuller steps at the price of one pipeline stage.
 constexpr int kPlanBlocksPerStepDense = 32;
 // The tall kernel (spmm_tall_sm100.cu) works on groups of up to kTallRows block-rows: a B panel fetched once feeds
-// half again as many rows, and the panels are read by the MMAs from tensor memory.  Its plans ("tall" plans) use
-// 32-byte step records and steps of at most kTallBlocksPerStep blocks.
+// half again as many rows, and the panels are read by the MMAs from tensor memory.  Its plans ("tall" plans) have
+// steps of at most kTallBlocksPerStep blocks, an even number of steps per group, and per pair of steps the list of
+// MMAs of each issuing warp (PlanView::winfo).
 constexpr int kTallRows = 24;
 constexpr int kTallBlocksPerStep = 24;
 // MMA-issuing warps of the kernel; each owns kPlanRowsPerGroup / kPlanOwners consecutive accumulators.

@@ -165,7 +165,7 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < FP; s++) mbar_init(full_p(s), 1);
         for (uint32_t s = 0; s < FB; s++) mbar_init(full_b(s), 1);
-        for (uint32_t s = 0; s < NPAIR; s++) { mbar_init(cp_done(s), 2); mbar_init(step_done(s), NMW); }
+        for (uint32_t s = 0; s < NPAIR; s++) { mbar_init(cp_done(s), 4); mbar_init(step_done(s), NMW); }  // cp_done: per step a commit and an arrive
         mbar_init(acc_full, NMW);
         mbar_init(acc_empty, NEW);
         st_shared_u32(abort_addr, 0);
@@ -293,11 +293,16 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
 #endif
                 tc_fence_after();
                 if (leader) {
+#ifndef SMAT_TALL_NOCP
                     if (subs & 1u) tc_cp_128x256b(tdst, pdesc);
                     if (subs & 2u) tc_cp_128x256b(tdst + 8, pdesc + 2);
                     if (subs & 4u) tc_cp_128x256b(tdst + 16, pdesc + 4);
                     if (subs & 8u) tc_cp_128x256b(tdst + 24, pdesc + 6);
+#endif
                     tc_commit(cp_done(pi % NPAIR));
+                    // A plain arrive beside the commit's: it is ordered after this thread's wait for the blocks and
+                    // lists of the step, so whoever passes cp_done may read them (the MMA warps wait for nothing else).
+                    mbar_arrive(cp_done(pi % NPAIR));
                 }
 #ifdef SMAT_PROFILE
                 if (leader) atomicMax(&stamp_cp[pi % 8], (unsigned int)clock());
@@ -353,31 +358,30 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
 #define SMAT_TALL_MMA(i)                                                                                               \
     {                                                                                                                  \
         const uint32_t e = ((i) & 1) ? (w[(i) >> 1] >> 16) : w[(i) >> 1];                                              \
-        if (leader)                                                                                                    \
-            mma_f16_ts_lohi(acc_m + ((e >> 5) & 16u), tpanel + ((e >> 3) & 56u), b_lo + (e & 63u) * 32u, B_HI,         \
-                            IDESC16 + ((e << 8) & (1u << 18)), 1u);                                                    \
+        mma_f16_ts_lohi(acc_m + ((e >> 5) & 16u), tpanel + ((e >> 3) & 56u), b_lo + (e & 63u) * 32u, B_HI,             \
+                        IDESC16 + ((e << 8) & (1u << 18)), 1u);                                                        \
     }
                     static_assert(IDESC32 == IDESC16 + (1u << 18), "the 32-column descriptor is the 16-column one plus bit 18");
-                    switch (count) {
-                        case 8: SMAT_TALL_MMA(7) [[fallthrough]];
-                        case 7: SMAT_TALL_MMA(6) [[fallthrough]];
-                        case 6: SMAT_TALL_MMA(5) [[fallthrough]];
-                        case 5: SMAT_TALL_MMA(4) [[fallthrough]];
-                        case 4: SMAT_TALL_MMA(3) [[fallthrough]];
-                        case 3: SMAT_TALL_MMA(2) [[fallthrough]];
-                        case 2: SMAT_TALL_MMA(1) [[fallthrough]];
-                        case 1: SMAT_TALL_MMA(0) [[fallthrough]];
-                        default: break;
+                    // one region of the elected lane per pair (every separate `if (leader)` costs the warp a divergence
+                    // and a reconvergence: one region instead of one per MMA was worth 7 % of the kernel's time)
+                    if (leader) {
+                        switch (count) {
+                            case 8: SMAT_TALL_MMA(7) [[fallthrough]];
+                            case 7: SMAT_TALL_MMA(6) [[fallthrough]];
+                            case 6: SMAT_TALL_MMA(5) [[fallthrough]];
+                            case 5: SMAT_TALL_MMA(4) [[fallthrough]];
+                            case 4: SMAT_TALL_MMA(3) [[fallthrough]];
+                            case 3: SMAT_TALL_MMA(2) [[fallthrough]];
+                            case 2: SMAT_TALL_MMA(1) [[fallthrough]];
+                            case 1: SMAT_TALL_MMA(0) tc_commit(step_done(pi % NPAIR)); break;
+                            default: mbar_arrive(step_done(pi % NPAIR)); break;
+                        }
+#ifdef SMAT_PROFILE
+                        atomicMax(&stamp_mma[pi % 8], (unsigned int)clock());
+#endif
                     }
 #undef SMAT_TALL_MMA
                     PROF_MARK(10);
-                    if (leader) {
-                        if (count) tc_commit(step_done(pi % NPAIR));
-                        else mbar_arrive(step_done(pi % NPAIR));
-                    }
-#ifdef SMAT_PROFILE
-                    if (leader) atomicMax(&stamp_mma[pi % 8], (unsigned int)clock());
-#endif
                     PROF_MARK(11);
                 }
                 if (leader) tc_commit(acc_full);

@@ -749,8 +749,8 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
         }
     }
     // Tall plan: groups of up to 24 block-rows for the kernel that reads the B panels from tensor memory.  Its steps
-    // cost a little more than those of the 16-row kernels (measured ~600 against ~540 cycles, the latter growing with
-    // the blocks of the step: ~48 cycles each with the hand-overs, the shared-memory operand port), so it pays where taller groups mean
+    // cost a little more than those of the 16-row kernels (measured ~600 against ~470 cycles, the latter growing with
+    // the blocks of the step: ~45 cycles each with the hand-overs, the shared-memory operand port), so it pays where taller groups mean
     // fewer steps: matrices whose quads mostly hold a block (a block-sparse layer, a reordered random matrix: three
     // quarters of the steps), not scattered ones (as many steps as before) and not dense clusters (steps of 32 blocks
     // already).  Both plans are counted and the estimates compared; smat_spmm_set_variant(4) forces a tall plan,
@@ -803,7 +803,7 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
         if (rc == SMAT_OK) {
             const double per_step = (double)range_blocks / (double)total_steps;
             const double est16 = rounds_for(sz.n_groups * tiles, (size_t)ctx->sm_count, true, (size_t)steps_per_group, false) * steps_per_group *
-                                 (per_step * 48.0 > 540.0 ? per_step * 48.0 : 540.0);
+                                 (per_step * 45.0 > 470.0 ? per_step * 45.0 : 470.0);
             const double steps_per_tall = (double)tall_total_and_max[0] / (double)sz_tall.n_groups;
             const double est_tall =
                 rounds_for(sz_tall.n_groups * tiles, (size_t)ctx->sm_count, true, (size_t)steps_per_tall, false) * steps_per_tall * 600.0;

@@ -440,6 +440,9 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_const
                     const uint32_t whi = ld_shared_u32(base + OFF_META + slot * 8 + 4);
                     const uint32_t mw0 = __ballot_sync(0xffffffffu, (wlo >> lane) & 1u);
                     const uint32_t mw1 = __ballot_sync(0xffffffffu, (whi >> lane) & 1u);
+                    // one region of the elected lane per step: every separate `if (leader)` costs the warp a
+                    // divergence and a reconvergence
+                    if (leader) {
                     uint32_t qbase = 0;
 #pragma unroll
                     for (int half = 0; half < 2; half++) {
@@ -453,20 +456,19 @@ spmm_bcsr_tc_kernel(const __grid_constant__ CUtensorMap mapB, const __grid_const
                             const uint32_t r0 = b & 15u, sub = (uint32_t)half * 2u + (b >> 4);
                             const uint32_t idesc = IDESC_N0 + ((2u * len) << 17);
                             own &= ~(((1u << len) - 1u) << b);
-                            if (leader) {
-                                if (TS) {
-                                    mma_f16_ts_lohi(acc0 + r0 * 16, tpanel + sub * 8u, b_lo + q * (ABLK_BYTES >> 4), B_HI, idesc, 1u);
-                                } else {
+                            if (TS) {
+                                mma_f16_ts_lohi(acc0 + r0 * 16, tpanel + sub * 8u, b_lo + q * (ABLK_BYTES >> 4), B_HI, idesc, 1u);
+                            } else {
 #pragma unroll
-                                    for (int h = 0; h < NH; h++)  // one MMA per 128-column half, each into its own accumulators
-                                        mma_f16_ss_lohi(acc0 + (h * RG + r0) * 16, p_lo + sub * 2u + h * (128 * 128 >> 4), P_HI,
-                                                        b_lo + q * (ABLK_BYTES >> 4), B_HI, idesc, 1u);
-                                }
+                                for (int h = 0; h < NH; h++)  // one MMA per 128-column half, each into its own accumulators
+                                    mma_f16_ss_lohi(acc0 + (h * RG + r0) * 16, p_lo + sub * 2u + h * (128 * 128 >> 4), P_HI,
+                                                    b_lo + q * (ABLK_BYTES >> 4), B_HI, idesc, 1u);
                             }
                         }
                         qbase += (uint32_t)__popc(mw);
                     }
-                    if (leader) tc_commit(empty(slot));
+                    tc_commit(empty(slot));
+                    }
                 }
                 if (leader) tc_commit(acc_full(buf));
                 ++it;

@@ -355,11 +355,26 @@ spmm_bcsr_tall_kernel(const __grid_constant__ CUtensorMap mapB, const uint8_t* _
                     const uint32_t b_lo = b_lo0 + bs * (BLK_SLOT_BYTES >> 4);
                     const uint32_t count = w[0] >> 28;
                     PROF_MARK(9);
+                    // operands of the first four entries (most lists are no longer) worked out here, where the warp is
+                    // converged and the values stay in uniform registers; the elected lane's region below only issues
+                    uint32_t od[4], oa[4], ob[4], oi[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const uint32_t e = (i & 1) ? (w[i >> 1] >> 16) : w[i >> 1];
+                        od[i] = acc_m + ((e >> 5) & 16u);
+                        oa[i] = tpanel + ((e >> 3) & 56u);
+                        ob[i] = b_lo + (e & 63u) * 32u;
+                        oi[i] = IDESC16 + ((e << 8) & (1u << 18));
+                    }
 #define SMAT_TALL_MMA(i)                                                                                               \
     {                                                                                                                  \
-        const uint32_t e = ((i) & 1) ? (w[(i) >> 1] >> 16) : w[(i) >> 1];                                              \
-        mma_f16_ts_lohi(acc_m + ((e >> 5) & 16u), tpanel + ((e >> 3) & 56u), b_lo + (e & 63u) * 32u, B_HI,             \
-                        IDESC16 + ((e << 8) & (1u << 18)), 1u);                                                        \
+        if ((i) < 4) {                                                                                                 \
+            mma_f16_ts_lohi(od[(i) & 3], oa[(i) & 3], ob[(i) & 3], B_HI, oi[(i) & 3], 1u);                             \
+        } else {                                                                                                       \
+            const uint32_t e = ((i) & 1) ? (w[(i) >> 1] >> 16) : w[(i) >> 1];                                          \
+            mma_f16_ts_lohi(acc_m + ((e >> 5) & 16u), tpanel + ((e >> 3) & 56u), b_lo + (e & 63u) * 32u, B_HI,         \
+                            IDESC16 + ((e << 8) & (1u << 18)), 1u);                                                    \
+        }                                                                                                              \
     }
                     static_assert(IDESC32 == IDESC16 + (1u << 18), "the 32-column descriptor is the 16-column one plus bit 18");
                     // one region of the elected lane per pair (every separate `if (leader)` costs the warp a divergence

@@ -749,7 +749,7 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
         }
     }
     // Tall plan: groups of up to 24 block-rows for the kernel that reads the B panels from tensor memory.  Its steps
-    // cost a little more than those of the 16-row kernels (measured ~600 against ~470 cycles, the latter growing with
+    // cost a little more than those of the 16-row kernels (measured ~550 against ~470 cycles, the latter growing with
     // the blocks of the step: ~45 cycles each with the hand-overs, the shared-memory operand port), so it pays where taller groups mean
     // fewer steps: matrices whose quads mostly hold a block (a block-sparse layer, a reordered random matrix: three
     // quarters of the steps), not scattered ones (as many steps as before) and not dense clusters (steps of 32 blocks
@@ -806,8 +806,8 @@ int smat_plan_create(smat_plan** out, const void* bcsrValuesA, const int* bcsrRo
                                  (per_step * 45.0 > 470.0 ? per_step * 45.0 : 470.0);
             const double steps_per_tall = (double)tall_total_and_max[0] / (double)sz_tall.n_groups;
             const double est_tall =
-                rounds_for(sz_tall.n_groups * tiles, (size_t)ctx->sm_count, true, (size_t)steps_per_tall, false) * steps_per_tall * 600.0;
-            tall = tall_forced || est_tall < 0.95 * est16;
+                rounds_for(sz_tall.n_groups * tiles, (size_t)ctx->sm_count, true, (size_t)steps_per_tall, false) * steps_per_tall * 550.0;
+            tall = tall_forced || est_tall < 0.97 * est16;
             if (std::getenv("SMAT_PLAN_DEBUG"))
                 fprintf(stderr, "[smat plan] estimates: 16-row %.0f cycles, tall (rg %zu, %d steps) %.0f cycles -> %s\n", est16, rg_tall,
                         tall_total_and_max[0], est_tall, tall ? "tall" : "16-row");

@@ -64,3 +64,26 @@ def test_balanced_schedule_arithmetic():
         if rng.random() < 0.2:
             ns = rng.integers(0, 3, ng)                              # fewer steps than CTAs
         _check(ns, int(rng.integers(1, 4)), int(rng.integers(1, 149)), rng)
+
+
+def test_cut_last_round_at_multiples_of_a_quantum():
+    """The round-robin schedule cuts the items of the last round into P segments at k = (ns / q) * j / P * q
+    (spmm_sched.cuh, SegGen<0>): q = 1 for the 16-row kernels, q = 2 for the tall kernel, whose plans pad every group
+    to an even number of steps and whose MMA warps take the steps two at a time.  Restated here: the segments tile
+    [0, ns) in order, every cut is a multiple of q, and the last segment ends at ns whatever ns is."""
+    rng = np.random.default_rng(1)
+    for _ in range(2000):
+        q = int(rng.choice([1, 2]))
+        ns = int(rng.integers(0, 4000))
+        if q == 2:
+            ns += ns & 1  # tall plans: even step counts
+        P = int(rng.integers(1, 5))  # kMaxTailParts = 4
+        nq = ns // q
+        cuts = [(nq * j // P) * q for j in range(P)] + [ns]
+        for j in range(P):
+            k0, k1 = cuts[j], (ns if j + 1 == P else (nq * (j + 1) // P) * q)
+            assert k1 == cuts[j + 1] and 0 <= k0 <= k1 <= ns
+            assert k0 % q == 0 and (k1 % q == 0 or k1 == ns)
+            if q == 2:
+                assert (k1 - k0) % 2 == 0  # a pair of steps never spans two segments
+        assert cuts[0] == 0 and cuts[-1] == ns

@@ -169,6 +169,24 @@ int smat_bcsr_knapsack(const int* csr_rowptr, const int* csr_colidx, const uint1
 int smat_knapsack_to_csr(const int* bcsr_rowptr, const int* bcsr_colidx, const uint16_t* bcsr_vals, size_t M, size_t K,
                          size_t* nnz, int** csr_rowptr, int** csr_colidx, uint16_t** csr_vals);
 
+/* Variable-height blocking (host).  Replaces VBR::fill_from_CSR_inplace(cmat, grouping, col_block_size)
+ * (preprocess/src/general/vbr.cpp:135-237, with get_permutation / get_partition, utilities.cpp:8-43), the blocked format
+ * of the reference's preprocessing library when a grouping of unequal groups is kept as it is (its pipeline for the
+ * kernels above passes -F 1 and gets 16-row groups): rows are taken in the order of an argsort of `grouping` (int64 per
+ * row; negative numbers allowed, the smallest must not be -1), each group becomes a block-row of its own height, and
+ * a block of that height x col_block columns is stored where any of its rows has a stored entry.  Output arrays are
+ * malloc'ed (release with smat_free_host) and laid out as the reference's: row_part int64[block_rows + 1], row_perm
+ * int64[M] (permuted position -> original row), nzcount int64[block_rows], jab int64[nblocks] (block-columns,
+ * ascending inside a block-row), mab fp16 bit patterns, block after block, each column-major (height contiguous).
+ * The SpMM entry points above take 16-row blocks only; smat_vbr_to_csr converts back (entries that are zero inside a
+ * block are dropped). */
+int smat_vbr_from_csr(const int* csr_rowptr, const int* csr_colidx, const uint16_t* csr_vals, size_t M, size_t K,
+                      const int64_t* grouping, size_t col_block, size_t* block_rows, int64_t** row_part, int64_t** row_perm,
+                      int64_t** nzcount, size_t* nblocks, int64_t** jab, size_t* nvals, uint16_t** mab);
+int smat_vbr_to_csr(size_t M, size_t K, size_t col_block, size_t block_rows, const int64_t* row_part, const int64_t* row_perm,
+                    const int64_t* nzcount, const int64_t* jab, const uint16_t* mab, size_t* nnz, int** csr_rowptr,
+                    int** csr_colidx, uint16_t** csr_vals);
+
 /* Matrix-Market reader (host).  Replaces mmio_allinone
  * (src/cuda_hgemm/src/common/mmio_highlevel.h:619-786): dimensions padded up to multiples of 16,
  * 0-based CSR in file order inside each row, symmetric/hermitian files mirrored, pattern files get

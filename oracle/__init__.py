@@ -91,6 +91,10 @@ def ref():
         if hasattr(L, "ref_vbr_from_csr"):
             L.ref_vbr_from_csr.restype = C.c_long
             L.ref_vbr_from_csr.argtypes = [C.c_long, C.c_long, i32p, i32p, f32p, C.c_long, C.c_long, C.c_long, i64p, i64p, f32p]
+        if hasattr(L, "ref_vbr_from_grouping"):
+            L.ref_vbr_from_grouping.restype = C.c_long
+            L.ref_vbr_from_grouping.argtypes = [C.c_long, C.c_long, i32p, i32p, f32p, i64p, C.c_long, C.c_long, C.c_long, C.c_long,
+                                                i64p, i64p, i64p, i64p, i64p, f32p]
         _REF = L
     return _REF
 
@@ -201,6 +205,35 @@ def reorder_rows(rowptr, cols, tau=0.5, col_block=16, row_block=16):
     p = np.zeros(max(rows, 1), np.int64)
     lib().orc_reorder_rows(rows, _i64(rowptr), _i64(cols), tau, col_block, row_block, g, p)
     return g[:rows], p[:rows]
+
+
+def ref_vbr_from_grouping(M, K, rowptr, colidx, vals, grouping, col_block):
+    """Variable-height blocking by the UNMODIFIED reference code VBR::fill_from_CSR_inplace(cmat, grouping, col_block)
+    (oracle/_ref): dict of row_part, nzcount, jab (int64), mab (float32, column-major blocks) and row_perm (the
+    reference's get_permutation of the grouping).  Costs O(nnz * K / col_block) in the reference: small matrices only."""
+    R = ref()
+    if R is None or not hasattr(R, "ref_vbr_from_grouping"):
+        raise RuntimeError("oracle/_ref/libsmat_ref.so with ref_vbr_from_grouping is not built")
+    rowptr = np.ascontiguousarray(rowptr, dtype=np.int32)
+    colidx = np.ascontiguousarray(colidx, dtype=np.int32)
+    vals32 = np.ascontiguousarray(np.asarray(vals, dtype=np.float16).astype(np.float32))
+    if colidx.size == 0:
+        colidx, vals32 = np.zeros(1, np.int32), np.zeros(1, np.float32)
+    g = np.ascontiguousarray(grouping, dtype=np.int64)
+    Kb = (K - 1) // col_block + 1
+    max_blocks = int(min(len(colidx), M * Kb)) + 1
+    max_vals = max_blocks * M * col_block if M * col_block * max_blocks < (1 << 26) else (1 << 26)
+    br, nv = np.zeros(1, np.int64), np.zeros(1, np.int64)
+    part, nzc = np.zeros(M + 1, np.int64), np.zeros(M, np.int64)
+    jab, mab = np.zeros(max_blocks, np.int64), np.zeros(max_vals, np.float32)
+    nb = R.ref_vbr_from_grouping(M, K, rowptr, colidx, vals32, g, col_block, M, max_blocks, max_vals, br, part, nzc, jab, nv, mab)
+    if nb < 0:
+        raise RuntimeError("ref_vbr_from_grouping: bound too small")
+    perm = np.zeros(M, np.int64)
+    R.ref_get_permutation(M, g, perm)
+    n_br = int(br[0])
+    return {"col_block": col_block, "row_part": part[: n_br + 1].copy(), "row_perm": perm, "nzcount": nzc[:n_br].copy(),
+            "jab": jab[:nb].copy(), "mab": mab[: int(nv[0])].copy()}
 
 
 def ref_bcsr_via_vbr(M, K, rowptr, colidx, vals):

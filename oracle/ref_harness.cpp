@@ -145,4 +145,53 @@ long ref_vbr_from_csr(long rows, long cols, const int* rowptr, const int* colidx
     return rc;
 }
 
+// VBR::fill_from_CSR_inplace(cmat, grouping, col_block) of the unmodified reference: the variable-height blocking
+// (one block-row per group of the grouping, rows in the order of the reference's get_permutation).  Outputs: row_part
+// (block_rows + 1 entries), nzcount, jab, mab (column-major blocks, floats).  Returns the number of blocks, -1 when a
+// bound is too small; *block_rows_out and *nvals_out are set either way.
+long ref_vbr_from_grouping(long rows, long cols, const int* rowptr, const int* colidx, const float* vals, const long* grouping,
+                           long col_block, long max_block_rows, long max_blocks, long max_vals, long* block_rows_out,
+                           long* row_part_out, long* nzcount_out, long* jab_out, long* nvals_out, float* mab_out) {
+    CSR* c = static_cast<CSR*>(::operator new(sizeof(CSR)));
+    c->rows = rows;
+    c->cols = cols;
+    c->pattern_only = false;
+    c->nzcount = new intT[rows];
+    c->ja = new intT*[rows];
+    c->ma = new DataT*[rows];
+    for (long r = 0; r < rows; r++) {
+        const long n = rowptr[r + 1] - rowptr[r];
+        c->nzcount[r] = n;
+        c->ja[r] = new intT[n > 0 ? n : 1];
+        c->ma[r] = new DataT[n > 0 ? n : 1];
+        for (long j = 0; j < n; j++) {
+            c->ja[r][j] = colidx[rowptr[r] + j];
+            c->ma[r][j] = vals[rowptr[r] + j];
+        }
+    }
+    std::vector<intT> g((size_t)rows);
+    for (long r = 0; r < rows; r++) g[(size_t)r] = (intT)grouping[r];
+    VBR v;
+    v.fill_from_CSR_inplace(*c, g, (intT)col_block);
+    long nb = 0;
+    for (long ib = 0; ib < v.block_rows; ib++) nb += v.nzcount[ib];
+    *block_rows_out = v.block_rows;
+    *nvals_out = v.nztot;
+    long rc = nb;
+    if (v.block_rows > max_block_rows || nb > max_blocks || v.nztot > max_vals) {
+        rc = -1;
+    } else {
+        for (long ib = 0; ib <= v.block_rows; ib++) row_part_out[ib] = v.row_part[ib];
+        for (long ib = 0; ib < v.block_rows; ib++) nzcount_out[ib] = v.nzcount[ib];
+        for (long i = 0; i < nb; i++) jab_out[i] = v.jab[i];
+        memcpy(mab_out, v.mab, sizeof(DataT) * (size_t)v.nztot);
+    }
+    for (long r = 0; r < rows; r++) { delete[] c->ja[r]; delete[] c->ma[r]; }
+    delete[] c->nzcount;
+    delete[] c->ja;
+    delete[] c->ma;
+    ::operator delete(c);
+    return rc;
+}
+
 }  // extern "C"

@@ -22,6 +22,8 @@ from .api import (  # noqa: F401
     bcsr_knapsack,
     jaccard_group,
     knapsack_to_csr,
+    vbr_from_csr,
+    vbr_to_csr,
     launch_count,
     lib,
     partition_block_rows,

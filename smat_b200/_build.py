@@ -6,7 +6,7 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.environ.get("SMAT_LIB", os.path.join(HERE, "libsmat_b200.so"))
-SOURCES = ["spmm_sm100.cu", "spmm_tall_sm100.cu", "plan.cu", "spmm_static.cu", "bcsr_build.cu", "capi.cu", "mtx_reader.cpp", "reorder.cpp", "knapsack.cpp"]
+SOURCES = ["spmm_sm100.cu", "spmm_tall_sm100.cu", "plan.cu", "spmm_static.cu", "bcsr_build.cu", "capi.cu", "mtx_reader.cpp", "reorder.cpp", "knapsack.cpp", "vbr_build.cpp"]
 HEADERS = ["ptx_sm100.cuh", "spmm_sched.cuh", "smat_internal.h", os.path.join("..", "..", "include", "smat_b200.h")]
 
 

@@ -205,6 +205,50 @@ def knapsack_to_csr(M, K, bcsr_rowptr, bcsr_colidx, bcsr_vals):
             _take(pv, nnz.value, C.c_uint16, np.float16))
 
 
+def vbr_from_csr(M, K, rowptr, colidx, vals, grouping, col_block=16):
+    """Variable-height blocking (VBR::fill_from_CSR_inplace with a grouping, preprocess/src/general/vbr.cpp:135-237):
+    every group of rows becomes a block-row of its own height.  Returns a dict with the reference's arrays: row_part,
+    row_perm, nzcount, jab (int64) and mab (float16, blocks column-major), plus col_block."""
+    rp = np.ascontiguousarray(rowptr, dtype=np.int32)
+    ci = np.ascontiguousarray(colidx, dtype=np.int32)
+    v = np.ascontiguousarray(vals, dtype=np.float16).view(np.uint16)
+    g = np.ascontiguousarray(grouping, dtype=np.int64)
+    assert g.size == M
+    i64pp, szp = C.POINTER(C.POINTER(C.c_int64)), C.POINTER(C.c_size_t)
+    br, nb, nv = C.c_size_t(), C.c_size_t(), C.c_size_t()
+    ppart, pperm, pnz, pjab, pmab = (C.POINTER(C.c_int64)(), C.POINTER(C.c_int64)(), C.POINTER(C.c_int64)(),
+                                     C.POINTER(C.c_int64)(), C.POINTER(C.c_uint16)())
+    L = lib()
+    L.smat_vbr_from_csr.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t, szp, i64pp,
+                                    i64pp, i64pp, szp, i64pp, szp, C.POINTER(C.POINTER(C.c_uint16))]
+    _check(L.smat_vbr_from_csr(rp.ctypes.data, ci.ctypes.data if ci.size else None, v.ctypes.data if v.size else None, M, K,
+                               g.ctypes.data, col_block, C.byref(br), C.byref(ppart), C.byref(pperm), C.byref(pnz), C.byref(nb),
+                               C.byref(pjab), C.byref(nv), C.byref(pmab)))
+    return {"col_block": col_block, "row_part": _take(ppart, br.value + 1, C.c_int64, np.int64),
+            "row_perm": _take(pperm, M, C.c_int64, np.int64), "nzcount": _take(pnz, br.value, C.c_int64, np.int64),
+            "jab": _take(pjab, nb.value, C.c_int64, np.int64), "mab": _take(pmab, nv.value, C.c_uint16, np.float16)}
+
+
+def vbr_to_csr(M, K, vbr):
+    """Back from the variable-height blocking to CSR (columns ascending; zero entries of a block are dropped)."""
+    part = np.ascontiguousarray(vbr["row_part"], dtype=np.int64)
+    perm = np.ascontiguousarray(vbr["row_perm"], dtype=np.int64)
+    nz = np.ascontiguousarray(vbr["nzcount"], dtype=np.int64)
+    jab = np.ascontiguousarray(vbr["jab"], dtype=np.int64)
+    mab = np.ascontiguousarray(vbr["mab"], dtype=np.float16).view(np.uint16)
+    nnz = C.c_size_t()
+    prp, pci, pv = C.POINTER(C.c_int)(), C.POINTER(C.c_int)(), C.POINTER(C.c_uint16)()
+    L = lib()
+    L.smat_vbr_to_csr.argtypes = [C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                  C.c_void_p, C.POINTER(C.c_size_t), C.POINTER(C.POINTER(C.c_int)), C.POINTER(C.POINTER(C.c_int)),
+                                  C.POINTER(C.POINTER(C.c_uint16))]
+    _check(L.smat_vbr_to_csr(M, K, int(vbr["col_block"]), part.size - 1, part.ctypes.data, perm.ctypes.data,
+                             nz.ctypes.data if nz.size else None, jab.ctypes.data if jab.size else None,
+                             mab.ctypes.data if mab.size else None, C.byref(nnz), C.byref(prp), C.byref(pci), C.byref(pv)))
+    return (_take(prp, M + 1, C.c_int, np.int32), _take(pci, nnz.value, C.c_int, np.int32),
+            _take(pv, nnz.value, C.c_uint16, np.float16))
+
+
 def b_slice_of_rank(N, world, rank):
     """Which rows of the [N][K] array B (= columns of the logical K x N matrix) a rank uploads in the sharded
     host-buffer product: (first, last + 1, rows per rank before the last one = the padded slice height).  Slices are

@@ -271,6 +271,36 @@ def formats_fixtures():
     print("formats fixtures:", sorted(os.listdir(out)))
 
 
+def vbr_cases():
+    """(name, M, K, rowptr, colidx, vals fp16, grouping, col_block): groupings of unequal groups, negative group
+    numbers as the clustering writes them for full groups, empty rows, a last block-column that sticks out of K."""
+    cases = []
+    for name, M, K, density, n_groups, cb, seed in [("small", 23, 40, 0.2, 6, 4, 1), ("ragged", 64, 100, 0.08, 11, 16, 2),
+                                                    ("tall", 96, 48, 0.1, 3, 8, 3), ("singletons", 17, 33, 0.3, 17, 5, 4)]:
+        rng = np.random.default_rng(seed)
+        mask = rng.random((M, K)) < density
+        mask[M // 2] = False  # an empty row
+        vals = (rng.standard_normal((M, K)) * mask).astype(np.float16)
+        mask = vals != 0
+        rowptr = np.zeros(M + 1, np.int32)
+        rowptr[1:] = np.cumsum(mask.sum(axis=1))
+        g = rng.integers(0, n_groups, M).astype(np.int64) if n_groups < M else rng.permutation(M).astype(np.int64)
+        full = rng.random(M) < 0.3
+        g = np.where(full & (g != M - 1), g - M, g)  # "full group" marks of the clustering (never -1)
+        cases.append((name, M, K, rowptr, np.nonzero(mask)[1].astype(np.int32), vals[mask], g, cb))
+    return cases
+
+
+def vbr_fixtures():
+    """Outputs of the unmodified VBR::fill_from_CSR_inplace(cmat, grouping, col_block) for vbr_cases()."""
+    for name, M, K, rowptr, colidx, vals, g, cb in vbr_cases():
+        v = oracle.ref_vbr_from_grouping(M, K, rowptr, colidx, vals, g, cb)
+        np.savez_compressed(os.path.join(HERE, f"vbr_{name}.npz"), M=M, K=K, rowptr=rowptr, colidx=colidx,
+                            vals=vals.view(np.uint16), grouping=g, col_block=cb, row_part=v["row_part"], row_perm=v["row_perm"],
+                            nzcount=v["nzcount"], jab=v["jab"], mab=v["mab"].astype(np.float16).view(np.uint16))
+        print("vbr", name, "block-rows", len(v["nzcount"]), "blocks", len(v["jab"]))
+
+
 if __name__ == "__main__":
     assert oracle.have_ref(), "build oracle/_ref first: make -C oracle ref REF=<reference tree>"
     similarities()
@@ -278,3 +308,4 @@ if __name__ == "__main__":
     multiply_fixtures()
     reader_fixtures()
     formats_fixtures()
+    vbr_fixtures()

@@ -107,6 +107,38 @@ def test_knapsack_blocking_matches_reference_run(path):
         assert np.array_equal(np.diff(rp2), np.bincount(rows[keep], minlength=M))
 
 
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(ROOT, "tests", "golden", "vbr_*.npz"))))
+def test_variable_height_blocking_matches_reference_run(path):
+    """smat_vbr_from_csr against the arrays the reference's own VBR::fill_from_CSR_inplace(cmat, grouping, col_block)
+    produced (fixtures): groups of unequal size, negative group numbers, an empty row, a last block-column that sticks
+    out of the matrix.  Everything is bit-exact, the order of the rows inside a group included (the reference's
+    unstable argsort).  Converting back gives the matrix again."""
+    z = np.load(path)
+    M, K, cb = int(z["M"]), int(z["K"]), int(z["col_block"])
+    rp, ci, v = z["rowptr"], z["colidx"], z["vals"].view(np.float16)
+    got = S.vbr_from_csr(M, K, rp, ci, v, z["grouping"], cb)
+    for key in ("row_part", "row_perm", "nzcount", "jab"):
+        assert np.array_equal(got[key], z[key]), key
+    assert np.array_equal(got["mab"].view(np.uint16), z["mab"])
+    heights = np.diff(got["row_part"])
+    assert got["mab"].size == int(np.sum(got["nzcount"] * heights)) * cb and heights.min() >= 1 and heights.sum() == M
+    rp2, ci2, v2 = S.vbr_to_csr(M, K, got)
+    assert np.array_equal(rp2, rp) and np.array_equal(ci2, ci) and np.array_equal(v2.view(np.uint16), v.view(np.uint16))
+
+
+def test_variable_height_blocking_rejects_bad_input():
+    rp = np.array([0, 1, 2], np.int32)
+    ci = np.array([0, 3], np.int32)
+    v = np.array([1.0, 2.0], np.float16)
+    with pytest.raises(S.SmatError):  # the reference's partition scan would lose a smallest group numbered -1
+        S.vbr_from_csr(2, 4, rp, ci, v, np.array([-1, 0]), 2)
+    with pytest.raises(S.SmatError):  # column outside the matrix
+        S.vbr_from_csr(2, 3, rp, ci, v, np.array([0, 0]), 2)
+    one = S.vbr_from_csr(2, 4, rp, ci, v, np.array([5, 5]), 4)  # one group of both rows, one block
+    assert one["row_part"].tolist() == [0, 2] and one["nzcount"].tolist() == [1] and one["jab"].tolist() == [0]
+    assert one["mab"].astype(np.float32).tolist() == [1.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 2.0]  # column-major, height 2
+
+
 def test_reader_matches_oracle(tmp_path):
     rng = np.random.default_rng(2)
     M, K, n = 253, 251, 3000  # not multiples of 16: both readers pad to 256 x 256

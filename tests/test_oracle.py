@@ -178,3 +178,27 @@ def test_live_reference_fuzz(tmp_path):
         assert R.ref_group_and_permute(str(el).encode(), tau, cb, rb, 1, n, G, P) == n
         g, p = oracle.reorder_rows(rowptr, cols, tau=tau, col_block=cb, row_block=rb)
         assert np.array_equal(G, g) and np.array_equal(P, p), case
+
+
+@pytest.mark.skipif(not (oracle.have_ref() and hasattr(oracle.ref(), "ref_vbr_from_grouping")),
+                    reason="oracle/_ref not built (reference tree absent)")
+def test_variable_height_blocking_matches_live_reference():
+    """smat_vbr_from_csr against the unmodified VBR::fill_from_CSR_inplace(cmat, grouping, col_block) run here, on
+    random matrices and groupings (many equal keys: the order inside a group is the unstable sort's)."""
+    import smat_b200 as S
+    rng = np.random.default_rng(77)
+    for _ in range(25):
+        M, K = int(rng.integers(1, 120)), int(rng.integers(1, 90))
+        cb = int(rng.integers(1, 20))
+        mask = rng.random((M, K)) < rng.uniform(0.02, 0.4)
+        vals = (rng.standard_normal((M, K)) * mask).astype(np.float16)
+        mask = vals != 0
+        rowptr = np.zeros(M + 1, np.int32)
+        rowptr[1:] = np.cumsum(mask.sum(axis=1))
+        colidx = np.nonzero(mask)[1].astype(np.int32)
+        g = rng.integers(0, max(1, M // int(rng.integers(1, 20))) + 1, M).astype(np.int64)
+        want = oracle.ref_vbr_from_grouping(M, K, rowptr, colidx, vals[mask], g, cb)
+        got = S.vbr_from_csr(M, K, rowptr, colidx, vals[mask], g, cb)
+        for key in ("row_part", "row_perm", "nzcount", "jab"):
+            assert np.array_equal(got[key], want[key]), key
+        assert np.array_equal(got["mab"].astype(np.float32), want["mab"])

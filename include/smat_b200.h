@@ -208,6 +208,12 @@ void smat_free_host(void* p);
  * threads <= 0 uses every hardware thread. */
 int smat_reorder_rows(size_t rows, const int64_t* rowptr, const int32_t* cols, float tau, int col_block,
                       int row_block, int threads, int64_t* grouping, int64_t* perm);
+/* The same clustering without the fixed-size regrouping (the program run without -F 1): grouping[rows] as
+ * BlockingEngine::GetGrouping returns it -- groups of at most max_group_rows rows, numbered by their seed row, full
+ * groups lowered by the row count -- and, if perm is not NULL, get_permutation of it.  With smat_vbr_from_csr this is
+ * the reference's variable-height blocking of a matrix. */
+int smat_cluster_rows(size_t rows, const int64_t* rowptr, const int32_t* cols, float tau, int col_block, int max_group_rows,
+                      int threads, int64_t* grouping, int64_t* perm);
 
 /* Jaccard distance on column-block quotients between a group pattern and a row
  * (JaccardDistanceGroup, preprocess/src/general/blocking.cpp:904-975). */

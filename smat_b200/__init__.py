@@ -22,6 +22,7 @@ from .api import (  # noqa: F401
     bcsr_knapsack,
     jaccard_group,
     knapsack_to_csr,
+    cluster_rows,
     vbr_from_csr,
     vbr_to_csr,
     launch_count,

@@ -119,6 +119,22 @@ def reorder_rows(rowptr, colidx, tau=0.5, col_block=16, row_block=16, threads=0)
     return grouping[:rows], perm[:rows]
 
 
+def cluster_rows(rowptr, colidx, tau=0.5, col_block=16, max_group_rows=16, threads=0):
+    """The clustering of ``reorder_rows`` without the fixed-size regrouping (`Matrix_Blocking` without -F 1): the
+    grouping as BlockingEngine::GetGrouping returns it (groups of unequal size, full groups numbered below zero) and
+    get_permutation of it.  Feed it to ``vbr_from_csr`` for the reference's variable-height blocking."""
+    rp = np.ascontiguousarray(rowptr, dtype=np.int64)
+    ci = np.ascontiguousarray(colidx, dtype=np.int32)
+    rows = rp.size - 1
+    grouping = np.zeros(max(rows, 1), np.int64)
+    perm = np.zeros(max(rows, 1), np.int64)
+    L = lib()
+    L.smat_cluster_rows.argtypes = L.smat_reorder_rows.argtypes
+    _check(L.smat_cluster_rows(rows, rp.ctypes.data, ci.ctypes.data if ci.size else None, tau, col_block, max_group_rows, threads,
+                               grouping.ctypes.data, perm.ctypes.data))
+    return grouping[:rows], perm[:rows]
+
+
 def apply_row_permutation(rowptr, colidx, vals, perm):
     """CSR with rows permuted: new row r = old row perm[r] (CSR::permute_rows,
     preprocess/src/general/csr.cpp:65-74).  Unlike the reference's text round trip, which drops the

@@ -211,10 +211,17 @@ float smat_jaccard_group(const int64_t* rowA, size_t sizeA, int64_t gA, const in
     return (float)((2.0 * (double)count) / (double)(nA * gA + nB * gB + count));
 }
 
-int smat_reorder_rows(size_t rows_, const int64_t* rowptr, const int32_t* cols, float tau, int col_block, int row_block,
-                      int threads, int64_t* grouping_out, int64_t* perm_out) {
+}  // extern "C"
+
+namespace {
+
+// The clustering, then either the fixed-size regrouping of the reference's -F 1 (fixed) or the grouping as the
+// clustering leaves it (numbers of full groups lowered by the row count, as the reference does), and the
+// permutation get_permutation derives from whichever it is.
+int reorder_impl(size_t rows_, const int64_t* rowptr, const int32_t* cols, float tau, int col_block, int row_block, int threads,
+                 bool fixed_size, int64_t* grouping_out, int64_t* perm_out) {
     clear_error();
-    if ((rows_ && (!rowptr || !grouping_out || !perm_out)) || col_block < 1 || row_block < 1)
+    if ((rows_ && (!rowptr || !grouping_out)) || col_block < 1 || row_block < 1)
         return fail(SMAT_ERR_BAD_ARG, "bad argument");
     const int64_t rows = (int64_t)rows_;
     if (rows == 0) return SMAT_OK;
@@ -369,12 +376,35 @@ int smat_reorder_rows(size_t rows_, const int64_t* rowptr, const int32_t* cols, 
         return v;
     };
     const std::vector<int64_t> p1 = argsort(grouping);
+    if (!fixed_size) {
+        memcpy(grouping_out, grouping.data(), (size_t)rows * sizeof(int64_t));
+        if (perm_out) memcpy(perm_out, p1.data(), (size_t)rows * sizeof(int64_t));
+        return SMAT_OK;
+    }
     std::vector<int64_t> fixed((size_t)rows, -1);
     for (int64_t x = 0; x < rows; x++) fixed[(size_t)p1[(size_t)x]] = x / row_block;
     const std::vector<int64_t> p2 = argsort(fixed);
     memcpy(grouping_out, fixed.data(), (size_t)rows * sizeof(int64_t));
-    memcpy(perm_out, p2.data(), (size_t)rows * sizeof(int64_t));
+    if (perm_out) memcpy(perm_out, p2.data(), (size_t)rows * sizeof(int64_t));
     return SMAT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int smat_reorder_rows(size_t rows, const int64_t* rowptr, const int32_t* cols, float tau, int col_block, int row_block,
+                      int threads, int64_t* grouping_out, int64_t* perm_out) {
+    if (rows && !perm_out) {
+        clear_error();
+        return fail(SMAT_ERR_BAD_ARG, "bad argument");
+    }
+    return reorder_impl(rows, rowptr, cols, tau, col_block, row_block, threads, true, grouping_out, perm_out);
+}
+
+int smat_cluster_rows(size_t rows, const int64_t* rowptr, const int32_t* cols, float tau, int col_block, int max_group_rows,
+                      int threads, int64_t* grouping_out, int64_t* perm_out) {
+    return reorder_impl(rows, rowptr, cols, tau, col_block, max_group_rows, threads, false, grouping_out, perm_out);
 }
 
 }  // extern "C"

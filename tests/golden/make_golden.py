@@ -114,6 +114,12 @@ def reorder_fixtures():
             np.savetxt(el, np.stack([np.repeat(np.arange(n), np.diff(rowptr)), cols], 1), fmt="%d")
             got = R.ref_group_and_permute(el.encode(), tau, cb, rb, 1, n, G, P)
         assert got == n and np.array_equal(G, g_prog), name
+        G_raw = np.zeros(n, np.int64)  # the clustering's own grouping (no -F 1) and its permutation
+        P_raw = np.zeros(n, np.int64)
+        with tempfile.TemporaryDirectory() as d:
+            el = os.path.join(d, "m.el")
+            np.savetxt(el, np.stack([np.repeat(np.arange(n), np.diff(rowptr)), cols], 1), fmt="%d")
+            assert R.ref_group_and_permute(el.encode(), tau, cb, rb, 0, n, G_raw, P_raw) == n
         # the program's reordered edge list must be the CSR with rows taken in order P
         lens = np.diff(rowptr)[P]
         exp_rows = np.repeat(np.arange(n), lens)
@@ -121,7 +127,7 @@ def reorder_fixtures():
         assert np.array_equal(reordered[:, 0], exp_rows) and np.array_equal(reordered[:, 1], exp_cols), name
         np.savez_compressed(os.path.join(HERE, f"reorder_{name}.npz"), rowptr=rowptr, cols=cols.astype(np.int32),
                             tau=np.float32(tau), col_block=cb, row_block=rb, grouping=G.astype(np.int32),
-                            perm=P.astype(np.int32))
+                            perm=P.astype(np.int32), raw_grouping=G_raw.astype(np.int32), raw_perm=P_raw.astype(np.int32))
         print("reorder", name, n, "rows; identity perm:", bool(np.array_equal(P, np.arange(n))))
 
 

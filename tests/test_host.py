@@ -194,6 +194,25 @@ def test_reorder_engine_matches_reference_fixtures(path, threads):
     g, p = S.reorder_rows(z["rowptr"], z["cols"], tau=float(z["tau"]), col_block=int(z["col_block"]),
                           row_block=int(z["row_block"]), threads=threads)
     assert np.array_equal(g, z["grouping"]) and np.array_equal(p, z["perm"])
+    # the clustering's own grouping (the program without -F 1) and its permutation
+    g, p = S.cluster_rows(z["rowptr"], z["cols"], tau=float(z["tau"]), col_block=int(z["col_block"]),
+                          max_group_rows=int(z["row_block"]), threads=threads)
+    assert np.array_equal(g, z["raw_grouping"]) and np.array_equal(p, z["raw_perm"])
+
+
+def test_cluster_then_variable_height_blocking_round_trip():
+    """The reference's other blocking end to end on the host: cluster the rows (groups of at most 12 rows, 8-column
+    blocks), block every group at its own height, convert back: the matrix again, its rows found through row_perm."""
+    p = gen.make_config("uniform", scale=0.01)
+    g, perm = S.cluster_rows(p.rowptr, p.colidx, tau=0.5, col_block=8, max_group_rows=12, threads=2)
+    vbr = S.vbr_from_csr(p.M, p.K, p.rowptr, p.colidx, p.vals, g, col_block=8)
+    assert np.array_equal(vbr["row_perm"], perm) and np.diff(vbr["row_part"]).max() <= 12
+    assert int(vbr["row_part"][-1]) == p.M and vbr["jab"].size == int(vbr["nzcount"].sum())
+    rp, ci, v = S.vbr_to_csr(p.M, p.K, vbr)
+    keep = (p.vals.view(np.uint16) & 0x7fff) != 0
+    rows = np.repeat(np.arange(p.M), np.diff(p.rowptr))
+    assert np.array_equal(np.diff(rp), np.bincount(rows[keep], minlength=p.M))
+    assert np.array_equal(ci, p.colidx[keep]) and np.array_equal(v.view(np.uint16), p.vals[keep].view(np.uint16))
 
 
 @pytest.mark.parametrize("name,scale", [("uniform", 0.06), ("powerlaw", 0.03), ("clustered", 0.008), ("band", 0.5)])

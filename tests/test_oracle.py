@@ -178,6 +178,15 @@ def test_live_reference_fuzz(tmp_path):
         assert R.ref_group_and_permute(str(el).encode(), tau, cb, rb, 1, n, G, P) == n
         g, p = oracle.reorder_rows(rowptr, cols, tau=tau, col_block=cb, row_block=rb)
         assert np.array_equal(G, g) and np.array_equal(P, p), case
+        # without -F 1: the clustering's own grouping (unequal groups) and its permutation, from the product
+        import smat_b200 as S
+        assert R.ref_group_and_permute(str(el).encode(), tau, cb, rb, 0, n, G, P) == n
+        g, p = S.cluster_rows(rowptr, cols, tau=tau, col_block=cb, max_group_rows=rb)
+        assert np.array_equal(G, g) and np.array_equal(P, p), case
+        g2, p2 = S.reorder_rows(rowptr, cols, tau=tau, col_block=cb, row_block=rb)
+        fixed = np.zeros(n, np.int64)
+        R.ref_fixed_size_grouping(n, G, rb, fixed)
+        assert np.array_equal(fixed, g2), case
 
 
 @pytest.mark.skipif(not (oracle.have_ref() and hasattr(oracle.ref(), "ref_vbr_from_grouping")),
